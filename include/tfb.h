@@ -1,0 +1,102 @@
+/* libtfb — C-ABI of the B200-native dense-contraction path for tensorforge.
+ *
+ * Everything a host runtime needs to route Tensor::matmul, nn::Linear, nn::Conv2d and
+ * MatmulBackward through hand-written sm_100a kernels. Plain pointers and sizes only;
+ * device pointers refer to the CUDA device that is current on the calling thread.
+ * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream), as in the
+ * reference launchers, so callers compiled without CUDA headers can use this file.
+ *
+ * All functions return 0 on success or a negative TFB_ERR_* code; they never throw and
+ * never fall back to a CPU or library implementation. Work is enqueued on `stream` and
+ * is asynchronous with respect to the host unless stated otherwise.
+ *
+ * Citations "ref:" name the file:line of the reference interface each entry point
+ * replaces (paths relative to the reference project root).
+ */
+#ifndef TFB_H_
+#define TFB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same numbering as the reference's `enum class Dtype` (ref: tensor/Dtype.hpp:9-16). */
+#define TFB_DTYPE_F32 0
+#define TFB_DTYPE_F16 1
+#define TFB_DTYPE_BF16 2
+
+#define TFB_OK 0
+#define TFB_ERR_INVALID_ARG (-1)   /* null pointer, negative size, bad flag */
+#define TFB_ERR_UNSUPPORTED (-2)   /* dtype / layout / alignment the kernels do not take */
+#define TFB_ERR_CUDA (-3)          /* a CUDA runtime or driver call failed */
+#define TFB_ERR_DEVICE (-4)        /* a kernel recorded an error (see tfb_device_status) */
+#define TFB_ERR_NO_MEMORY (-5)
+#define TFB_ERR_TOO_LARGE (-6)     /* exceeds a stated fixed limit */
+
+/* Epilogue flags for tfb_gemm_ex. */
+#define TFB_EPI_NONE 0
+#define TFB_EPI_BIAS_COL 1   /* C[m,n] += bias[n]  (Linear) */
+#define TFB_EPI_BIAS_ROW 2   /* C[m,n] += bias[m]  (Conv2d output channel) */
+#define TFB_EPI_RELU 4       /* C = max(C, 0) after the bias */
+
+/* ---- library -------------------------------------------------------------------- */
+
+/* Idempotent set-up for the current device (resolves the driver's tensor-map encoder,
+ * allocates the device status word, raises the kernels' shared-memory limit). Called
+ * implicitly by every other entry point. ref: the static registrars of
+ * cuda/kernels/elementwise.cu:306-336 plus the explicit init_tensor_autograd() pattern
+ * of tensor/AutogradWirer.hpp:72-76. */
+int tfb_init(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* tfb_last_error_string(void);
+
+/* Synchronises the current device and reports the first error code a kernel recorded
+ * (0 = none; 101..106 = a bounded wait inside a kernel ran out), then clears it. The
+ * reference never checks launches (ref: cuda/kernels/gemm.cu:82-87 has no
+ * cudaGetLastError); this is the replacement's fail-soft channel. */
+int tfb_device_status(int* code_out);
+
+/* ---- GEMM ------------------------------------------------------------------------ */
+
+/* C[M,N] = A[M,K] · B[K,N], all row-major and dense, C of the same dtype as A and B,
+ * FP32 accumulation. FP32 inputs run as an error-compensated 3xTF32 product. Like the
+ * reference launchers it is a silent no-op for M, N or K <= 0 and for unknown dtypes.
+ * ref: launch_gemm_naive / launch_gemm_tiled_16x16 / launch_gemm_optimized,
+ * cuda/kernels/gemm.cuh:33-53, cuda/kernels/gemm.cu:275-357. */
+int tfb_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int dtype,
+             void* stream);
+
+/* The CUDA branch of Tensor::matmul: same contraction, separate input and output dtypes
+ * (F32 -> F32; F16/BF16 -> F32 or the input dtype). Unlike tfb_gemm it reports bad
+ * arguments. ref: Tensor::matmul, tensor/Tensor.cpp:334-368; the registry slot it fills
+ * sits beside register_cuda_add in cuda/CudaKernelRegistry.hpp:15-26. */
+int tfb_matmul(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+               int in_dtype, int out_dtype, void* stream);
+
+/* General form. op(A) is M x K, op(B) is K x N:
+ *   trans_a = 0: A stored [M,K] row-major (lda >= K); 1: A stored [K,M] row-major (lda >= M)
+ *   trans_b = 0: B stored [K,N] row-major (ldb >= N); 1: B stored [N,K] row-major (ldb >= K)
+ * C is [M,N] row-major (ldc >= N). `bias` is FP32 and is read only when an
+ * TFB_EPI_BIAS_* flag is set. Transposed operands are consumed in place through the
+ * matching shared-memory descriptor; no transpose copy is made.
+ * ref: replaces launch_transpose_2d + launch_gemm_* pairs (cuda/kernels/transpose.cu:29-37,
+ * nn/Conv2d.cpp:182-198) and launch_bias_add (cuda/kernels/bias_add.cu:49-58). */
+int tfb_gemm_ex(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b, int in_dtype,
+                int out_dtype, const float* bias, int epilogue_flags, void* stream);
+
+/* dA[M,K] = dC[M,N] · Bᵀ and dB[K,N] = Aᵀ · dC for C = A · B (row-major, dense). Either
+ * output pointer may be NULL to skip it. ref: MatmulBackward::apply,
+ * autograd/ops/MatmulBackward.hpp:26-34. */
+int tfb_matmul_backward(const void* dC, const void* A, const void* B, void* dA, void* dB,
+                        int64_t M, int64_t N, int64_t K, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TFB_H_ */

@@ -1,0 +1,62 @@
+"""ctypes declarations for every symbol of include/tfb.h."""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtfb.so")
+
+DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
+EPI_NONE, EPI_BIAS_COL, EPI_BIAS_ROW, EPI_RELU = 0, 1, 2, 4
+
+
+class TfbError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"libtfb error {code}: {message}")
+        self.code = code
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `make -C tensors_b200/csrc` "
+        "(or `python -c 'import __graft_entry__ as g; g.build()'`). There is no fallback path."
+    )
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i64, _i32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+_ip = ctypes.POINTER(ctypes.c_int)
+
+# name -> (restype, argtypes); kept in the order of include/tfb.h
+PROTOTYPES = {
+    "tfb_init": (_i32, []),
+    "tfb_last_error_string": (ctypes.c_char_p, []),
+    "tfb_device_status": (_i32, [_ip]),
+    "tfb_gemm": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tfb_gemm_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
+                           _vp, _i32, _vp]),
+    "tfb_matmul_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+}
+
+for _name, (_res, _args) in PROTOTYPES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.tfb_last_error_string().decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise TfbError(rc, last_error())
+
+
+def device_status() -> int:
+    """Synchronises the current device and returns the first error a kernel recorded."""
+    code = ctypes.c_int(0)
+    rc = lib.tfb_device_status(ctypes.byref(code))
+    if rc != 0 and code.value == 0:
+        raise TfbError(rc, last_error())
+    return code.value

@@ -1,0 +1,65 @@
+// extern "C" entry points of the GEMM family.
+#include "internal.hpp"
+
+using namespace tfb;
+
+namespace {
+bool known_dtype(int d) { return d == TFB_DTYPE_F32 || d == TFB_DTYPE_F16 || d == TFB_DTYPE_BF16; }
+}  // namespace
+
+extern "C" {
+
+int tfb_gemm_ex(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                int64_t ldb, int64_t ldc, int trans_a, int trans_b, int in_dtype, int out_dtype,
+                const float* bias, int epilogue_flags, void* stream) {
+    if (M < 0 || N < 0 || K < 0) return fail(TFB_ERR_INVALID_ARG, "gemm_ex: negative extent");
+    if (!known_dtype(in_dtype) || !known_dtype(out_dtype))
+        return fail(TFB_ERR_UNSUPPORTED, "gemm_ex: unknown dtype (in %d, out %d)", in_dtype, out_dtype);
+    if ((epilogue_flags & TFB_EPI_BIAS_COL) && (epilogue_flags & TFB_EPI_BIAS_ROW))
+        return fail(TFB_ERR_INVALID_ARG, "gemm_ex: both bias modes requested");
+    GemmCall c;
+    c.A = A; c.B = B; c.C = C;
+    c.M = M; c.N = N; c.K = K;
+    c.lda = lda; c.ldb = ldb; c.ldc = ldc;
+    c.a_kmajor = (trans_a == 0);
+    c.b_kmajor = (trans_b != 0);
+    c.in_dtype = in_dtype; c.out_dtype = out_dtype;
+    c.bias = bias;
+    c.bias_mode = (epilogue_flags & TFB_EPI_BIAS_COL) ? 1 : ((epilogue_flags & TFB_EPI_BIAS_ROW) ? 2 : 0);
+    c.relu = (epilogue_flags & TFB_EPI_RELU) != 0;
+    return gemm_run(c, static_cast<cudaStream_t>(stream));
+}
+
+int tfb_matmul(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int in_dtype,
+               int out_dtype, void* stream) {
+    return tfb_gemm_ex(A, B, C, M, N, K, K, N, N, 0, 0, in_dtype, out_dtype, nullptr, TFB_EPI_NONE, stream);
+}
+
+int tfb_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int dtype,
+             void* stream) {
+    // Mirrors the reference launchers: nothing happens for empty problems or unknown dtypes.
+    if (M <= 0 || N <= 0 || K <= 0 || !known_dtype(dtype)) return TFB_OK;
+    return tfb_matmul(A, B, C, M, N, K, dtype, dtype, stream);
+}
+
+int tfb_matmul_backward(const void* dC, const void* A, const void* B, void* dA, void* dB, int64_t M,
+                        int64_t N, int64_t K, int dtype, void* stream) {
+    if (M < 0 || N < 0 || K < 0) return fail(TFB_ERR_INVALID_ARG, "matmul_backward: negative extent");
+    if (!known_dtype(dtype)) return fail(TFB_ERR_UNSUPPORTED, "matmul_backward: unknown dtype %d", dtype);
+    if (dC == nullptr) return fail(TFB_ERR_INVALID_ARG, "matmul_backward: null upstream gradient");
+    int rc = TFB_OK;
+    if (dA != nullptr) {
+        // dA[M,K] = dC[M,N] · Bᵀ : B is stored [K,N] = ["n"=K rows, contraction N contiguous].
+        if (B == nullptr) return fail(TFB_ERR_INVALID_ARG, "matmul_backward: dA needs B");
+        rc = tfb_gemm_ex(dC, B, dA, M, K, N, N, N, K, 0, 1, dtype, dtype, nullptr, TFB_EPI_NONE, stream);
+        if (rc != TFB_OK) return rc;
+    }
+    if (dB != nullptr) {
+        // dB[K,N] = Aᵀ · dC : A is stored [M,K] = [contraction M rows, "m"=K contiguous].
+        if (A == nullptr) return fail(TFB_ERR_INVALID_ARG, "matmul_backward: dB needs A");
+        rc = tfb_gemm_ex(A, dC, dB, K, N, M, K, N, N, 1, 0, dtype, dtype, nullptr, TFB_EPI_NONE, stream);
+    }
+    return rc;
+}
+
+}  // extern "C"

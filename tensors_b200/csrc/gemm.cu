@@ -1,0 +1,401 @@
+// Host side of the tcgen05 GEMM: tensor-map construction, operand preparation
+// (TF32 hi/lo split, re-packing of unaligned 16-bit operands), tile-shape choice, launch.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "gemm_kernel.cuh"
+#include "internal.hpp"
+
+namespace tfb {
+
+// ---------------------------------------------------------------------------
+// Tensor maps
+// ---------------------------------------------------------------------------
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+int resolve_encoder() {
+    std::call_once(g_encode_once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        else
+            (void)cudaGetLastError();
+    });
+    if (g_encode == nullptr)
+        return fail(TFB_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled");
+    return TFB_OK;
+}
+
+// `atom32` selects the 128-byte swizzle with 32-byte atoms that MN-major 32-bit operands need.
+// 2-D map over a row-major matrix: `inner` contiguous elements per row, `outer` rows,
+// rows `row_stride_bytes` apart; box of box_inner x box_outer elements, 128-byte swizzle,
+// out-of-range elements read as zero.
+int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
+             uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+             bool atom32 = false) {
+    CUtensorMapDataType dt = dtype == TFB_DTYPE_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                             : dtype == TFB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    cuuint64_t gdim[2] = {inner, outer};
+    cuuint64_t gstride[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TFB_ERR_CUDA,
+                    "cuTensorMapEncodeTiled failed with %d (inner %llu outer %llu stride %llu box %ux%u)",
+                    (int)r, (unsigned long long)inner, (unsigned long long)outer,
+                    (unsigned long long)row_stride_bytes, box_inner, box_outer);
+    return TFB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Operand preparation kernels (HBM-bound, one pass)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float tf32_round(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// hi = x rounded to TF32 (10-bit mantissa), lo = x - hi (exact in FP32).
+// One thread per group of 4 output columns; ld_out is a multiple of 4 so the stores are
+// 16-byte vectors. Columns in [cols, ld_out) are written as zeros.
+__global__ void split_tf32_kernel(const float* __restrict__ src, long long rows, long long cols,
+                                  long long ld, const float* __restrict__ mask,
+                                  float* __restrict__ hi, float* __restrict__ lo, long long ld_out) {
+    const long long groups = ld_out >> 2;
+    const long long total = rows * groups;
+    const bool vec_in = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) &&
+                        (mask == nullptr || (reinterpret_cast<uintptr_t>(mask) & 15u) == 0);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / groups;
+        const long long c = (i - r * groups) << 2;
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* p = src + r * ld + c;
+        if (vec_in && c + 4 <= cols) {
+            const float4 v = *reinterpret_cast<const float4*>(p);
+            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+            if (mask != nullptr) {
+                const float4 m = *reinterpret_cast<const float4*>(mask + r * ld + c);
+                x[0] = m.x > 0.f ? x[0] : 0.f;
+                x[1] = m.y > 0.f ? x[1] : 0.f;
+                x[2] = m.z > 0.f ? x[2] : 0.f;
+                x[3] = m.w > 0.f ? x[3] : 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (c + j < cols) {
+                    float v = p[j];
+                    if (mask != nullptr) v = mask[r * ld + c + j] > 0.f ? v : 0.f;
+                    x[j] = v;
+                }
+            }
+        }
+        float h[4], l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            h[j] = tf32_round(x[j]);
+            l[j] = x[j] - h[j];
+        }
+        *reinterpret_cast<float4*>(hi + r * ld_out + c) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(lo + r * ld_out + c) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+// Copies a 16-bit matrix into a buffer whose leading dimension is a multiple of 8.
+__global__ void pack16_kernel(const uint16_t* __restrict__ src, long long rows, long long cols,
+                              long long ld, uint16_t* __restrict__ dst, long long ld_out) {
+    const long long total = rows * ld_out;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / ld_out;
+        const long long c = i - r * ld_out;
+        dst[i] = c < cols ? src[r * ld + c] : (uint16_t)0;
+    }
+}
+
+// C = epilogue(0) for a contraction of length zero.
+__global__ void empty_k_kernel(const GemmArgs a) {
+    const long long total = (long long)a.M * a.N;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / a.N, c = i - r * a.N;
+        float v = 0.f;
+        if (a.bias_mode == kBiasPerCol) v = a.bias[c];
+        if (a.bias_mode == kBiasPerRow) v = a.bias[r];
+        if (a.relu) v = v > 0.f ? v : 0.f;
+        if (a.out_type == kOutF32) static_cast<float*>(a.C)[r * a.ldc + c] = v;
+        else if (a.out_type == kOutBF16)
+            static_cast<__nv_bfloat16*>(a.C)[r * a.ldc + c] = __float2bfloat16_rn(v);
+        else static_cast<__half*>(a.C)[r * a.ldc + c] = __float2half_rn(v);
+    }
+}
+
+int grid_for(long long work_items, int block, int sm_count) {
+    long long g = (work_items + block - 1) / block;
+    const long long cap = (long long)sm_count * 16;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return (int)g;
+}
+
+// ---------------------------------------------------------------------------
+// Launch
+// ---------------------------------------------------------------------------
+template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN>
+int launch_variant(const CUtensorMap maps[4], const GemmArgs& args, int grid, cudaStream_t stream) {
+    using S = GemmSmem<KIND, BN, STAGES>;
+    auto kern = gemm_tcgen05_kernel<KIND, BN, STAGES, A_MN, B_MN>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    TFB_CUDA_OK(cudaGetDevice(&dev));
+    if (!attr_set[dev]) {
+        TFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+        attr_set[dev] = true;
+    }
+    kern<<<grid, gemm_threads(KIND), S::TOTAL, stream>>>(maps[0], maps[1], maps[2], maps[3], args);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+template <int KIND, int BN, int STAGES>
+int launch_layout(bool a_mn, bool b_mn, const CUtensorMap maps[4], const GemmArgs& args, int grid,
+                  cudaStream_t stream) {
+    if (!a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, false, false>(maps, args, grid, stream);
+    if (!a_mn && b_mn) return launch_variant<KIND, BN, STAGES, false, true>(maps, args, grid, stream);
+    if (a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, true, false>(maps, args, grid, stream);
+    return launch_variant<KIND, BN, STAGES, true, true>(maps, args, grid, stream);
+}
+
+int choose_bn(int64_t M, int64_t N, int sm_count) {
+    const int cands[3] = {256, 128, 64};
+    long long best_cost = -1;
+    int best = 256;
+    const long long tiles_m = (M + kBlockM - 1) / kBlockM;
+    for (int bn : cands) {
+        const long long tiles = tiles_m * ((N + bn - 1) / bn);
+        const long long waves = (tiles + sm_count - 1) / sm_count;
+        // Clocks per 32-byte K step: tensor pipe (BN/2) or shared-memory reads ((128+BN)/4).
+        const long long step = bn / 2 > (128 + bn) / 4 ? bn / 2 : (128 + bn) / 4;
+        const long long cost = waves * step;
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
+                  float* hi, float* lo, int64_t ld_out, cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    if (rows <= 0 || cols <= 0) return TFB_OK;
+    const long long items = rows * (ld_out >> 2);
+    split_tf32_kernel<<<grid_for(items, 256, st->sm_count), 256, 0, stream>>>(
+        src, rows, cols, ld, mask, hi, lo, ld_out);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+size_t gemm_workspace_bytes(const GemmCall& c) {
+    size_t bytes = 0;
+    const int64_t a_rows = c.a_kmajor ? c.M : c.K, a_cols = c.a_kmajor ? c.K : c.M;
+    const int64_t b_rows = c.b_kmajor ? c.N : c.K, b_cols = c.b_kmajor ? c.K : c.N;
+    if (c.in_dtype == TFB_DTYPE_F32) {
+        if (!c.a_presplit) bytes += (size_t)(2 * a_rows * round_up(a_cols, 4) * 4 + 256);
+        if (!c.b_presplit) bytes += (size_t)(2 * b_rows * round_up(b_cols, 4) * 4 + 256);
+    } else {
+        if (!aligned16(c.A) || (c.lda & 7)) bytes += (size_t)(a_rows * round_up(a_cols, 8) * 2 + 256);
+        if (!aligned16(c.B) || (c.ldb & 7)) bytes += (size_t)(b_rows * round_up(b_cols, 8) * 2 + 256);
+    }
+    return bytes;
+}
+
+int gemm_run(const GemmCall& c, cudaStream_t stream) {
+    if (c.M <= 0 || c.N <= 0) return TFB_OK;
+    if (c.A == nullptr || c.B == nullptr || c.C == nullptr)
+        return fail(TFB_ERR_INVALID_ARG, "gemm: null operand pointer");
+    if (c.in_dtype != TFB_DTYPE_F32 && c.in_dtype != TFB_DTYPE_F16 && c.in_dtype != TFB_DTYPE_BF16)
+        return fail(TFB_ERR_UNSUPPORTED, "gemm: unsupported input dtype %d", c.in_dtype);
+    if (c.out_dtype != TFB_DTYPE_F32 && c.out_dtype != c.in_dtype)
+        return fail(TFB_ERR_UNSUPPORTED, "gemm: output dtype %d must be F32 or the input dtype", c.out_dtype);
+    if (c.M > INT32_MAX || c.N > INT32_MAX || c.K > INT32_MAX)
+        return fail(TFB_ERR_TOO_LARGE, "gemm: extents above 2^31-1 are not supported");
+    const int64_t a_rows = c.a_kmajor ? c.M : c.K, a_cols = c.a_kmajor ? c.K : c.M;
+    const int64_t b_rows = c.b_kmajor ? c.N : c.K, b_cols = c.b_kmajor ? c.K : c.N;
+    if (c.lda < a_cols || c.ldb < b_cols || c.ldc < c.N)
+        return fail(TFB_ERR_INVALID_ARG, "gemm: leading dimension smaller than the row length");
+    if (c.bias_mode != 0 && c.bias == nullptr)
+        return fail(TFB_ERR_INVALID_ARG, "gemm: bias epilogue requested without a bias pointer");
+
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    rc = resolve_encoder();
+    if (rc != TFB_OK) return rc;
+
+    const bool f32 = c.in_dtype == TFB_DTYPE_F32;
+    const int es = f32 ? 4 : 2;
+
+    // ---- operand preparation into scratch -------------------------------------
+    const void* a_ptr[2] = {c.A, nullptr};
+    const void* b_ptr[2] = {c.B, nullptr};
+    int64_t lda = c.lda, ldb = c.ldb;
+    const size_t need = gemm_workspace_bytes(c);
+    uint8_t* ws = nullptr;
+    if (need > 0) {
+        if (c.workspace != nullptr) {
+            if (c.workspace_bytes < need)
+                return fail(TFB_ERR_INVALID_ARG, "gemm: caller scratch of %zu bytes is smaller than the %zu needed",
+                            c.workspace_bytes, need);
+            ws = static_cast<uint8_t*>(c.workspace);
+        } else {
+            void* p = nullptr;
+            rc = workspace_get(stream, need, &p);
+            if (rc != TFB_OK) return rc;
+            ws = static_cast<uint8_t*>(p);
+        }
+    }
+    auto carve = [&](size_t bytes) {
+        uint8_t* p = ws;
+        ws += (bytes + 255) & ~(size_t)255;
+        return p;
+    };
+    if (c.K > 0) {
+        if (f32) {
+            if (c.a_presplit) {
+                a_ptr[1] = static_cast<const float*>(c.A) + c.a_lo_off;
+            } else {
+                const int64_t ldp = round_up(a_cols, 4);
+                float* hi = reinterpret_cast<float*>(carve((size_t)(2 * a_rows * ldp * 4)));
+                float* lo = hi + a_rows * ldp;
+                rc = split_operand(static_cast<const float*>(c.A), a_rows, a_cols, c.lda, c.a_mask, hi,
+                                   lo, ldp, stream);
+                if (rc != TFB_OK) return rc;
+                a_ptr[0] = hi; a_ptr[1] = lo; lda = ldp;
+            }
+            if (c.b_presplit) {
+                b_ptr[1] = static_cast<const float*>(c.B) + c.b_lo_off;
+            } else {
+                const int64_t ldp = round_up(b_cols, 4);
+                float* hi = reinterpret_cast<float*>(carve((size_t)(2 * b_rows * ldp * 4)));
+                float* lo = hi + b_rows * ldp;
+                rc = split_operand(static_cast<const float*>(c.B), b_rows, b_cols, c.ldb, nullptr, hi, lo,
+                                   ldp, stream);
+                if (rc != TFB_OK) return rc;
+                b_ptr[0] = hi; b_ptr[1] = lo; ldb = ldp;
+            }
+        } else {
+            if (c.a_mask != nullptr)
+                return fail(TFB_ERR_UNSUPPORTED, "gemm: operand mask is only available for F32 inputs");
+            if (!aligned16(c.A) || (c.lda & 7)) {
+                const int64_t ldp = round_up(a_cols, 8);
+                uint16_t* d = reinterpret_cast<uint16_t*>(carve((size_t)(a_rows * ldp * 2)));
+                pack16_kernel<<<grid_for(a_rows * ldp, 256, st->sm_count), 256, 0, stream>>>(
+                    static_cast<const uint16_t*>(c.A), a_rows, a_cols, c.lda, d, ldp);
+                TFB_CUDA_OK(cudaGetLastError());
+                a_ptr[0] = d; lda = ldp;
+            }
+            if (!aligned16(c.B) || (c.ldb & 7)) {
+                const int64_t ldp = round_up(b_cols, 8);
+                uint16_t* d = reinterpret_cast<uint16_t*>(carve((size_t)(b_rows * ldp * 2)));
+                pack16_kernel<<<grid_for(b_rows * ldp, 256, st->sm_count), 256, 0, stream>>>(
+                    static_cast<const uint16_t*>(c.B), b_rows, b_cols, c.ldb, d, ldp);
+                TFB_CUDA_OK(cudaGetLastError());
+                b_ptr[0] = d; ldb = ldp;
+            }
+        }
+    }
+
+    // ---- tile shape and tensor maps ---------------------------------------------
+    // TFB_GEMM_BN / TFB_GEMM_CHUNK_KB: debugging overrides of the tile width and of the FP32
+    // accumulation chunk, read on every call.
+    int env_bn = 0, env_chunk = 0;
+    if (const char* e = getenv("TFB_GEMM_BN")) env_bn = atoi(e);
+    if (const char* e = getenv("TFB_GEMM_CHUNK_KB")) env_chunk = atoi(e);
+    const int bn = c.force_bn ? c.force_bn : (env_bn ? env_bn : choose_bn(c.M, c.N, st->sm_count));
+    if (bn != 64 && bn != 128 && bn != 256) return fail(TFB_ERR_INVALID_ARG, "gemm: tile N %d", bn);
+    const int bk = 128 / es;
+    const int t_mn = 128 / es;
+
+    GemmArgs args;
+    memset(&args, 0, sizeof(args));
+    args.M = (int)c.M; args.N = (int)c.N; args.K = (int)c.K;
+    args.tiles_m = (int)((c.M + kBlockM - 1) / kBlockM);
+    args.tiles_n = (int)((c.N + bn - 1) / bn);
+    args.num_tiles = args.tiles_m * args.tiles_n;
+    args.k_blocks = (int)((c.K + bk - 1) / bk);
+    args.group_m = 16;
+    // FP32: close the TMEM accumulator every 256 K elements (see gemm_kernel.cuh).
+    args.chunk_kb = f32 ? (c.chunk_kb > 0 ? c.chunk_kb : (env_chunk > 0 ? env_chunk : 8)) : args.k_blocks;
+    if (args.chunk_kb < 1) args.chunk_kb = 1;
+    args.C = c.C; args.ldc = c.ldc;
+    args.out_type = c.out_dtype == TFB_DTYPE_F32 ? kOutF32 : (c.out_dtype == TFB_DTYPE_F16 ? kOutF16 : kOutBF16);
+    args.bias = c.bias; args.bias_mode = c.bias_mode; args.relu = c.relu ? 1 : 0;
+    args.is_bf16 = c.in_dtype == TFB_DTYPE_BF16 ? 1 : 0;
+    args.status = st->status;
+
+    if (c.K <= 0) {
+        // Empty contraction: the product is zero and only the epilogue remains.
+        const long long total = (long long)c.M * c.N;
+        empty_k_kernel<<<grid_for(total, 256, st->sm_count), 256, 0, stream>>>(args);
+        TFB_CUDA_OK(cudaGetLastError());
+        return TFB_OK;
+    }
+
+    CUtensorMap maps[4];
+    memset(maps, 0, sizeof(maps));
+    const int nplanes = f32 ? 2 : 1;
+    for (int p = 0; p < nplanes; ++p) {
+        if (c.a_kmajor)
+            rc = make_map(&maps[p], c.in_dtype, a_ptr[p], (uint64_t)c.K, (uint64_t)c.M, (uint64_t)lda * es, bk, kBlockM);
+        else
+            rc = make_map(&maps[p], c.in_dtype, a_ptr[p], (uint64_t)c.M, (uint64_t)c.K, (uint64_t)lda * es, t_mn, bk, f32);
+        if (rc != TFB_OK) return rc;
+        if (c.b_kmajor)
+            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.K, (uint64_t)c.N, (uint64_t)ldb * es, bk, bn);
+        else
+            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.N, (uint64_t)c.K, (uint64_t)ldb * es, t_mn, bk, f32);
+        if (rc != TFB_OK) return rc;
+    }
+    if (!f32) { maps[1] = maps[0]; maps[3] = maps[2]; }
+
+    const int grid = args.num_tiles < st->sm_count ? args.num_tiles : st->sm_count;
+    const bool a_mn = !c.a_kmajor, b_mn = !c.b_kmajor;
+    if (f32) {
+        if (bn == 256) return launch_layout<kKindTF32x3, 256, 2>(a_mn, b_mn, maps, args, grid, stream);
+        if (bn == 128) return launch_layout<kKindTF32x3, 128, 3>(a_mn, b_mn, maps, args, grid, stream);
+        return launch_layout<kKindTF32x3, 64, 4>(a_mn, b_mn, maps, args, grid, stream);
+    }
+    if (bn == 256) return launch_layout<kKind16, 256, 4>(a_mn, b_mn, maps, args, grid, stream);
+    if (bn == 128) return launch_layout<kKind16, 128, 6>(a_mn, b_mn, maps, args, grid, stream);
+    return launch_layout<kKind16, 64, 8>(a_mn, b_mn, maps, args, grid, stream);
+}
+
+}  // namespace tfb

@@ -1,0 +1,74 @@
+// Declarations shared by the translation units of libtfb.so (not part of the C-ABI).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/tfb.h"
+
+namespace tfb {
+
+// Records a message retrievable through tfb_last_error_string() and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+#define TFB_CUDA_OK(expr)                                                                  \
+    do {                                                                                   \
+        cudaError_t e_ = (expr);                                                           \
+        if (e_ != cudaSuccess)                                                             \
+            return ::tfb::fail(TFB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,               \
+                               cudaGetErrorString(e_), __FILE__, __LINE__);                \
+    } while (0)
+
+// Per-device state created on first use with that device current.
+struct DeviceState {
+    int device = -1;
+    int sm_count = 0;
+    int* status = nullptr;   // device word: first error code a kernel recorded, 0 = none
+};
+int device_state(DeviceState** out);   // for the current device
+
+// Stream-ordered scratch owned by the library, one grow-only buffer per (device, stream).
+int workspace_get(cudaStream_t stream, size_t bytes, void** out);
+
+// Element size of a TFB_DTYPE_* code, 0 if unknown.
+size_t dtype_size(int dtype);
+
+// ---------------------------------------------------------------------------
+// GEMM (gemm.cu)
+// ---------------------------------------------------------------------------
+struct GemmCall {
+    const void* A = nullptr;   // op(A) is M x K
+    const void* B = nullptr;   // op(B) is K x N
+    void* C = nullptr;         // M x N row-major
+    int64_t M = 0, N = 0, K = 0;
+    int64_t lda = 0, ldb = 0, ldc = 0;   // elements
+    // a_kmajor: A stored [M,K] row-major (contraction contiguous); else stored [K,M].
+    // b_kmajor: B stored [N,K] row-major (contraction contiguous); else stored [K,N].
+    bool a_kmajor = true, b_kmajor = false;
+    int in_dtype = TFB_DTYPE_F32;
+    int out_dtype = TFB_DTYPE_F32;
+    const float* bias = nullptr;
+    int bias_mode = 0;         // 0 none, 1 per output column, 2 per output row
+    bool relu = false;
+    // FP32 only: multiply A elementwise by (a_mask > 0) while splitting it (same shape and
+    // leading dimension as A). Used to fold the ReLU backward mask into the operand.
+    const float* a_mask = nullptr;
+    // FP32 only: operands already split by gemm_split_operand (hi at ptr, lo at ptr + lo_off).
+    bool a_presplit = false, b_presplit = false;
+    int64_t a_lo_off = 0, b_lo_off = 0;   // elements
+    int force_bn = 0;          // 0 = choose; else 64 / 128 / 256
+    int chunk_kb = 0;          // FP32: K blocks (of 32) per TMEM accumulation chunk; 0 = default
+    void* workspace = nullptr; // optional caller scratch; nullptr = library-owned
+    size_t workspace_bytes = 0;
+};
+int gemm_run(const GemmCall& call, cudaStream_t stream);
+// Scratch bytes gemm_run needs for this call (0 for aligned 16-bit inputs).
+size_t gemm_workspace_bytes(const GemmCall& call);
+
+// Splits a row-major FP32 matrix (rows x cols, leading dimension ld) into TF32 hi / lo
+// planes with leading dimension ld_out (multiple of 4, padding zero-filled).
+int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
+                  float* hi, float* lo, int64_t ld_out, cudaStream_t stream);
+
+}  // namespace tfb
