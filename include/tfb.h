@@ -89,11 +89,64 @@ int tfb_gemm_ex(const void* A, const void* B, void* C, int64_t M, int64_t N, int
                 int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b, int in_dtype,
                 int out_dtype, const float* bias, int epilogue_flags, void* stream);
 
+/* FP32 operands can be split once and reused by several products (a weight matrix feeds the
+ * forward product and the input-gradient product of the same step).
+ * tfb_split_tf32: hi = src rounded to TF32, lo = src - hi, both written row-major with leading
+ * dimension ld_out (a multiple of 4, >= cols; padding columns are zero-filled). `src` is
+ * rows x cols with leading dimension ld.
+ * tfb_gemm_presplit: tfb_gemm_ex for FP32 operands given as such hi / lo planes (leading
+ * dimensions multiples of 4, 16-byte aligned bases); C is FP32. No scratch memory is used.
+ * ref: no counterpart; the reference has no tensor-core path (cuda/kernels/gemm.cu:60-254). */
+int tfb_split_tf32(const float* src, int64_t rows, int64_t cols, int64_t ld, float* hi, float* lo,
+                   int64_t ld_out, void* stream);
+int tfb_gemm_presplit(const float* A_hi, const float* A_lo, const float* B_hi, const float* B_lo,
+                      float* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                      int64_t ldc, int trans_a, int trans_b, const float* bias, int epilogue_flags,
+                      void* stream);
+
 /* dA[M,K] = dC[M,N] · Bᵀ and dB[K,N] = Aᵀ · dC for C = A · B (row-major, dense). Either
  * output pointer may be NULL to skip it. ref: MatmulBackward::apply,
  * autograd/ops/MatmulBackward.hpp:26-34. */
 int tfb_matmul_backward(const void* dC, const void* A, const void* B, void* dA, void* dB,
                         int64_t M, int64_t N, int64_t K, int dtype, void* stream);
+
+/* ---- nn::Linear ------------------------------------------------------------------ */
+
+/* Y[batch,out] = X[batch,in] · Wᵀ (+ bias[out]) (then ReLU if relu != 0); W is [out,in] as the
+ * reference stores it. One GEMM with the bias and the activation in its epilogue; bias may be
+ * NULL (the reference registers a bias but never adds it). Y has the dtype of X and W; bias is
+ * FP32. ref: nn::Linear::forward, nn/Linear.cpp:45-64; Tensor::relu, tensor/Tensor.cpp:227-249;
+ * CUDA ReluOp, cuda/kernels/elementwise.cu:112-114. */
+int tfb_linear_forward(const void* X, const void* W, const float* bias, void* Y, int64_t batch,
+                       int64_t in_features, int64_t out_features, int relu, int dtype, void* stream);
+
+/* Backward of the above for the upstream gradient dY[batch,out]:
+ *   dZ = relu ? dY ⊙ (Y > 0) : dY      (Y = the forward output; may be NULL when relu == 0)
+ *   dX[batch,in] = dZ · W,  dW[out,in] = dZᵀ · X,  dbias[out] = column sums of dZ (FP32).
+ * Any of dX, dW, dbias may be NULL. No transposed copy of W, X or dZ is made.
+ * ref: ReluBackward, autograd/ops/ReluBackward.hpp:22-32; MatmulBackward,
+ * autograd/ops/MatmulBackward.hpp:26-34; TransposeBackward, autograd/ops/TransposeBackward.hpp:26-28. */
+int tfb_linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+                        float* dbias, int64_t batch, int64_t in_features, int64_t out_features, int relu,
+                        int dtype, void* stream);
+
+/* ---- MLP training step neighbours ------------------------------------------------- */
+
+/* Mean negative log-likelihood of log_softmax(logits) and its gradient:
+ *   loss = -(1/global_rows) · Σ_r log_softmax(logits)[r, labels[r]]      (this call's rows only)
+ *   dlogits = (softmax(logits) - onehot(labels)) / global_rows
+ * global_rows is the batch size of the whole data-parallel step, so per-rank gradients add up to
+ * the full-batch gradient. loss_out (one device float) and dlogits may be NULL. FP32, labels int64.
+ * ref: Tensor::log_softmax, tensor/Tensor.cpp:411-447; LogSoftmaxBackward,
+ * autograd/ops/LogSoftmaxBackward.hpp:26-58; the loss graph of examples/train_mlp.cpp:54-76. */
+int tfb_log_softmax_nll(const float* logits, const int64_t* labels, float* dlogits, float* loss_out,
+                        int64_t rows, int64_t cols, int64_t global_rows, void* stream);
+
+/* v <- momentum·v + grad_scale·g ;  p <- p - lr·v, elementwise over n FP32 values.
+ * ref: the update documented in nn/optim/SGD.hpp:3-6 (the shipped SGD::step throws for
+ * parameters with more than one element, nn/optim/SGD.cpp:38-57). */
+int tfb_sgd_momentum(float* params, float* velocity, const float* grads, int64_t n, float lr,
+                     float momentum, float grad_scale, void* stream);
 
 #ifdef __cplusplus
 }

@@ -81,6 +81,30 @@ int ref_matmul(const float* A, const float* B, float* C, int64_t M, int64_t N, i
     });
 }
 
+// A matrix kept as a reference Tensor across calls (the reference never frees storage, so the
+// handle lives until the process exits). Used to time row panels of one large product without
+// re-copying B for every panel.
+void* ref_hold_matrix(const float* src, int64_t rows, int64_t cols) {
+    try {
+        tensorforge::init_tensor_autograd();
+        return new Tensor(from_host(src, Shape{rows, cols}));
+    } catch (const std::exception& e) {
+        g_what = e.what();
+        return nullptr;
+    }
+}
+
+// C[M,N] = A[M,K] · held B[K,N] through Tensor::matmul. Safe to call from several threads at
+// once on different A panels: the call only reads B and allocates its own tensors.
+int ref_matmul_held(const float* A, void* held_b, float* C, int64_t M) {
+    return guarded([&] {
+        const Tensor& b = *static_cast<const Tensor*>(held_b);
+        Tensor a = from_host(A, Shape{M, b.shape()[0]});
+        Tensor c = a.matmul(b);
+        to_host(c, C);
+    });
+}
+
 // C = A·B followed by backward with upstream gradient G (MatmulBackward,
 // autograd/ops/MatmulBackward.hpp:26-34).
 int ref_matmul_backward(const float* A, const float* B, const float* G, float* dA, float* dB,

@@ -35,7 +35,14 @@ PROTOTYPES = {
     "tfb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_gemm_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
                            _vp, _i32, _vp]),
+    "tfb_split_tf32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
+    "tfb_gemm_presplit": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp,
+                                 _i32, _vp]),
     "tfb_matmul_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_linear_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tfb_linear_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tfb_log_softmax_nll": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "tfb_sgd_momentum": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
 }
 
 for _name, (_res, _args) in PROTOTYPES.items():

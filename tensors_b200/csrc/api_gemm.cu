@@ -1,4 +1,6 @@
 // extern "C" entry points of the GEMM family.
+#include <initializer_list>
+
 #include "internal.hpp"
 
 using namespace tfb;
@@ -40,6 +42,47 @@ int tfb_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_
     // Mirrors the reference launchers: nothing happens for empty problems or unknown dtypes.
     if (M <= 0 || N <= 0 || K <= 0 || !known_dtype(dtype)) return TFB_OK;
     return tfb_matmul(A, B, C, M, N, K, dtype, dtype, stream);
+}
+
+int tfb_split_tf32(const float* src, int64_t rows, int64_t cols, int64_t ld, float* hi, float* lo,
+                   int64_t ld_out, void* stream) {
+    if (rows < 0 || cols < 0) return fail(TFB_ERR_INVALID_ARG, "split_tf32: negative extent");
+    if (src == nullptr || hi == nullptr || lo == nullptr)
+        return fail(TFB_ERR_INVALID_ARG, "split_tf32: null pointer");
+    if (ld < cols || ld_out < cols || (ld_out & 3))
+        return fail(TFB_ERR_INVALID_ARG, "split_tf32: ld_out must be a multiple of 4 and >= cols");
+    if ((reinterpret_cast<uintptr_t>(hi) & 15u) || (reinterpret_cast<uintptr_t>(lo) & 15u))
+        return fail(TFB_ERR_UNSUPPORTED, "split_tf32: output planes must be 16-byte aligned");
+    return split_operand(src, rows, cols, ld, nullptr, hi, lo, ld_out, static_cast<cudaStream_t>(stream));
+}
+
+int tfb_gemm_presplit(const float* A_hi, const float* A_lo, const float* B_hi, const float* B_lo,
+                      float* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                      int64_t ldc, int trans_a, int trans_b, const float* bias, int epilogue_flags,
+                      void* stream) {
+    if (M < 0 || N < 0 || K < 0) return fail(TFB_ERR_INVALID_ARG, "gemm_presplit: negative extent");
+    if (A_hi == nullptr || A_lo == nullptr || B_hi == nullptr || B_lo == nullptr)
+        return fail(TFB_ERR_INVALID_ARG, "gemm_presplit: null operand plane");
+    if ((lda & 3) || (ldb & 3))
+        return fail(TFB_ERR_UNSUPPORTED, "gemm_presplit: leading dimensions must be multiples of 4");
+    for (const float* p : {A_hi, A_lo, B_hi, B_lo})
+        if (reinterpret_cast<uintptr_t>(p) & 15u)
+            return fail(TFB_ERR_UNSUPPORTED, "gemm_presplit: planes must be 16-byte aligned");
+    if ((epilogue_flags & TFB_EPI_BIAS_COL) && (epilogue_flags & TFB_EPI_BIAS_ROW))
+        return fail(TFB_ERR_INVALID_ARG, "gemm_presplit: both bias modes requested");
+    GemmCall c;
+    c.A = A_hi; c.B = B_hi; c.C = C;
+    c.M = M; c.N = N; c.K = K;
+    c.lda = lda; c.ldb = ldb; c.ldc = ldc;
+    c.a_kmajor = (trans_a == 0);
+    c.b_kmajor = (trans_b != 0);
+    c.in_dtype = TFB_DTYPE_F32; c.out_dtype = TFB_DTYPE_F32;
+    c.a_presplit = true; c.b_presplit = true;
+    c.a_lo_off = A_lo - A_hi; c.b_lo_off = B_lo - B_hi;
+    c.bias = bias;
+    c.bias_mode = (epilogue_flags & TFB_EPI_BIAS_COL) ? 1 : ((epilogue_flags & TFB_EPI_BIAS_ROW) ? 2 : 0);
+    c.relu = (epilogue_flags & TFB_EPI_RELU) != 0;
+    return gemm_run(c, static_cast<cudaStream_t>(stream));
 }
 
 int tfb_matmul_backward(const void* dC, const void* A, const void* B, void* dA, void* dB, int64_t M,

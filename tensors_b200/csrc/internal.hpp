@@ -71,4 +71,13 @@ size_t gemm_workspace_bytes(const GemmCall& call);
 int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
                   float* hi, float* lo, int64_t ld_out, cudaStream_t stream);
 
+// ---------------------------------------------------------------------------
+// nn::Linear (linear.cu)
+// ---------------------------------------------------------------------------
+int linear_forward(const void* X, const void* W, const float* bias, void* Y, int64_t batch, int64_t in_f,
+                   int64_t out_f, bool relu, int dtype, cudaStream_t stream);
+int linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+                    float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
+                    cudaStream_t stream);
+
 }  // namespace tfb

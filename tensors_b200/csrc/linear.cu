@@ -1,0 +1,235 @@
+// nn::Linear forward and backward on the tcgen05 GEMM.
+//
+// forward : Y = relu?(X · Wᵀ + b)            one GEMM, bias and ReLU in its epilogue
+// backward: dZ = dY ⊙ (Y > 0)                 folded into the operand-split pass of dZ,
+//           db = column sums of dZ            which also emits the partial column sums
+//           dX = dZ · W                       W consumed as an MN-major operand
+//           dW = dZᵀ · X                      dZ and X consumed as MN-major operands
+// No transpose copy is made anywhere: the split planes of dZ feed both backward GEMMs.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "internal.hpp"
+
+namespace tfb {
+
+namespace {
+
+constexpr int kColsumRowsPerBlock = 128;
+
+__device__ __forceinline__ float tf32_rna(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// One block covers kColsumRowsPerBlock rows x (4 * blockDim.x) columns. Each thread owns four
+// adjacent columns, walks the block's rows in ascending order, writes the masked value's hi / lo
+// planes and keeps the running column sums, which land in partial[blockIdx.y][col].
+__global__ void split_mask_colsum_kernel(const float* __restrict__ dY, const float* __restrict__ Y,
+                                         long long rows, long long cols, long long ld,
+                                         float* __restrict__ hi, float* __restrict__ lo, long long ld_out,
+                                         float* __restrict__ partial) {
+    const long long c = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= ld_out) return;
+    const long long r0 = (long long)blockIdx.y * kColsumRowsPerBlock;
+    const long long r1 = min(r0 + (long long)kColsumRowsPerBlock, rows);
+    const bool vec = ((ld & 3) == 0) && (c + 4 <= cols) && ((reinterpret_cast<uintptr_t>(dY) & 15u) == 0) &&
+                     (Y == nullptr || (reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    for (long long r = r0; r < r1; ++r) {
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (vec) {
+            const float4 g = *reinterpret_cast<const float4*>(dY + r * ld + c);
+            x[0] = g.x; x[1] = g.y; x[2] = g.z; x[3] = g.w;
+            if (Y != nullptr) {
+                const float4 y = *reinterpret_cast<const float4*>(Y + r * ld + c);
+                x[0] = y.x > 0.f ? x[0] : 0.f;
+                x[1] = y.y > 0.f ? x[1] : 0.f;
+                x[2] = y.z > 0.f ? x[2] : 0.f;
+                x[3] = y.w > 0.f ? x[3] : 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (c + j < cols) {
+                    float v = dY[r * ld + c + j];
+                    if (Y != nullptr) v = Y[r * ld + c + j] > 0.f ? v : 0.f;
+                    x[j] = v;
+                }
+            }
+        }
+        float h[4], l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            h[j] = tf32_rna(x[j]);
+            l[j] = x[j] - h[j];
+            s[j] += x[j];
+        }
+        *reinterpret_cast<float4*>(hi + r * ld_out + c) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(lo + r * ld_out + c) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+    if (partial != nullptr)
+        *reinterpret_cast<float4*>(partial + (long long)blockIdx.y * ld_out + c) = make_float4(s[0], s[1], s[2], s[3]);
+}
+
+// 16-bit variant: writes the masked gradient in the input type and the partial column sums.
+template <typename T>
+__global__ void mask_colsum16_kernel(const T* __restrict__ dY, const T* __restrict__ Y, long long rows,
+                                     long long cols, long long ld, T* __restrict__ dZ, long long ld_out,
+                                     float* __restrict__ partial) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= ld_out) return;
+    const long long r0 = (long long)blockIdx.y * kColsumRowsPerBlock;
+    const long long r1 = min(r0 + (long long)kColsumRowsPerBlock, rows);
+    float s = 0.f;
+    for (long long r = r0; r < r1; ++r) {
+        float v = 0.f;
+        if (c < cols) {
+            v = static_cast<float>(dY[r * ld + c]);
+            if (Y != nullptr) v = static_cast<float>(Y[r * ld + c]) > 0.f ? v : 0.f;
+        }
+        dZ[r * ld_out + c] = static_cast<T>(v);
+        s += v;
+    }
+    if (partial != nullptr) partial[(long long)blockIdx.y * ld_out + c] = s;
+}
+
+// db[c] = sum over row blocks (ascending) of partial[b][c].
+__global__ void colsum_finish_kernel(const float* __restrict__ partial, long long blocks, long long cols,
+                                     long long ld, float* __restrict__ out) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (long long b = 0; b < blocks; ++b) s += partial[b * ld + c];
+    out[c] = s;
+}
+
+inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+}  // namespace
+
+int linear_forward(const void* X, const void* W, const float* bias, void* Y, int64_t batch, int64_t in_f,
+                   int64_t out_f, bool relu, int dtype, cudaStream_t stream) {
+    GemmCall c;
+    c.A = X; c.B = W; c.C = Y;
+    c.M = batch; c.N = out_f; c.K = in_f;
+    c.lda = in_f; c.ldb = in_f; c.ldc = out_f;
+    c.a_kmajor = true; c.b_kmajor = true;
+    c.in_dtype = dtype; c.out_dtype = dtype;
+    c.bias = bias; c.bias_mode = bias != nullptr ? 1 : 0;
+    c.relu = relu;
+    return gemm_run(c, stream);
+}
+
+int linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+                    float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
+                    cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    if (batch <= 0 || in_f <= 0 || out_f <= 0) return TFB_OK;
+    const bool f32 = dtype == TFB_DTYPE_F32;
+    const int64_t ldz = round_up(out_f, f32 ? 4 : 8);
+    const int64_t row_blocks = (batch + kColsumRowsPerBlock - 1) / kColsumRowsPerBlock;
+
+    // The two products, described first so that their scratch needs are known.
+    GemmCall gx, gw;
+    gx.M = batch; gx.N = in_f; gx.K = out_f;        // dX = dZ[batch,out] · W[out,in]
+    gx.B = W; gx.ldb = in_f; gx.b_kmajor = false;
+    gx.C = dX; gx.ldc = in_f;
+    gx.a_kmajor = true; gx.lda = ldz;
+    gw.M = out_f; gw.N = in_f; gw.K = batch;        // dW = dZᵀ · X, both stored with the contraction outermost
+    gw.B = X; gw.ldb = in_f; gw.b_kmajor = false;
+    gw.C = dW; gw.ldc = in_f;
+    gw.a_kmajor = false; gw.lda = ldz;
+    gx.in_dtype = gw.in_dtype = dtype;
+    gx.out_dtype = gw.out_dtype = dtype;
+    gx.a_presplit = gw.a_presplit = f32;
+    gx.a_lo_off = gw.a_lo_off = batch * ldz;
+    // Placeholders so that the scratch computation sees aligned A operands.
+    gx.A = gw.A = reinterpret_cast<const void*>(static_cast<uintptr_t>(256));
+
+    const size_t dz_bytes = align256((size_t)(batch * ldz) * (f32 ? 8 : 2));
+    const size_t partial_bytes = db != nullptr ? align256((size_t)(row_blocks * ldz) * 4) : 0;
+    const size_t gx_bytes = dX != nullptr ? gemm_workspace_bytes(gx) : 0;
+    const size_t gw_bytes = dW != nullptr ? gemm_workspace_bytes(gw) : 0;
+    const size_t gemm_bytes = align256(gx_bytes > gw_bytes ? gx_bytes : gw_bytes);
+    void* ws_v = nullptr;
+    rc = workspace_get(stream, dz_bytes + partial_bytes + gemm_bytes + 256, &ws_v);
+    if (rc != TFB_OK) return rc;
+    uint8_t* ws = static_cast<uint8_t*>(ws_v);
+    void* dz = ws;
+    float* partial = db != nullptr ? reinterpret_cast<float*>(ws + dz_bytes) : nullptr;
+    void* gemm_ws = ws + dz_bytes + partial_bytes;
+
+    const void* mask = relu ? Y : nullptr;
+    if (relu && Y == nullptr) return fail(TFB_ERR_INVALID_ARG, "linear_backward: ReLU needs the forward output");
+    if (f32) {
+        float* hi = static_cast<float*>(dz);
+        float* lo = hi + batch * ldz;
+        dim3 block(128), grid((unsigned)((ldz / 4 + 127) / 128), (unsigned)row_blocks);
+        split_mask_colsum_kernel<<<grid, block, 0, stream>>>(static_cast<const float*>(dY),
+                                                             static_cast<const float*>(mask), batch, out_f,
+                                                             out_f, hi, lo, ldz, partial);
+    } else {
+        dim3 block(128), grid((unsigned)((ldz + 127) / 128), (unsigned)row_blocks);
+        if (dtype == TFB_DTYPE_BF16)
+            mask_colsum16_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(
+                static_cast<const __nv_bfloat16*>(dY), static_cast<const __nv_bfloat16*>(mask), batch, out_f,
+                out_f, static_cast<__nv_bfloat16*>(dz), ldz, partial);
+        else
+            mask_colsum16_kernel<__half><<<grid, block, 0, stream>>>(
+                static_cast<const __half*>(dY), static_cast<const __half*>(mask), batch, out_f, out_f,
+                static_cast<__half*>(dz), ldz, partial);
+    }
+    TFB_CUDA_OK(cudaGetLastError());
+    if (db != nullptr) {
+        colsum_finish_kernel<<<(unsigned)((out_f + 127) / 128), 128, 0, stream>>>(partial, row_blocks, out_f, ldz, db);
+        TFB_CUDA_OK(cudaGetLastError());
+    }
+    gx.A = gw.A = dz;
+    gx.workspace = gw.workspace = gemm_ws;
+    gx.workspace_bytes = gw.workspace_bytes = gemm_bytes;
+    if (dX != nullptr) {
+        rc = gemm_run(gx, stream);
+        if (rc != TFB_OK) return rc;
+    }
+    if (dW != nullptr) {
+        rc = gemm_run(gw, stream);
+        if (rc != TFB_OK) return rc;
+    }
+    return TFB_OK;
+}
+
+}  // namespace tfb
+
+extern "C" {
+
+int tfb_linear_forward(const void* X, const void* W, const float* bias, void* Y, int64_t batch,
+                       int64_t in_features, int64_t out_features, int relu, int dtype, void* stream) {
+    using namespace tfb;
+    if (batch < 0 || in_features < 0 || out_features < 0)
+        return fail(TFB_ERR_INVALID_ARG, "linear_forward: negative extent");
+    if (dtype_size(dtype) == 0) return fail(TFB_ERR_UNSUPPORTED, "linear_forward: unknown dtype %d", dtype);
+    if (X == nullptr || W == nullptr || Y == nullptr) return fail(TFB_ERR_INVALID_ARG, "linear_forward: null pointer");
+    return linear_forward(X, W, bias, Y, batch, in_features, out_features, relu != 0, dtype,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int tfb_linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+                        float* dbias, int64_t batch, int64_t in_features, int64_t out_features, int relu,
+                        int dtype, void* stream) {
+    using namespace tfb;
+    if (batch < 0 || in_features < 0 || out_features < 0)
+        return fail(TFB_ERR_INVALID_ARG, "linear_backward: negative extent");
+    if (dtype_size(dtype) == 0) return fail(TFB_ERR_UNSUPPORTED, "linear_backward: unknown dtype %d", dtype);
+    if (dY == nullptr) return fail(TFB_ERR_INVALID_ARG, "linear_backward: null upstream gradient");
+    if (dX != nullptr && W == nullptr) return fail(TFB_ERR_INVALID_ARG, "linear_backward: dX needs W");
+    if (dW != nullptr && X == nullptr) return fail(TFB_ERR_INVALID_ARG, "linear_backward: dW needs X");
+    return linear_backward(X, W, Y, dY, dX, dW, dbias, batch, in_features, out_features, relu != 0, dtype,
+                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,110 @@
+"""Data-parallel MLP training step on libtfb (host side).
+
+Mirrors the dataflow of the reference's training example (examples/train_mlp.cpp:161-183):
+Linear -> ReLU -> Linear -> ReLU -> Linear -> log_softmax + mean NLL -> backward -> SGD, with the
+documented momentum update (nn/optim/SGD.hpp:3-6). Every tensor operation is a libtfb call; torch
+only supplies device memory, streams and — for more than one rank — the NCCL all-reduce of the flat
+gradient buffer (one per step, a pure sum because each rank already divides by the global batch).
+"""
+import ctypes
+
+import torch
+
+from . import capi
+
+lib = capi.lib
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class MLP:
+    """dims = (d0, d1, ..., dL): L Linear layers, ReLU after all but the last."""
+
+    def __init__(self, dims, weights, biases=None, device="cuda", process_group=None):
+        self.dims = tuple(int(d) for d in dims)
+        self.L = len(self.dims) - 1
+        sizes = []
+        for i in range(self.L):
+            sizes += [self.dims[i + 1] * self.dims[i], self.dims[i + 1]]
+        # 16-byte aligned segment starts keep every parameter usable as a TMA operand
+        self.offsets = []
+        off = 0
+        for sz in sizes:
+            self.offsets.append(off)
+            off += (sz + 3) // 4 * 4
+        self.numel = off
+        self.params = torch.zeros(off, device=device, dtype=torch.float32)
+        self.grads = torch.zeros(off, device=device, dtype=torch.float32)
+        self.velocity = torch.zeros(off, device=device, dtype=torch.float32)
+        self.group = process_group
+        for i in range(self.L):
+            self.weight(i).copy_(torch.as_tensor(weights[i], dtype=torch.float32).reshape(self.dims[i + 1], self.dims[i]))
+            if biases is not None and biases[i] is not None:
+                self.bias(i).copy_(torch.as_tensor(biases[i], dtype=torch.float32))
+        self.loss = torch.zeros(1, device=device, dtype=torch.float32)
+        self._acts = None
+
+    def _seg(self, buf, k, shape):
+        n = 1
+        for s in shape:
+            n *= s
+        return buf[self.offsets[k]:self.offsets[k] + n].view(*shape)
+
+    def weight(self, i, buf=None):
+        return self._seg(self.params if buf is None else buf, 2 * i, (self.dims[i + 1], self.dims[i]))
+
+    def bias(self, i, buf=None):
+        return self._seg(self.params if buf is None else buf, 2 * i + 1, (self.dims[i + 1],))
+
+    def forward(self, X):
+        batch = X.shape[0]
+        acts = [X]
+        for i in range(self.L):
+            Y = torch.empty((batch, self.dims[i + 1]), device=X.device, dtype=torch.float32)
+            capi.check(lib.tfb_linear_forward(_p(acts[-1]), _p(self.weight(i)), _p(self.bias(i)), _p(Y), batch,
+                                              self.dims[i], self.dims[i + 1], int(i < self.L - 1),
+                                              capi.DTYPE_F32, _stream()))
+            acts.append(Y)
+        self._acts = acts
+        return acts[-1]
+
+    def forward_backward(self, X, labels, global_rows=None):
+        """Fills self.grads (this rank's share of the full-batch gradient) and self.loss."""
+        batch = X.shape[0]
+        global_rows = int(global_rows or batch)
+        logits = self.forward(X)
+        acts = self._acts
+        dz = torch.empty_like(logits)
+        capi.check(lib.tfb_log_softmax_nll(_p(logits), _p(labels), _p(dz), _p(self.loss), batch, self.dims[-1],
+                                           global_rows, _stream()))
+        upstream = dz
+        for i in reversed(range(self.L)):
+            relu = i < self.L - 1
+            dX = torch.empty_like(acts[i]) if i > 0 else None
+            capi.check(lib.tfb_linear_backward(_p(acts[i]), _p(self.weight(i)), _p(acts[i + 1]), _p(upstream), _p(dX),
+                                               _p(self.weight(i, self.grads)), _p(self.bias(i, self.grads)), batch,
+                                               self.dims[i], self.dims[i + 1], int(relu), capi.DTYPE_F32, _stream()))
+            upstream = dX
+        return self.loss
+
+    def allreduce_grads(self):
+        if self.group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
+                                      and torch.distributed.get_world_size() > 1):
+            torch.distributed.all_reduce(self.grads, group=self.group)
+            torch.distributed.all_reduce(self.loss, group=self.group)
+
+    def sgd_step(self, lr, momentum):
+        capi.check(lib.tfb_sgd_momentum(_p(self.params), _p(self.velocity), _p(self.grads), self.numel,
+                                        float(lr), float(momentum), 1.0, _stream()))
+
+    def train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None):
+        self.forward_backward(X, labels, global_rows)
+        self.allreduce_grads()
+        self.sgd_step(lr, momentum)
+        return self.loss

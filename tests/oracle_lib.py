@@ -223,6 +223,21 @@ class Reference:
         self._ok(self.lib.ref_matmul(fp(A), fp(B), fp(C), _i64(M), _i64(N), _i64(K)))
         return C
 
+    def hold_matrix(self, B):
+        B = f32(B)
+        self.lib.ref_hold_matrix.restype = ctypes.c_void_p
+        h = self.lib.ref_hold_matrix(fp(B), _i64(B.shape[0]), _i64(B.shape[1]))
+        if not h:
+            raise RuntimeError("reference threw: " + self.lib.ref_last_error().decode())
+        return (ctypes.c_void_p(h), B.shape)
+
+    def matmul_held(self, A, held):
+        A = f32(A)
+        handle, (K, N) = held
+        C = np.empty((A.shape[0], N), np.float32)
+        self._ok(self.lib.ref_matmul_held(fp(A), handle, fp(C), _i64(A.shape[0])))
+        return C
+
     def matmul_backward(self, A, B, G):
         A, B, G = f32(A), f32(B), f32(G)
         M, K = A.shape

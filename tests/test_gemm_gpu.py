@@ -1,0 +1,194 @@
+"""Parity of the tcgen05 GEMM (through the C-ABI) with the oracle: bit patterns of the reference's
+own kernel tests, seeded cases in every operand layout, the BF16 path, fused epilogues, and the
+full-size configurations through sampled rows/columns plus size-independent properties."""
+import numpy as np
+import pytest
+import torch
+
+import refdata
+import tensors_b200.capi as capi
+from gpu_util import assert_device_ok, dev, gemm_ex, lib, ptr, rel_err, stream_ptr
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5   # normwise, against the reference FP32 matmul
+BF16_TOL = 1e-2
+
+
+def tfb_matmul(a, b, in_dtype=capi.DTYPE_F32, out_dtype=capi.DTYPE_F32):
+    M, K = a.shape
+    N = b.shape[1]
+    td = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}
+    A, B = dev(a, td[in_dtype]), dev(b, td[in_dtype])
+    C = torch.full((M, N), float("nan"), device="cuda", dtype=td[out_dtype])
+    capi.check(lib.tfb_matmul(ptr(A), ptr(B), ptr(C), M, N, K, in_dtype, out_dtype, stream_ptr()))
+    assert_device_ok()
+    return C.float().cpu().numpy()
+
+
+def test_reference_kernel_test_patterns(oracle, golden):
+    # The cases of cuda/kernels/gemm_{naive,tiled_16x16,optimized}_test.cpp, against the golden
+    # outputs of the reference's Tensor::matmul, with the tolerances those tests use or tighter.
+    for name, a, b in refdata.gemm_test_patterns():
+        got = tfb_matmul(a, b)
+        want = golden[f"gemm_{name}"]
+        assert not np.isnan(got).any(), name
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6, err_msg=name)
+    got = tfb_matmul(np.array([[1, 2], [3, 4]], np.float32), np.array([[5, 6], [7, 8]], np.float32))
+    assert got.tolist() == [[19.0, 22.0], [43.0, 50.0]]
+
+
+def test_launcher_semantics_same_dtype_and_noop():
+    # launch_gemm_* keep the input dtype for C and silently ignore empty problems and unknown dtypes
+    # (cuda/kernels/gemm.cu:81,298).
+    for dt, tdt, eps in ((capi.DTYPE_F16, torch.float16, 0.05), (capi.DTYPE_BF16, torch.bfloat16, 0.1)):
+        A = dev(np.array([[1, 2], [3, 4]], np.float32), tdt)
+        B = dev(np.array([[5, 6], [7, 8]], np.float32), tdt)
+        C = torch.zeros((2, 2), device="cuda", dtype=tdt)
+        capi.check(lib.tfb_gemm(ptr(A), ptr(B), ptr(C), 2, 2, 2, dt, stream_ptr()))
+        assert_device_ok()
+        np.testing.assert_allclose(C.float().cpu().numpy(), [[19, 22], [43, 50]], rtol=eps)
+    C = torch.full((2, 2), 7.0, device="cuda")
+    assert lib.tfb_gemm(ptr(C), ptr(C), ptr(C), 0, 2, 2, capi.DTYPE_F32, stream_ptr()) == 0
+    assert lib.tfb_gemm(ptr(C), ptr(C), ptr(C), 2, 2, 2, 5, stream_ptr()) == 0
+    assert_device_ok()
+    assert torch.all(C == 7.0)
+
+
+def test_bad_arguments_report_errors():
+    C = torch.zeros((2, 2), device="cuda")
+    assert lib.tfb_matmul(None, ptr(C), ptr(C), 2, 2, 2, 0, 0, stream_ptr()) == -1
+    assert "null" in capi.last_error()
+    assert lib.tfb_matmul(ptr(C), ptr(C), ptr(C), 2, 2, 2, 4, 0, stream_ptr()) == -2
+    assert lib.tfb_matmul(ptr(C), ptr(C), ptr(C), -1, 2, 2, 0, 0, stream_ptr()) == -1
+    assert lib.tfb_gemm_ex(ptr(C), ptr(C), ptr(C), 2, 2, 2, 1, 2, 2, 0, 0, 0, 0, None, 0, stream_ptr()) == -1
+    assert lib.tfb_gemm_ex(ptr(C), ptr(C), ptr(C), 2, 2, 2, 2, 2, 2, 0, 0, 0, 0, None, 1, stream_ptr()) == -1
+
+
+@pytest.mark.parametrize("trans_a", [False, True])
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("shape", [(128, 128, 128), (300, 200, 100), (17, 23, 19), (2, 2, 2), (64, 256, 784),
+                                   (784, 256, 64), (1000, 10, 1024), (513, 257, 33), (1, 1, 1)])
+def test_fp32_layouts_against_oracle(oracle, shape, trans_a, trans_b):
+    M, N, K = shape
+    a, b = refdata.uniform(100 + M, (M, K)), refdata.uniform(200 + N, (K, N))
+    want = oracle.matmul(a, b)
+    A = dev(np.ascontiguousarray(a.T) if trans_a else a)
+    B = dev(np.ascontiguousarray(b.T) if trans_b else b)
+    C = gemm_ex(A, B, M, N, K, trans_a, trans_b)
+    assert_device_ok()
+    got = C.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert rel_err(got, want) < FP32_TOL
+
+
+@pytest.mark.parametrize("in_dtype", [capi.DTYPE_BF16, capi.DTYPE_F16])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(256, 256, 512), (300, 200, 100), (17, 23, 19), (64, 256, 784)])
+def test_16bit_layouts_against_oracle(oracle, shape, trans_a, trans_b, in_dtype):
+    # Inputs rounded to the 16-bit type on the host, reference loop on the up-converted values.
+    M, N, K = shape
+    tdt = torch.bfloat16 if in_dtype == capi.DTYPE_BF16 else torch.float16
+    a16 = dev(refdata.uniform(300 + M, (M, K)), tdt)
+    b16 = dev(refdata.uniform(400 + N, (K, N)), tdt)
+    want = oracle.matmul(a16.float().cpu().numpy(), b16.float().cpu().numpy())
+    A = a16.t().contiguous() if trans_a else a16
+    B = b16.t().contiguous() if trans_b else b16
+    C = gemm_ex(A, B, M, N, K, trans_a, trans_b, in_dtype=in_dtype)
+    assert_device_ok()
+    got = C.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert rel_err(got, want) < 1e-5          # exact products, FP32 accumulate: far inside 1e-2
+    C16 = gemm_ex(A, B, M, N, K, trans_a, trans_b, in_dtype=in_dtype, out_dtype=in_dtype)
+    assert rel_err(C16.float().cpu().numpy(), want) < BF16_TOL
+
+
+@pytest.mark.parametrize("flags", [capi.EPI_BIAS_COL, capi.EPI_BIAS_ROW, capi.EPI_RELU,
+                                   capi.EPI_BIAS_COL | capi.EPI_RELU, capi.EPI_BIAS_ROW | capi.EPI_RELU])
+def test_fused_epilogues(oracle, flags):
+    M, N, K = 300, 200, 100
+    a, b = refdata.uniform(1, (M, K)), refdata.uniform(2, (K, N))
+    bias = refdata.normal(3, (N if flags & capi.EPI_BIAS_COL else M,))
+    want = oracle.matmul(a, b)
+    if flags & capi.EPI_BIAS_COL:
+        want = want + bias[None, :]
+    if flags & capi.EPI_BIAS_ROW:
+        want = want + bias[:, None]
+    if flags & capi.EPI_RELU:
+        want = np.maximum(want, 0)
+    C = gemm_ex(dev(a), dev(b), M, N, K, bias=dev(bias), flags=flags)
+    assert_device_ok()
+    assert rel_err(C.cpu().numpy(), want) < FP32_TOL
+
+
+def test_strided_operands_and_empty_k(oracle):
+    M, N, K = 70, 50, 40
+    a, b = refdata.uniform(5, (M, K + 8)), refdata.uniform(6, (K, N + 4))
+    want = oracle.matmul(a[:, :K], b[:, :N])
+    C = gemm_ex(dev(a), dev(b), M, N, K, lda=K + 8, ldb=N + 4)
+    assert_device_ok()
+    assert rel_err(C.cpu().numpy(), want) < FP32_TOL
+    # K == 0: the reference loop leaves acc = 0 (tensor/Tensor.cpp:354-362)
+    C = gemm_ex(dev(a), dev(b), M, N, 0, lda=K + 8, ldb=N + 4)
+    assert_device_ok()
+    assert torch.all(C == 0)
+
+
+def test_matmul_backward_against_golden(oracle, golden):
+    a, b, g = refdata.uniform(11, (96, 112)), refdata.uniform(12, (112, 80)), refdata.normal(13, (96, 80))
+    A, B, G = dev(a), dev(b), dev(g)
+    dA, dB = torch.empty_like(A), torch.empty_like(B)
+    capi.check(lib.tfb_matmul_backward(ptr(G), ptr(A), ptr(B), ptr(dA), ptr(dB), 96, 80, 112, capi.DTYPE_F32,
+                                       stream_ptr()))
+    assert_device_ok()
+    assert rel_err(dA.cpu().numpy(), golden["matmul_bwd_dA"]) < FP32_TOL
+    assert rel_err(dB.cpu().numpy(), golden["matmul_bwd_dB"]) < FP32_TOL
+    # the reference's arange known answer (autograd/ops/autograd_all_ops_test.cpp:281-328)
+    a = np.arange(6, dtype=np.float32).reshape(2, 3)
+    b = np.arange(6, dtype=np.float32).reshape(3, 2)
+    A, B, G = dev(a), dev(b), dev(np.ones((2, 2), np.float32))
+    dA, dB = torch.empty_like(A), torch.empty_like(B)
+    capi.check(lib.tfb_matmul_backward(ptr(G), ptr(A), ptr(B), ptr(dA), ptr(dB), 2, 2, 3, 0, stream_ptr()))
+    assert_device_ok()
+    np.testing.assert_allclose(dA.cpu().numpy(), [[1, 5, 9], [1, 5, 9]], rtol=1e-6)
+    np.testing.assert_allclose(dB.cpu().numpy(), [[3, 3], [5, 5], [7, 7]], rtol=1e-6)
+
+
+def test_config1_2048_cubed_full_oracle(oracle):
+    # FP32 GEMM 2048^3, uniform[-1,1) seed 0, via the Tensor::matmul entry point; full oracle.
+    n = 2048
+    a, b = refdata.uniform(0, (n, n)), refdata.uniform(1, (n, n))
+    got = tfb_matmul(a, b)
+    want = oracle.matmul(a, b)
+    assert rel_err(got, want) < FP32_TOL
+    # and both within FP32 rounding noise of the FP64 product on a sample of rows
+    rows = [0, 1, 777, 2047]
+    exact = a[rows].astype(np.float64) @ b.astype(np.float64)
+    assert rel_err(got[rows], exact) < FP32_TOL
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_square_sweep_sampled_rows_and_columns(oracle, n):
+    # Full products at these sizes take the scalar reference loop minutes to hours; the same loop
+    # is applied to 64 full rows and 64 full columns, and linearity is checked on the whole matrix.
+    a, b = refdata.uniform(2, (n, n)), refdata.uniform(3, (n, n))
+    A, B = dev(a), dev(b)
+    C = gemm_ex(A, B, n, n, n)
+    assert_device_ok()
+    rows = np.linspace(0, n - 1, 64).astype(np.int64)
+    cols = np.linspace(0, n - 1, 64).astype(np.int64)
+    assert rel_err(C[torch.from_numpy(rows).cuda()].cpu().numpy(), oracle.matmul_rows(a, b, rows)) < FP32_TOL
+    assert rel_err(C[:, torch.from_numpy(cols).cuda()].cpu().numpy(), oracle.matmul_cols(a, b, cols)) < FP32_TOL
+    # size-independent properties over the full output: C·1 == A·(B·1) and linearity in A
+    ones = torch.ones((n,), device="cuda", dtype=torch.float64)
+    lhs = C.double() @ ones
+    rhs = A.double() @ (B.double() @ ones)
+    assert float((lhs - rhs).norm() / rhs.norm()) < 1e-5
+    C2 = gemm_ex(A * 2.0, B, n, n, n)
+    assert torch.equal(C2, C * 2.0)   # scaling by 2 is exact in every split and product
+    # BF16 inputs (host-rounded), FP32 accumulate and output
+    a16, b16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
+    Cb = gemm_ex(a16, b16, n, n, n, in_dtype=capi.DTYPE_BF16)
+    assert_device_ok()
+    want = oracle.matmul_rows(a16.float().cpu().numpy(), b16.float().cpu().numpy(), rows[:16])
+    assert rel_err(Cb[torch.from_numpy(rows[:16]).cuda()].cpu().numpy(), want) < BF16_TOL

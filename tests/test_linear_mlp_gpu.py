@@ -1,0 +1,140 @@
+"""Parity of nn::Linear forward/backward, the loss kernels, SGD and the MLP step with the oracle and
+with the golden outputs of the unmodified reference."""
+import numpy as np
+import pytest
+import torch
+
+import refdata
+import tensors_b200.capi as capi
+from golden.make_golden import LINEAR_DW_ROWS
+from gpu_util import assert_device_ok, dev, lib, ptr, rel_err, stream_ptr
+
+pytestmark = pytest.mark.gpu
+FP32_TOL = 1e-5
+BF16_TOL = 1e-2
+
+
+def linear_fwd_bwd(x, w, b, g, relu, dtype=capi.DTYPE_F32):
+    tdt = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}[dtype]
+    batch, in_f = x.shape
+    out_f = w.shape[0]
+    X, W, G = dev(x, tdt), dev(w, tdt), dev(g, tdt)
+    B = dev(b) if b is not None else None
+    Y = torch.full((batch, out_f), float("nan"), device="cuda", dtype=tdt)
+    capi.check(lib.tfb_linear_forward(ptr(X), ptr(W), ptr(B), ptr(Y), batch, in_f, out_f, int(relu), dtype, stream_ptr()))
+    dX = torch.full((batch, in_f), float("nan"), device="cuda", dtype=tdt)
+    dW = torch.full((out_f, in_f), float("nan"), device="cuda", dtype=tdt)
+    db = torch.full((out_f,), float("nan"), device="cuda")
+    capi.check(lib.tfb_linear_backward(ptr(X), ptr(W), ptr(Y), ptr(G), ptr(dX), ptr(dW), ptr(db), batch, in_f, out_f,
+                                       int(relu), dtype, stream_ptr()))
+    assert_device_ok()
+    return [t.float().cpu().numpy() for t in (Y, dX, dW, db)]
+
+
+def test_config2_against_reference_golden(oracle, golden):
+    # X 64x784 normalised pixels, W from the reference's Linear(784, 256), bias zeros, ReLU, dY ~ N(0,1)
+    w = refdata.linear_weight(784, 256)
+    x, g = refdata.mnist_like(21, (64, 784)), refdata.normal(22, (64, 256))
+    Y, dX, dW, db = linear_fwd_bwd(x, w, np.zeros(256, np.float32), g, relu=True)
+    assert rel_err(Y, golden["linear_c2_Y"]) < FP32_TOL
+    # the ReLU mask must be the reference's wherever the pre-activation is not within rounding of zero
+    gy = golden["linear_c2_Y"]
+    assert ((Y > 0) != (gy > 0)).sum() <= 2
+    assert rel_err(dX, golden["linear_c2_dX"]) < 5e-5 if ((Y > 0) != (gy > 0)).any() else rel_err(dX, golden["linear_c2_dX"]) < FP32_TOL
+    assert rel_err(dW[LINEAR_DW_ROWS], golden["linear_c2_dW_rows"]) < FP32_TOL
+    assert rel_err(dW.astype(np.float64).sum(axis=1), golden["linear_c2_dW_rowsum"]) < FP32_TOL
+    _, _, odb = oracle.linear_backward(x, w, gy, g, relu=True)
+    assert rel_err(db, odb) < FP32_TOL
+
+
+@pytest.mark.parametrize("relu", [False, True])
+@pytest.mark.parametrize("shape", [(64, 784, 256), (33, 50, 10), (256, 1024, 10), (200, 10, 300), (1, 7, 3)])
+def test_linear_with_bias_against_oracle(oracle, shape, relu):
+    batch, in_f, out_f = shape
+    x, w = refdata.normal(1, (batch, in_f)), refdata.linear_weight(in_f, out_f)
+    b, g = refdata.normal(2, (out_f,)) * np.float32(0.1), refdata.normal(3, (batch, out_f))
+    Y, dX, dW, db = linear_fwd_bwd(x, w, b, g, relu)
+    oy = oracle.linear_forward(x, w, b, relu)
+    assert rel_err(Y, oy) < FP32_TOL
+    # use the device's own mask for the backward oracle so a sign flip at |pre-activation| ~ 1e-7
+    # cannot turn into a spurious mismatch
+    odx, odw, odb = oracle.linear_backward(x, w, Y, g, relu)
+    assert rel_err(dX, odx) < FP32_TOL
+    assert rel_err(dW, odw) < FP32_TOL
+    assert rel_err(db, odb) < FP32_TOL
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_BF16, capi.DTYPE_F16])
+def test_linear_16bit(oracle, dtype):
+    batch, in_f, out_f = 64, 784, 256
+    tdt = torch.bfloat16 if dtype == capi.DTYPE_BF16 else torch.float16
+    rnd = lambda a: torch.from_numpy(a).to(tdt).float().numpy()
+    x, w, g = rnd(refdata.normal(1, (batch, in_f))), rnd(refdata.linear_weight(in_f, out_f)), rnd(refdata.normal(3, (batch, out_f)))
+    b = refdata.normal(2, (out_f,)) * np.float32(0.1)
+    Y, dX, dW, db = linear_fwd_bwd(x, w, b, g, True, dtype)
+    assert rel_err(Y, oracle.linear_forward(x, w, b, True)) < BF16_TOL
+    odx, odw, odb = oracle.linear_backward(x, w, Y, g, True)
+    assert rel_err(dX, odx) < BF16_TOL
+    assert rel_err(dW, odw) < BF16_TOL
+    assert rel_err(db, odb) < BF16_TOL
+
+
+def test_log_softmax_nll_and_sgd(oracle, golden):
+    z = refdata.normal(41, (32, 10)) * np.float32(3.0)
+    lab = refdata.labels(43, 32)
+    Z, L = dev(z), torch.from_numpy(lab).cuda()
+    dz = torch.empty_like(Z)
+    loss = torch.zeros(1, device="cuda")
+    capi.check(lib.tfb_log_softmax_nll(ptr(Z), ptr(L), ptr(dz), ptr(loss), 32, 10, 32, stream_ptr()))
+    assert_device_ok()
+    ol, odz = oracle.nll_mean(z, lab)
+    assert abs(float(loss.item()) - ol) <= 1e-6 * abs(ol)
+    assert rel_err(dz.cpu().numpy(), odz) < 1e-6
+    # the implied log_softmax equals the reference's golden output: dz = (exp(lsm) - onehot) / N
+    lsm = golden["log_softmax_32x10"]
+    onehot = np.eye(10, dtype=np.float32)[lab]
+    assert rel_err(dz.cpu().numpy(), (np.exp(lsm) - onehot) / 32) < 1e-6
+    # data-parallel scaling: half the rows with global_rows = 32 gives the same per-row gradients
+    capi.check(lib.tfb_log_softmax_nll(ptr(Z), ptr(L), ptr(dz), ptr(loss), 16, 10, 32, stream_ptr()))
+    assert rel_err(dz[:16].cpu().numpy(), odz[:16]) < 1e-6
+    # SGD with momentum: same IEEE operations as the host formula, bit for bit
+    p, v, g = refdata.normal(1, (100003,)), refdata.normal(2, (100003,)), refdata.normal(3, (100003,))
+    P, V, G = dev(p), dev(v), dev(g)
+    capi.check(lib.tfb_sgd_momentum(ptr(P), ptr(V), ptr(G), p.size, 0.1, 0.9, 1.0, stream_ptr()))
+    assert_device_ok()
+    op, ov = oracle.sgd_momentum(p, v, g, 0.1, 0.9)
+    assert np.array_equal(V.cpu().numpy(), ov)
+    assert np.array_equal(P.cpu().numpy(), op)
+
+
+def test_mlp_step_against_reference_golden_and_oracle(oracle, golden):
+    from tensors_b200.mlp import MLP
+    dims = (784, 64, 48, 10)
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    xb, lab = refdata.mnist_like(42, (32, 784)), refdata.labels(43, 32)
+    m = MLP(dims, ws)
+    m.forward_backward(dev(xb), torch.from_numpy(lab).cuda())
+    assert_device_ok()
+    assert abs(float(m.loss.item()) - float(golden["mlp_loss"][0])) < 1e-5
+    assert rel_err(m.weight(2, m.grads).cpu().numpy(), golden["mlp_dW3"]) < 2e-5
+    assert rel_err(m.weight(1, m.grads).cpu().numpy(), golden["mlp_dW2"]) < 2e-5
+    assert rel_err(m.weight(0, m.grads).cpu().numpy()[[0, 7, 63]], golden["mlp_dW1_rows"]) < 2e-5
+
+
+def test_mlp_step_config5_shapes_reduced_batch(oracle):
+    # 784 -> 1024 -> 1024 -> 10 at batch 256 (the named configuration uses 8192 rows), then one SGD step
+    from tensors_b200.mlp import MLP
+    dims = (784, 1024, 1024, 10)
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    xb, lab = refdata.mnist_like(7, (256, 784)), refdata.labels(8, 256)
+    m = MLP(dims, ws)
+    p0 = m.params.clone()
+    m.train_step(dev(xb), torch.from_numpy(lab).cuda(), lr=0.1, momentum=0.9)
+    assert_device_ok()
+    ol, odw, odb = oracle.mlp_grads(xb, lab, ws, bs=[np.zeros(d, np.float32) for d in dims[1:]])
+    assert abs(float(m.loss.item()) - ol) < 1e-5
+    for i in range(3):
+        assert rel_err(m.weight(i, m.grads).cpu().numpy(), odw[i]) < 2e-5, i
+        assert rel_err(m.bias(i, m.grads).cpu().numpy(), odb[i]) < 2e-5, i
+    # velocity starts at zero: p1 = p0 - lr * g
+    assert torch.allclose(m.params, p0 - 0.1 * m.grads, rtol=0, atol=1e-7)
