@@ -130,6 +130,43 @@ int tfb_linear_backward(const void* X, const void* W, const void* Y, const void*
                         float* dbias, int64_t batch, int64_t in_features, int64_t out_features, int relu,
                         int dtype, void* stream);
 
+/* ---- nn::Conv2d (implicit GEMM; the im2col / col2im matrices are never materialised) ---- */
+
+/* Output extent of a convolution axis: (in + 2·pad − dilation·(k−1) − 1) / stride + 1.
+ * Host function. ref: cuda/kernels/im2col.cu:109-110, nn/Conv2d.cpp:69-75. */
+int64_t tfb_conv_out_dim(int64_t in, int64_t k, int64_t stride, int64_t pad, int64_t dilation);
+
+/* out[N,Cout,outH,outW] = conv2d(x[N,Cin,H,W], w[Cout,Cin,kH,kW]) (+ bias[Cout]) (then ReLU if
+ * relu != 0), NCHW, FP32. The producers of the GEMM kernel evaluate the im2col index map on the
+ * fly; the bias is added in the epilogue. ref: nn::Conv2d::forward, nn/Conv2d.cpp:77-138
+ * (launch_im2col cuda/kernels/im2col.cu:58-99 + per-sample launch_gemm_tiled_16x16 +
+ * launch_bias_add cuda/kernels/bias_add.cu:49-58). */
+int tfb_conv2d_forward(const void* x, const void* w, const float* bias, void* out, int64_t N, int64_t Cin,
+                       int64_t H, int64_t W, int64_t Cout, int64_t kH, int64_t kW, int64_t stride_h,
+                       int64_t stride_w, int64_t pad_h, int64_t pad_w, int64_t dil_h, int64_t dil_w, int relu,
+                       int dtype, void* stream);
+
+/* grad_input[N,Cin,H,W], grad_weight[Cout,Cin,kH,kW] and grad_bias[Cout] for the upstream gradient
+ * grad_out[N,Cout,outH,outW]; any output may be NULL. grad_input is computed in gather form (no
+ * atomics, fixed summation order); grad_weight is a split-K product over (sample, position) with a
+ * second-stage reduction in fixed order, and the bias gradient comes out of the same product.
+ * Uses library-owned scratch memory. ref: nn::Conv2d::backward, nn/Conv2d.cpp:140-260
+ * (launch_col2im cuda/kernels/col2im.cu:50-80, launch_transpose_2d,
+ * launch_reduce_sum_axis_nchw cuda/kernels/reduce_sum_axis.cu:54-87). */
+int tfb_conv2d_backward(const void* x, const void* w, const void* grad_out, void* grad_input, void* grad_weight,
+                        float* grad_bias, int64_t N, int64_t Cin, int64_t H, int64_t W, int64_t Cout, int64_t kH,
+                        int64_t kW, int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w,
+                        int64_t dil_h, int64_t dil_w, int dtype, void* stream);
+
+/* Writes the im2col index map the forward kernel uses, for samples [n_first, n_first + n_count):
+ * out[((n - n_first)·K + t)·P + p] = flat NCHW offset of the input element that column-matrix
+ * entry (n, t, p) reads, or -1 where it falls in the padding (K = Cin·kH·kW, P = outH·outW).
+ * `out` is a device buffer of n_count·K·P int64. For verification against
+ * ref: cuda/kernels/im2col.cu:67-98. */
+int tfb_im2col_index_map(int64_t* out, int64_t n_first, int64_t n_count, int64_t Cin, int64_t H, int64_t W,
+                         int64_t kH, int64_t kW, int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w,
+                         int64_t dil_h, int64_t dil_w, void* stream);
+
 /* ---- MLP training step neighbours ------------------------------------------------- */
 
 /* Mean negative log-likelihood of log_softmax(logits) and its gradient:

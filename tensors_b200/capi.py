@@ -41,6 +41,10 @@ PROTOTYPES = {
     "tfb_matmul_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tfb_linear_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_linear_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tfb_conv_out_dim": (_i64, [_i64, _i64, _i64, _i64, _i64]),
+    "tfb_conv2d_forward": (_i32, [_vp, _vp, _vp, _vp] + [_i64] * 13 + [_i32, _i32, _vp]),
+    "tfb_conv2d_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp] + [_i64] * 13 + [_i32, _vp]),
+    "tfb_im2col_index_map": (_i32, [_vp] + [_i64] * 13 + [_vp]),
     "tfb_log_softmax_nll": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tfb_sgd_momentum": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
 }

@@ -1,0 +1,406 @@
+// Implicit-GEMM convolution on tcgen05 (FP32 in/out through the 3xTF32 split).
+//
+// The column matrix of im2col is never written to memory. Producer warps gather input
+// elements straight from the NCHW tensor with the im2col index map, split each into TF32
+// hi + lo and store both into the shared-memory operand tile in the layout the tensor core
+// reads; the other operand (weights, or the upstream gradient for wgrad) arrives by TMA.
+//
+// One kernel, three contractions (D is always [128 "rows" x BN "columns"] per tile):
+//   fprop  rows = output positions of one sample, columns = output channels,
+//          contraction over taps t = (c, ki, kj):      out[n, co, p]  = Σ_t col[n][t, p] · W[co, t]
+//   dgrad  rows = input positions of one sample, columns = input channels,
+//          contraction over taps t = (co, ki, kj):     dX[n, c, q]    = Σ_t colT[n][t, q] · Wd[c, t]
+//          (gather form: each input pixel pulls the output pixels that touched it, so there
+//          is no scatter, no atomics and a fixed summation order)
+//   wgrad  rows = taps t = (c, ki, kj), columns = output channels, contraction over (n, p),
+//          split over CTAs:                            dW[co, t]     += Σ_{n,p} col[n][t, p] · dY[n, co, p]
+//          one extra all-ones tap makes the same product deliver the bias gradient.
+//
+// In all three the producer's lanes run over 32 consecutive spatial positions (coalesced global
+// reads, conflict-free shared-memory writes) for one tap at a time.
+//
+// Warp roles (320 threads): 0 = TMA for the B operand, 1 = MMA issuer + TMEM owner,
+// 2..5 = gather producers, 6..9 = epilogue. The TMEM accumulator is closed every `chunk_kb`
+// K blocks and summed in registers with round-to-nearest adds (see gemm_kernel.cuh).
+#pragma once
+
+#include "ptx.cuh"
+
+namespace tfb {
+
+enum ConvMode : int { kConvFprop = 0, kConvDgrad = 1, kConvWgrad = 2 };
+
+// Where tap t reads relative to a position: plane offset inside one sample and the two
+// coordinate offsets. plane_off < 0 marks taps that do not exist (-1) or the all-ones tap (-2).
+struct TapInfo {
+    int plane_off;
+    int ay;
+    int ax;
+    int pad;
+};
+
+struct ConvArgs {
+    const float* src;          // tensor the producers gather from (x for fprop / wgrad, dY for dgrad)
+    long long src_sample;      // elements per sample of src
+    int src_H, src_W;          // plane extents of src
+    int div_h, div_w;          // dgrad with stride > 1: coordinates must divide by these (else 1)
+    int mul_h, mul_w;          // position -> coordinate scale (stride for fprop / wgrad, 1 for dgrad)
+    int pos_W, pos_count;      // width of the position grid and positions per sample
+    int n_samples;
+    int taps;                  // entries of the tap table that may be valid (incl. the ones tap)
+    int taps_table;            // table length (multiple of 128)
+    const TapInfo* tap_table;  // device copy of the tap table
+    float* dst;                // output: dst[(outer * J + j) * rows_ext + row]
+    int J;                     // valid columns (output channels / input channels)
+    int rows_ext;              // row extent of the output (positions per sample, or taps for wgrad)
+    const float* bias;         // fprop: per-column bias or nullptr
+    int relu;
+    // tiling
+    int row_tiles, col_tiles, num_tiles;
+    int k_blocks;              // fprop / dgrad: tap blocks; wgrad: n_samples * pos_blocks
+    int pos_blocks;            // wgrad: 32-position blocks per sample
+    int splits;                // wgrad: CTAs sharing one output tile
+    int chunk_kb;
+    int b_rows_per_sample;     // wgrad: rows of the B matrix per sample (Cout)
+    int* status;
+};
+
+constexpr int kConvThreads = 320;
+
+template <int BN, int STAGES>
+struct ConvSmem {
+    static constexpr int A_TILE = 128 * 128;          // 128 rows x 32 fp32, per plane
+    static constexpr int B_TILE = BN * 128;
+    static constexpr int STAGE_BYTES = 2 * (A_TILE + B_TILE);
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int fixed() { return 1024 + STAGES * STAGE_BYTES + BAR_BYTES; }
+};
+
+__device__ __forceinline__ float tf32_rna_dev(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// The im2col index map as the producers evaluate it: source element (offset inside one sample)
+// that tap `ti` reads for the position whose scaled coordinates are (y0, x0), or -1 for padding.
+// fprop / wgrad: (u, v) = (oh*stride + ki*dil - pad, ow*stride + kj*dil - pad).
+// dgrad: (u, v) = ((ih + pad - ki*dil) / stride, ...) and only where the division is exact.
+template <int MODE>
+__device__ __forceinline__ int conv_src_offset(const TapInfo& ti, int y0, int x0, const ConvArgs& args) {
+    int u = y0 + ti.ay, v = x0 + ti.ax;
+    if (MODE == kConvDgrad && (args.div_h != 1 || args.div_w != 1)) {
+        if (u < 0 || v < 0 || (u % args.div_h) != 0 || (v % args.div_w) != 0) return -1;
+        u /= args.div_h;
+        v /= args.div_w;
+    }
+    if ((unsigned)u >= (unsigned)args.src_H || (unsigned)v >= (unsigned)args.src_W) return -1;
+    return ti.plane_off + u * args.src_W + v;
+}
+
+template <int MODE, int BN, int STAGES>
+__global__ void __launch_bounds__(kConvThreads, 1)
+conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
+                  const ConvArgs args) {
+    using S = ConvSmem<BN, STAGES>;
+    constexpr bool WGRAD = (MODE == kConvWgrad);
+    constexpr uint32_t TMEM_COLS = (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t bars = smem_base + STAGES * S::STAGE_BYTES;
+    auto full_a = [&](int s) { return bars + 8u * s; };
+    auto full_b = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+    auto tfull_bar = [&](int b) { return bars + 8u * (3 * STAGES + b); };
+    auto tempty_bar = [&](int b) { return bars + 8u * (3 * STAGES + 2 + b); };
+    uint8_t* after_bars = smem_gen + STAGES * S::STAGE_BYTES + 8 * (3 * STAGES + 4);
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(after_bars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(after_bars + 4);
+    TapInfo* taps_sm = reinterpret_cast<TapInfo*>(smem_gen + STAGES * S::STAGE_BYTES + S::BAR_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_a(s), 128);
+            mbar_init(full_b(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), 128);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmB);
+        tma_prefetch_desc(&tmB2);
+    }
+    for (int i = threadIdx.x; i < args.taps_table; i += blockDim.x) taps_sm[i] = args.tap_table[i];
+    if (warp == 1) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    // Tile -> (row tile, column tile, outer index). fprop / dgrad: outer = sample; wgrad: outer = split.
+    auto decode_tile = [&](int t, int& rt, int& ct, int& outer) {
+        ct = t % args.col_tiles;
+        const int r = t / args.col_tiles;
+        rt = r % args.row_tiles;
+        outer = r / args.row_tiles;
+    };
+    // K-block range of a tile.
+    auto k_range = [&](int outer, int& kb0, int& kb1) {
+        if constexpr (WGRAD) {
+            const int per = (args.k_blocks + args.splits - 1) / args.splits;
+            kb0 = outer * per;
+            kb1 = min(kb0 + per, args.k_blocks);
+            if (kb0 > kb1) kb0 = kb1;
+        } else {
+            kb0 = 0;
+            kb1 = args.k_blocks;
+        }
+    };
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer for B -----------------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+                int rt, ct, outer, kb0, kb1;
+                decode_tile(t, rt, ct, outer);
+                k_range(outer, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
+                    if (!ok) break;
+                    const uint32_t b_hi = smem_base + s * S::STAGE_BYTES + 2 * S::A_TILE;
+                    const uint32_t b_lo = b_hi + S::B_TILE;
+                    mbar_arrive_expect_tx(full_b(s), 2 * S::B_TILE);
+                    int x, y;
+                    if constexpr (WGRAD) {
+                        const int n = kb / args.pos_blocks, pb = kb - n * args.pos_blocks;
+                        x = pb * 32;
+                        y = n * args.b_rows_per_sample + ct * BN;
+                    } else {
+                        x = kb * 32;
+                        y = ct * BN;
+                    }
+                    tma_load_2d(b_hi, &tmB, x, y, full_b(s));
+                    tma_load_2d(b_lo, &tmB2, x, y, full_b(s));
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (!ok || *abort_flag != 0) {
+                for (int i = 0; i < STAGES; ++i) {
+                    const uint64_t t0 = global_timer_ns();
+                    while (!mbar_try_wait(full_b(i), 0) && !mbar_try_wait(full_b(i), 1)) {
+                        if (global_timer_ns() - t0 > 100000000ull) {
+                            if (args.status != nullptr) atomicCAS(args.status, 0, kDevTimeoutDrain);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ---------------------------------------
+        if (lane == 0) {
+            // A: fprop / dgrad tiles are MN-major (rows = positions contiguous) in the 128-byte
+            //    swizzle with 32-byte atoms: 32-row groups 4096 B apart, 4-tap groups 512 B apart,
+            //    one K step = 8 taps = 1024 B.  wgrad tiles are K-major (positions = contraction
+            //    contiguous), plain 128-byte swizzle, 8-row groups 1024 B apart, K step = 32 B.
+            // B: always K-major, 128-byte swizzle.
+            constexpr uint32_t A_MN = WGRAD ? 0u : 1u;
+            constexpr uint32_t A_LBO = WGRAD ? 16u : 4096u;
+            constexpr uint32_t A_SBO = WGRAD ? 1024u : 512u;
+            constexpr uint32_t A_SWZ = WGRAD ? 2u : 1u;
+            constexpr uint32_t A_KSTEP = WGRAD ? 32u : 1024u;
+            const uint32_t idesc = make_idesc(2u, A_MN, 0u, 128, BN);
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t cit = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+                int rt, ct, outer, kb0, kb1;
+                decode_tile(t, rt, ct, outer);
+                k_range(outer, kb0, kb1);
+                // Every tile has at least one K block (the host sizes the wgrad splits that way).
+                for (int c0 = kb0; c0 < kb1 && ok; c0 += args.chunk_kb, ++cit) {
+                    const uint32_t buf = cit & 1u;
+                    const uint32_t use = cit >> 1;
+                    ok = mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u, abort_flag, args.status, kDevTimeoutTmemEmpty);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + buf * (uint32_t)BN;
+                    const int c1 = min(c0 + args.chunk_kb, kb1);
+                    for (int kb = c0; kb < c1; ++kb) {
+                        ok = mbar_wait(full_a(s), ph, abort_flag, args.status, kDevTimeoutFull) &&
+                             mbar_wait(full_b(s), ph, abort_flag, args.status, kDevTimeoutFull);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        const uint32_t st = smem_base + s * S::STAGE_BYTES;
+                        const uint32_t a_hi = st, a_lo = st + S::A_TILE;
+                        const uint32_t b_hi = st + 2 * S::A_TILE, b_lo = b_hi + S::B_TILE;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t acc = (kb > c0 || j > 0) ? 1u : 0u;
+                            const uint64_t da = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_SWZ);
+                            const uint64_t dal = make_smem_desc(a_lo + j * A_KSTEP, A_LBO, A_SBO, A_SWZ);
+                            const uint64_t db = make_smem_desc(b_hi + j * 32u, 16u, 1024u, 2u);
+                            const uint64_t dbl = make_smem_desc(b_lo + j * 32u, 16u, 1024u, 2u);
+                            umma_ss<1, true>(d_tmem, dal, db, idesc, acc);
+                            umma_ss<1, true>(d_tmem, da, dbl, idesc, 1u);
+                            umma_ss<1, true>(d_tmem, da, db, idesc, 1u);
+                        }
+                        umma_commit<1>(empty_bar(s));
+                        if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    }
+                    if (!ok) break;
+                    umma_commit<1>(tfull_bar(buf));
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------ gather producers ------------------------------------
+        const int pw = warp - 2;   // 0..3
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+            int rt, ct, outer, kb0, kb1;
+            decode_tile(t, rt, ct, outer);
+            k_range(outer, kb0, kb1);
+            // fprop / dgrad: this thread's position is fixed for the tile.
+            int pos = 0, y0 = 0, x0 = 0;
+            bool pos_ok = false;
+            const float* base = args.src;
+            if constexpr (!WGRAD) {
+                pos = rt * 128 + pw * 32 + lane;
+                pos_ok = pos < args.pos_count;
+                const int oy = pos / args.pos_W, ox = pos - oy * args.pos_W;
+                y0 = oy * args.mul_h;
+                x0 = ox * args.mul_w;
+                base = args.src + (long long)outer * args.src_sample;
+            }
+            for (int kb = kb0; kb < kb1; ++kb) {
+                ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t* a_hi = smem_gen + s * S::STAGE_BYTES;
+                uint8_t* a_lo = a_hi + S::A_TILE;
+                int tap0;
+                uint32_t off0;   // byte offset of (tap index i = 0) for this thread, before swizzling
+                if constexpr (WGRAD) {
+                    const int n = kb / args.pos_blocks, pb = kb - n * args.pos_blocks;
+                    pos = pb * 32 + lane;
+                    pos_ok = pos < args.pos_count;
+                    const int oy = pos / args.pos_W, ox = pos - oy * args.pos_W;
+                    y0 = oy * args.mul_h;
+                    x0 = ox * args.mul_w;
+                    base = args.src + (long long)n * args.src_sample;
+                    tap0 = rt * 128 + pw * 32;   // rows (taps) pw*32 .. +31 of the tile
+                    off0 = 0;
+                } else {
+                    tap0 = kb * 32;              // K index = tap; this warp owns rows pw*32 .. +31
+                    off0 = (uint32_t)pw * 4096u + (uint32_t)(lane & 7) * 4u;
+                }
+#pragma unroll 4
+                for (int i = 0; i < 32; ++i) {
+                    const TapInfo ti = taps_sm[tap0 + i];
+                    float val = 0.f;
+                    if (ti.plane_off >= 0) {
+                        const int off = pos_ok ? conv_src_offset<MODE>(ti, y0, x0, args) : -1;
+                        if (off >= 0) val = __ldg(base + off);
+                    } else if (ti.plane_off == -2) {
+                        val = pos_ok ? 1.f : 0.f;
+                    }
+                    const float hi = tf32_rna_dev(val);
+                    const float lo = val - hi;
+                    uint32_t off;
+                    if constexpr (WGRAD) {
+                        // row m = pw*32 + i, contraction index kk = lane: K-major, 128-byte swizzle
+                        const uint32_t m = (uint32_t)(pw * 32 + i);
+                        off = m * 128u + ((((uint32_t)lane >> 2) ^ (m & 7u)) << 4) + ((uint32_t)lane & 3u) * 4u;
+                    } else {
+                        // row = position (lane), contraction index kk = i: MN-major, 32-byte atoms
+                        off = off0 + (uint32_t)i * 128u + ((((uint32_t)lane >> 3) ^ ((uint32_t)i & 3u)) << 5);
+                    }
+                    *reinterpret_cast<float*>(a_hi + off) = hi;
+                    *reinterpret_cast<float*>(a_lo + off) = lo;
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(full_a(s));
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------------------
+        const int q = warp & 3;   // warps 6..9 -> TMEM lane quarters 2, 3, 0, 1
+        uint32_t cit = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+            int rt, ct, outer, kb0, kb1;
+            decode_tile(t, rt, ct, outer);
+            k_range(outer, kb0, kb1);
+            const int row = rt * 128 + q * 32 + lane;
+            const bool row_ok = row < args.rows_ext;
+            const int j0 = ct * BN;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            float acc[BN];
+#pragma unroll
+            for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+            for (int c0 = kb0; c0 < kb1; c0 += args.chunk_kb, ++cit) {
+                const uint32_t buf = cit & 1u;
+                const uint32_t use = cit >> 1;
+                ok = mbar_wait(tfull_bar(buf), use & 1u, abort_flag, args.status, kDevTimeoutTmemFull);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    if (j0 + c * 32 < args.J) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(lane_addr + buf * (uint32_t)BN + (uint32_t)(c * 32), r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
+                    }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(tempty_bar(buf));
+            }
+            if (!ok) break;
+            if (row_ok) {
+                // Lanes hold consecutive rows, so each column is one coalesced 128-byte store.
+                float* dst = args.dst + ((long long)outer * args.J + j0) * args.rows_ext + row;
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    if (j0 + i < args.J) {
+                        float v = acc[i];
+                        if (args.bias != nullptr) v += __ldg(args.bias + j0 + i);
+                        if (args.relu) v = v > 0.f ? v : 0.f;
+                        dst[(long long)i * args.rows_ext] = v;
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace tfb

@@ -42,9 +42,12 @@ int resolve_encoder() {
 // 2-D map over a row-major matrix: `inner` contiguous elements per row, `outer` rows,
 // rows `row_stride_bytes` apart; box of box_inner x box_outer elements, 128-byte swizzle,
 // out-of-range elements read as zero.
+}  // namespace
+
 int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
-             uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
-             bool atom32 = false) {
+             uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32) {
+    int rc0 = resolve_encoder();
+    if (rc0 != TFB_OK) return rc0;
     CUtensorMapDataType dt = dtype == TFB_DTYPE_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                              : dtype == TFB_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -63,6 +66,8 @@ int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint
                     (unsigned long long)row_stride_bytes, box_inner, box_outer);
     return TFB_OK;
 }
+
+namespace {
 
 // ---------------------------------------------------------------------------
 // Operand preparation kernels (HBM-bound, one pass)

@@ -3,6 +3,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "../../include/tfb.h"
@@ -65,6 +66,12 @@ struct GemmCall {
 int gemm_run(const GemmCall& call, cudaStream_t stream);
 // Scratch bytes gemm_run needs for this call (0 for aligned 16-bit inputs).
 size_t gemm_workspace_bytes(const GemmCall& call);
+
+// 2-D tensor map over a row-major matrix (`inner` contiguous elements per row, `outer` rows,
+// rows row_stride_bytes apart) with a box of box_inner x box_outer elements and the 128-byte
+// swizzle; atom32 selects the variant with 32-byte atoms that MN-major FP32 operands need.
+int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
+             uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false);
 
 // Splits a row-major FP32 matrix (rows x cols, leading dimension ld) into TF32 hi / lo
 // planes with leading dimension ld_out (multiple of 4, padding zero-filled).

@@ -1,0 +1,188 @@
+"""Parity of the implicit-GEMM Conv2d (forward, dgrad, wgrad, bias gradient) with the oracle, with the
+reference's own known answers and golden outputs, and the bit-exact im2col index map."""
+import numpy as np
+import pytest
+import torch
+
+import refdata
+import tensors_b200.capi as capi
+from golden.make_golden import CONV_CHANNELS_L1, CONV_CHANNELS_L2
+from gpu_util import assert_device_ok, dev, lib, ptr, rel_err, stream_ptr
+
+pytestmark = pytest.mark.gpu
+FP32_TOL = 1e-5
+
+
+def out_dim(n, k, s, p, d):
+    return int(lib.tfb_conv_out_dim(n, k, s, p, d))
+
+
+def conv_forward(x, w, b, stride=(1, 1), pad=(0, 0), dil=(1, 1), relu=False):
+    N, C, H, W = x.shape
+    Cout, _, kH, kW = w.shape
+    oH, oW = out_dim(H, kH, stride[0], pad[0], dil[0]), out_dim(W, kW, stride[1], pad[1], dil[1])
+    X, Wt = dev(x), dev(w)
+    B = dev(b) if b is not None else None
+    out = torch.full((N, Cout, oH, oW), float("nan"), device="cuda")
+    capi.check(lib.tfb_conv2d_forward(ptr(X), ptr(Wt), ptr(B), ptr(out), N, C, H, W, Cout, kH, kW, stride[0], stride[1],
+                                      pad[0], pad[1], dil[0], dil[1], int(relu), capi.DTYPE_F32, stream_ptr()))
+    assert_device_ok()
+    return out.cpu().numpy()
+
+
+def conv_backward(x, w, g, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
+    N, C, H, W = x.shape
+    Cout, _, kH, kW = w.shape
+    X, Wt, G = dev(x), dev(w), dev(g)
+    gi = torch.full(x.shape, float("nan"), device="cuda")
+    gw = torch.full(w.shape, float("nan"), device="cuda")
+    gb = torch.full((Cout,), float("nan"), device="cuda")
+    capi.check(lib.tfb_conv2d_backward(ptr(X), ptr(Wt), ptr(G), ptr(gi), ptr(gw), ptr(gb), N, C, H, W, Cout, kH, kW,
+                                       stride[0], stride[1], pad[0], pad[1], dil[0], dil[1], capi.DTYPE_F32, stream_ptr()))
+    assert_device_ok()
+    return gi.cpu().numpy(), gw.cpu().numpy(), gb.cpu().numpy()
+
+
+def test_reference_known_answers():
+    # nn/conv2d_forward_test.cpp:112-137 and nn/conv2d_backward_test.cpp:110-160
+    x = np.array([1, 2, 3, 4], np.float32).reshape(1, 1, 2, 2)
+    w = np.array([2.0], np.float32).reshape(1, 1, 1, 1)
+    np.testing.assert_allclose(conv_forward(x, w, None).ravel(), [2, 4, 6, 8], rtol=1e-6)
+    go = np.array([0.1, 0.2, 0.3, 0.4], np.float32).reshape(1, 1, 2, 2)
+    gi, gw, gb = conv_backward(x, w, go)
+    np.testing.assert_allclose(gi.ravel(), [0.2, 0.4, 0.6, 0.8], rtol=1e-4)
+    np.testing.assert_allclose(gw.ravel(), [3.0], rtol=1e-4)
+    np.testing.assert_allclose(gb.ravel(), [1.0], rtol=1e-4)
+
+
+def test_reference_backward_test_patterns(oracle):
+    # the fill patterns of nn/conv2d_backward_test.cpp:162-300, tolerance of those tests (1e-3) or tighter
+    f = np.float32
+    cases = []
+    w = np.arange(1, 9, dtype=f).reshape(2, 1, 2, 2)
+    x = (f(0.1) * np.arange(1, 19, dtype=f)).reshape(2, 1, 3, 3)
+    go = (f(0.01) * ((np.arange(16) % 11) + 1).astype(f)).reshape(2, 2, 2, 2)
+    cases.append((x, w, np.array([0.1, -0.2], f), go, (0, 0)))
+    w = (f(0.02) * ((np.arange(3 * 2 * 9) % 7) + 1).astype(f)).reshape(3, 2, 3, 3)
+    x = (f(0.05) * ((np.arange(2 * 16) % 5) + 1).astype(f)).reshape(1, 2, 4, 4)
+    go = (f(0.01) * ((np.arange(3 * 16) % 13) + 1).astype(f)).reshape(1, 3, 4, 4)
+    cases.append((x, w, np.array([0.3, 0.1, -0.2], f), go, (1, 1)))
+    w = np.full((1, 1, 2, 2), 0.5, f)
+    x = np.arange(1, 10, dtype=f).reshape(1, 1, 3, 3)
+    go = (f(0.1) * np.arange(1, 5, dtype=f)).reshape(1, 1, 2, 2)
+    cases.append((x, w, None, go, (0, 0)))
+    for x, w, b, go, pad in cases:
+        y = conv_forward(x, w, b, pad=pad)
+        np.testing.assert_allclose(y, oracle.conv2d_forward(x, w, b, pad=pad), rtol=1e-5, atol=1e-6)
+        gi, gw, gb = conv_backward(x, w, go, pad=pad)
+        oi, ow, ob = oracle.conv2d_backward(x, w, go, pad=pad)
+        np.testing.assert_allclose(gi, oi, rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(gw, ow, rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(gb, ob, rtol=1e-4, atol=1e-6)
+
+
+def test_forward_against_reference_golden(golden):
+    # 3 -> 64 and 64 -> 128 channels, 3x3, pad 1, stride 1 on 32x32 images, reference Kaiming weights
+    x, w1 = refdata.normal(31, (2, 3, 32, 32)), refdata.conv_weight(3, 64, 3)
+    y1 = conv_forward(x, w1, None, pad=(1, 1))
+    assert rel_err(y1[:, CONV_CHANNELS_L1], golden["conv_l1_Y_ch"]) < FP32_TOL
+    assert rel_err(y1.astype(np.float64).sum(axis=(0, 2, 3)), golden["conv_l1_Y_sum"]) < FP32_TOL
+    x2, w2 = refdata.normal(32, (1, 64, 32, 32)), refdata.conv_weight(64, 128, 3)
+    y2 = conv_forward(x2, w2, None, pad=(1, 1))
+    assert rel_err(y2[:, CONV_CHANNELS_L2], golden["conv_l2_Y_ch"]) < FP32_TOL
+    assert rel_err(y2.astype(np.float64).sum(axis=(0, 2, 3)), golden["conv_l2_Y_sum"]) < FP32_TOL
+    xs, ws = refdata.normal(33, (2, 4, 9, 11)), refdata.conv_weight(4, 6, 3)
+    ys = conv_forward(xs, ws, None, (2, 2), (2, 2), (2, 2))
+    assert rel_err(ys, golden["conv_s2p2d2_Y"]) < FP32_TOL
+
+
+@pytest.mark.parametrize("case", [
+    # N, Cin, H, W, Cout, kH, kW, stride, pad, dil
+    (2, 3, 32, 32, 64, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (2, 64, 32, 32, 128, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (3, 5, 13, 17, 7, 3, 2, (2, 1), (1, 2), (1, 2)),
+    (2, 4, 9, 11, 6, 3, 3, (2, 2), (2, 2), (2, 2)),
+    (1, 130, 6, 5, 140, 1, 1, (1, 1), (0, 0), (1, 1)),
+    (2, 2, 40, 40, 3, 5, 5, (3, 3), (2, 2), (1, 1)),
+    (1, 1, 1, 1, 1, 1, 1, (1, 1), (0, 0), (1, 1)),
+])
+def test_forward_backward_against_oracle(oracle, case):
+    N, Cin, H, W, Cout, kH, kW, stride, pad, dil = case
+    x = refdata.normal(1, (N, Cin, H, W))
+    w = refdata.kaiming_uniform((Cout, Cin, kH, kW), Cin * kH * kW)
+    b = refdata.normal(2, (Cout,)) * np.float32(0.1)
+    y = conv_forward(x, w, b, stride, pad, dil)
+    assert not np.isnan(y).any()
+    assert rel_err(y, oracle.conv2d_forward(x, w, b, stride, pad, dil)) < FP32_TOL
+    yr = conv_forward(x, w, b, stride, pad, dil, relu=True)
+    assert rel_err(yr, np.maximum(oracle.conv2d_forward(x, w, b, stride, pad, dil), 0)) < FP32_TOL
+    g = refdata.normal(3, y.shape)
+    gi, gw, gb = conv_backward(x, w, g, stride, pad, dil)
+    oi, ow, ob = oracle.conv2d_backward(x, w, g, stride, pad, dil)
+    assert not (np.isnan(gi).any() or np.isnan(gw).any() or np.isnan(gb).any())
+    assert rel_err(gi, oi) < FP32_TOL
+    assert rel_err(gw, ow) < FP32_TOL
+    assert rel_err(gb, ob) < FP32_TOL
+
+
+def index_map(n_first, n_count, Cin, H, W, kH, kW, sh, sw, ph, pw, dh, dw):
+    K, P = Cin * kH * kW, out_dim(H, kH, sh, ph, dh) * out_dim(W, kW, sw, pw, dw)
+    out = torch.full((n_count * K * P,), -7, device="cuda", dtype=torch.int64)
+    capi.check(lib.tfb_im2col_index_map(ptr(out), n_first, n_count, Cin, H, W, kH, kW, sh, sw, ph, pw, dh, dw, stream_ptr()))
+    assert_device_ok()
+    return out.cpu().numpy()
+
+
+def test_im2col_index_map_bit_exact(oracle):
+    # layer 1 of the CIFAR-shaped configuration over its entire index space (128 x 27 x 1024 entries)
+    got = index_map(0, 128, 3, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1)
+    want = oracle.im2col_index_range(0, got.size, 3, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1)
+    assert np.array_equal(got, want)
+    # layer 2 (75.5 M entries): the map repeats per sample up to the sample offset; first, middle, last
+    per_n = 576 * 1024
+    for n in (0, 64, 127):
+        got = index_map(n, 1, 64, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1)
+        want = oracle.im2col_index_range(n * per_n, per_n, 64, 32, 32, 3, 3, 1, 1, 1, 1, 1, 1)
+        assert np.array_equal(got, want)
+    # strided, dilated and asymmetric cases
+    for args in [(5, 13, 17, 3, 2, 2, 1, 1, 2, 1, 2), (4, 9, 11, 3, 3, 2, 2, 2, 2, 2, 2), (2, 40, 40, 5, 5, 3, 3, 2, 2, 1, 1)]:
+        got = index_map(0, 3, *args)
+        want = oracle.im2col_index_range(0, got.size, *args)
+        assert np.array_equal(got, want)
+
+
+def test_config3_full_size_properties_and_sampled_oracle(oracle):
+    # N = 128 images of 3x32x32 through both layers; the scalar oracle covers a few samples, the
+    # adjoint identities <conv(x,w), g> = <x, dgrad(g)> = <w, wgrad(x,g)> cover the whole batch.
+    N = 128
+    x = refdata.normal(31, (N, 3, 32, 32))
+    w1, w2 = refdata.conv_weight(3, 64, 3), refdata.conv_weight(64, 128, 3)
+    y1 = conv_forward(x, w1, np.zeros(64, np.float32), pad=(1, 1))
+    y2 = conv_forward(y1, w2, np.zeros(128, np.float32), pad=(1, 1))
+    for n in (0, 127):
+        assert rel_err(y1[n:n + 1], oracle.conv2d_forward(x[n:n + 1], w1, None, pad=(1, 1))) < FP32_TOL
+    assert rel_err(y2[5:6], oracle.conv2d_forward(y1[5:6], w2, None, pad=(1, 1))) < FP32_TOL
+    for xin, w, y in ((x, w1, y1), (y1, w2, y2)):
+        g = refdata.normal(77, y.shape)
+        gi, gw, gb = conv_backward(xin, w, g, pad=(1, 1))
+        lhs = float(np.vdot(y.astype(np.float64), g.astype(np.float64)))
+        assert abs(float(np.vdot(xin.astype(np.float64), gi.astype(np.float64))) - lhs) < 1e-5 * abs(lhs) + 1e-3
+        assert abs(float(np.vdot(w.astype(np.float64), gw.astype(np.float64))) - lhs) < 1e-5 * abs(lhs) + 1e-3
+        assert rel_err(gb, g.astype(np.float64).sum(axis=(0, 2, 3))) < FP32_TOL
+        # sampled oracle for the gradients: two samples' worth of dgrad; wgrad of a 2-sample sub-batch
+        oi, _, _ = oracle.conv2d_backward(xin[3:5], w, g[3:5], pad=(1, 1))
+        assert rel_err(gi[3:5], oi) < FP32_TOL
+        _, gw2, gb2 = conv_backward(xin[3:5], w, g[3:5], pad=(1, 1))
+        _, ow2, ob2 = oracle.conv2d_backward(xin[3:5], w, g[3:5], pad=(1, 1))
+        assert rel_err(gw2, ow2) < FP32_TOL
+        assert rel_err(gb2, ob2) < FP32_TOL
+
+
+def test_conv_argument_errors():
+    t = torch.zeros(16, device="cuda")
+    args = [ptr(t), ptr(t), None, ptr(t), 1, 1, 2, 2, 1, 1, 1, 1, 1, 0, 0, 1, 1, 0]
+    assert lib.tfb_conv2d_forward(*args, capi.DTYPE_BF16, stream_ptr()) == -2
+    bad = list(args)
+    bad[11] = 0  # stride_h
+    assert lib.tfb_conv2d_forward(*bad, capi.DTYPE_F32, stream_ptr()) == -1
+    assert lib.tfb_conv2d_forward(None, ptr(t), None, ptr(t), *args[4:], capi.DTYPE_F32, stream_ptr()) == -1
