@@ -104,6 +104,21 @@ int tfb_gemm_presplit(const float* A_hi, const float* A_lo, const float* B_hi, c
                       int64_t ldc, int trans_a, int trans_b, const float* bias, int epilogue_flags,
                       void* stream);
 
+/* FP32 C[M,N] = A[M,K] · B[K,N] (row-major, dense) that never allocates: for hosts that may not
+ * call cudaMalloc where they call us — inside a latency-critical loop that cannot take the
+ * allocator's locks or its device-wide synchronisation, under a runtime that owns all device
+ * memory through its own arena, or during teardown. The scratch for the TF32 hi / lo operand
+ * planes is a fixed 16 MiB array inside the library (tfb_matmul_f32_static_limit() bytes; every
+ * GPU that loads the library holds it until the process exits), so products whose split operands
+ * do not fit — about M·K + K·N > 2 Mi elements — are rejected with TFB_ERR_TOO_LARGE.
+ * The first call on each device looks up the array's device address; make that call before any
+ * stream capture. All calls on a device share the array: calls that may overlap on the GPU
+ * (different streams) race on it, calls on one stream are safe. Same results as tfb_matmul.
+ * This entry point has no counterpart in the reference. */
+size_t tfb_matmul_f32_static_limit(void);
+int tfb_matmul_f32_static(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                          void* stream);
+
 /* dA[M,K] = dC[M,N] · Bᵀ and dB[K,N] = Aᵀ · dC for C = A · B (row-major, dense). Either
  * output pointer may be NULL to skip it. ref: MatmulBackward::apply,
  * autograd/ops/MatmulBackward.hpp:26-34. */

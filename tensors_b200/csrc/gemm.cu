@@ -215,17 +215,22 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
+int split_operand_on(int sm_count, const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
+                     float* hi, float* lo, int64_t ld_out, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return TFB_OK;
+    const long long items = rows * (ld_out >> 2);
+    split_tf32_kernel<<<grid_for(items, 256, sm_count), 256, 0, stream>>>(
+        src, rows, cols, ld, mask, hi, lo, ld_out);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
 int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
                   float* hi, float* lo, int64_t ld_out, cudaStream_t stream) {
     DeviceState* st = nullptr;
     int rc = device_state(&st);
     if (rc != TFB_OK) return rc;
-    if (rows <= 0 || cols <= 0) return TFB_OK;
-    const long long items = rows * (ld_out >> 2);
-    split_tf32_kernel<<<grid_for(items, 256, st->sm_count), 256, 0, stream>>>(
-        src, rows, cols, ld, mask, hi, lo, ld_out);
-    TFB_CUDA_OK(cudaGetLastError());
-    return TFB_OK;
+    return split_operand_on(st->sm_count, src, rows, cols, ld, mask, hi, lo, ld_out, stream);
 }
 
 size_t gemm_workspace_bytes(const GemmCall& c) {
@@ -244,6 +249,14 @@ size_t gemm_workspace_bytes(const GemmCall& c) {
 
 int gemm_run(const GemmCall& c, cudaStream_t stream) {
     if (c.M <= 0 || c.N <= 0) return TFB_OK;
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    return gemm_run_on(c, stream, st);
+}
+
+int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
+    if (c.M <= 0 || c.N <= 0) return TFB_OK;
     if (c.A == nullptr || c.B == nullptr || c.C == nullptr)
         return fail(TFB_ERR_INVALID_ARG, "gemm: null operand pointer");
     if (c.in_dtype != TFB_DTYPE_F32 && c.in_dtype != TFB_DTYPE_F16 && c.in_dtype != TFB_DTYPE_BF16)
@@ -259,10 +272,7 @@ int gemm_run(const GemmCall& c, cudaStream_t stream) {
     if (c.bias_mode != 0 && c.bias == nullptr)
         return fail(TFB_ERR_INVALID_ARG, "gemm: bias epilogue requested without a bias pointer");
 
-    DeviceState* st = nullptr;
-    int rc = device_state(&st);
-    if (rc != TFB_OK) return rc;
-    rc = resolve_encoder();
+    int rc = resolve_encoder();
     if (rc != TFB_OK) return rc;
 
     const bool f32 = c.in_dtype == TFB_DTYPE_F32;
@@ -300,8 +310,8 @@ int gemm_run(const GemmCall& c, cudaStream_t stream) {
                 const int64_t ldp = round_up(a_cols, 4);
                 float* hi = reinterpret_cast<float*>(carve((size_t)(2 * a_rows * ldp * 4)));
                 float* lo = hi + a_rows * ldp;
-                rc = split_operand(static_cast<const float*>(c.A), a_rows, a_cols, c.lda, c.a_mask, hi,
-                                   lo, ldp, stream);
+                rc = split_operand_on(st->sm_count, static_cast<const float*>(c.A), a_rows, a_cols, c.lda,
+                                      c.a_mask, hi, lo, ldp, stream);
                 if (rc != TFB_OK) return rc;
                 a_ptr[0] = hi; a_ptr[1] = lo; lda = ldp;
             }
@@ -311,8 +321,8 @@ int gemm_run(const GemmCall& c, cudaStream_t stream) {
                 const int64_t ldp = round_up(b_cols, 4);
                 float* hi = reinterpret_cast<float*>(carve((size_t)(2 * b_rows * ldp * 4)));
                 float* lo = hi + b_rows * ldp;
-                rc = split_operand(static_cast<const float*>(c.B), b_rows, b_cols, c.ldb, nullptr, hi, lo,
-                                   ldp, stream);
+                rc = split_operand_on(st->sm_count, static_cast<const float*>(c.B), b_rows, b_cols, c.ldb,
+                                      nullptr, hi, lo, ldp, stream);
                 if (rc != TFB_OK) return rc;
                 b_ptr[0] = hi; b_ptr[1] = lo; ldb = ldp;
             }

@@ -64,6 +64,9 @@ struct GemmCall {
     size_t workspace_bytes = 0;
 };
 int gemm_run(const GemmCall& call, cudaStream_t stream);
+// Same, with the device facts (SM count, status word) supplied by the caller instead of the
+// lazily created per-device state.
+int gemm_run_on(const GemmCall& call, cudaStream_t stream, const DeviceState* st);
 // Scratch bytes gemm_run needs for this call (0 for aligned 16-bit inputs).
 size_t gemm_workspace_bytes(const GemmCall& call);
 
