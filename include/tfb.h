@@ -200,6 +200,35 @@ int tfb_log_softmax_nll(const float* logits, const int64_t* labels, float* dlogi
 int tfb_sgd_momentum(float* params, float* velocity, const float* grads, int64_t n, float lr,
                      float momentum, float grad_scale, void* stream);
 
+/* ---- device memory: one explicit stream-ordered pool per device ------------------------ */
+
+/* ref for the whole group: CudaStorageAllocator, cuda/memory/CudaStorageAllocator.cpp:34-57
+ * (pool set-up, 64 MiB release threshold), :101-125 (allocate), :127-143 (free), :64-86 (copy
+ * callback). Differences by design: a pool per device instead of each device's default pool;
+ * the call runs with `device` current (the reference always issues on device 0's stream); a
+ * working free, so a Storage deleter can exist (tensor/Storage.hpp:27 has none). */
+int tfb_device_count(int* count_out);
+/* bytes == 0 allocates one byte, like the reference. `stream` must be a stream of `device`. */
+int tfb_alloc(int device, size_t bytes, void* stream, void** ptr_out);
+int tfb_free(void* ptr, int device, void* stream);
+int tfb_pool_set_release_threshold(int device, uint64_t bytes);
+int tfb_pool_trim(int device, size_t keep_bytes);
+int tfb_pool_stats(int device, uint64_t* reserved, uint64_t* used, uint64_t* reserved_high,
+                   uint64_t* used_high);
+/* Lets `peer` read and write memory allocated from `device`'s pool (plain peer loads / copies). */
+int tfb_pool_enable_peer(int device, int peer);
+/* Device and stream plumbing for hosts compiled without CUDA headers: a non-blocking stream per
+ * (thread, device) replaces the reference's single stream of device 0.
+ * ref: DeviceContext / CudaStream, cuda/CudaContext.cpp:18-60, cuda/CudaContext.hpp:134-140. */
+int tfb_set_device(int device);
+int tfb_get_device(int* device_out);
+int tfb_stream_create(int device, void** stream_out);
+int tfb_stream_destroy(void* stream);
+int tfb_stream_synchronize(void* stream);
+/* kind: 0 host-to-host, 1 host-to-device, 2 device-to-host, 3 device-to-device (the numbering of
+ * allocator_dispatch::CudaCopyKind). Asynchronous on `stream`. */
+int tfb_memcpy(void* dst, const void* src, size_t bytes, int kind, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

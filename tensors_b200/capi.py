@@ -49,6 +49,19 @@ PROTOTYPES = {
     "tfb_im2col_index_map": (_i32, [_vp] + [_i64] * 13 + [_vp]),
     "tfb_log_softmax_nll": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tfb_sgd_momentum": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
+    "tfb_device_count": (_i32, [_ip]),
+    "tfb_alloc": (_i32, [_i32, _sz, _vp, ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_free": (_i32, [_vp, _i32, _vp]),
+    "tfb_pool_set_release_threshold": (_i32, [_i32, ctypes.c_uint64]),
+    "tfb_pool_trim": (_i32, [_i32, _sz]),
+    "tfb_pool_stats": (_i32, [_i32] + [ctypes.POINTER(ctypes.c_uint64)] * 4),
+    "tfb_pool_enable_peer": (_i32, [_i32, _i32]),
+    "tfb_set_device": (_i32, [_i32]),
+    "tfb_get_device": (_i32, [_ip]),
+    "tfb_stream_create": (_i32, [_i32, ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_stream_destroy": (_i32, [_vp]),
+    "tfb_stream_synchronize": (_i32, [_vp]),
+    "tfb_memcpy": (_i32, [_vp, _vp, _sz, _i32, _vp]),
 }
 
 for _name, (_res, _args) in PROTOTYPES.items():

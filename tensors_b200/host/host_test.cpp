@@ -1,0 +1,160 @@
+// Checks of the host mirror that read like the reference's own tests (known answers of
+// cuda/kernels/gemm_*_test.cpp, autograd/ops/autograd_all_ops_test.cpp:281-328,
+// nn/conv2d_{forward,backward}_test.cpp, nn/linear_test.cpp, tensor/tensor_cuda_dispatch_test.cpp).
+//   host_test cpu   argument checks that need no GPU
+//   host_test gpu   everything (needs a B200)
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/tfb.h"
+#include "tensorforge_b200.hpp"
+
+using namespace tensorforge;
+
+static int g_failed = 0;
+#define CHECK(cond)                                                                 \
+    do {                                                                            \
+        if (!(cond)) {                                                              \
+            std::printf("CHECK failed at %s:%d: %s\n", __FILE__, __LINE__, #cond);  \
+            ++g_failed;                                                             \
+        }                                                                           \
+    } while (0)
+template <class F>
+static bool throws(F&& f) {
+    try { f(); } catch (const std::exception&) { return true; }
+    return false;
+}
+static bool approx(float a, float b, float eps) { return std::fabs(a - b) <= eps * std::fmax(1.0f, std::fabs(b)); }
+
+static Tensor upload(const std::vector<float>& h, Shape s, Device d = Device::cuda(0)) {
+    return Tensor::from_host(h.data(), std::move(s), Dtype::Float32, d);
+}
+static std::vector<float> download(const Tensor& t) {
+    std::vector<float> h(static_cast<size_t>(t.numel()));
+    t.copy_to_host(h.data());
+    return h;
+}
+
+static void cpu_checks() {
+    CHECK(registered_cuda_matmul() != nullptr);   // the static registrar ran
+    Tensor a = Tensor::empty(Shape{2, 3}, Dtype::Float32, Device::cpu());
+    Tensor b = Tensor::empty(Shape{4, 2}, Dtype::Float32, Device::cpu());
+    Tensor v = Tensor::empty(Shape{3}, Dtype::Float32, Device::cpu());
+    CHECK(throws([&] { (void)a.matmul(b); }));    // shape mismatch
+    CHECK(throws([&] { (void)a.matmul(v); }));    // not 2-D
+    Tensor c = Tensor::empty(Shape{3, 2}, Dtype::Float32, Device::cpu());
+    CHECK(throws([&] { (void)a.matmul(c); }));    // CPU tensors are not served here
+    register_cuda_matmul(nullptr);
+    CHECK(registered_cuda_matmul() == nullptr);
+    tfb_register_kernels();
+    CHECK(registered_cuda_matmul() != nullptr);
+    CHECK(dtype_size(Dtype::BFloat16) == 2 && dtype_size(Dtype::Int64) == 8);
+}
+
+static void gpu_checks() {
+    // 2x2 hand-computed case
+    Tensor A = upload({1, 2, 3, 4}, Shape{2, 2}), B = upload({5, 6, 7, 8}, Shape{2, 2});
+    auto C = download(A.matmul(B));
+    const float expected[4] = {19, 22, 43, 50};
+    for (int i = 0; i < 4; ++i) CHECK(approx(C[i], expected[i], 1e-5f));
+    // the launcher signature, non-multiple-of-16 bounds (17x19)*(19x23)
+    {
+        const int64_t M = 17, K = 19, N = 23;
+        std::vector<float> a(M * K), b(K * N), want(M * N, 0.f);
+        for (int64_t i = 0; i < M * K; ++i) a[i] = 0.01f * float(i + 1);
+        for (int64_t i = 0; i < K * N; ++i) b[i] = 0.02f * float((i % 7) + 1);
+        for (int64_t m = 0; m < M; ++m)
+            for (int64_t n = 0; n < N; ++n) {
+                float s = 0.f;
+                for (int64_t k = 0; k < K; ++k) s += a[m * K + k] * b[k * N + n];
+                want[m * N + n] = s;
+            }
+        Tensor At = upload(a, Shape{M, K}), Bt = upload(b, Shape{K, N});
+        Tensor Ct = Tensor::empty(Shape{M, N}, Dtype::Float32, Device::cuda(0));
+        launch_gemm_optimized(At.data(), Bt.data(), Ct.data(), M, N, K, Dtype::Float32, DeviceContext::current().current_stream);
+        auto got = download(Ct);
+        for (int64_t i = 0; i < M * N; ++i) CHECK(approx(got[i], want[i], 1e-5f));
+    }
+    // MatmulBackward on the arange case: gA = [1,5,9;1,5,9], gB = [3,3;5,5;7,7]
+    {
+        Tensor a = upload({0, 1, 2, 3, 4, 5}, Shape{2, 3}), b = upload({0, 1, 2, 3, 4, 5}, Shape{3, 2});
+        auto c = download(a.matmul(b));
+        CHECK(approx(c[0], 10, 1e-6f) && approx(c[1], 13, 1e-6f) && approx(c[2], 28, 1e-6f) && approx(c[3], 40, 1e-6f));
+        MatmulBackward node(a, b);
+        auto grads = node.apply({upload({1, 1, 1, 1}, Shape{2, 2})});
+        auto ga = download(grads[0]), gb = download(grads[1]);
+        const float ea[6] = {1, 5, 9, 1, 5, 9}, eb[6] = {3, 3, 5, 5, 7, 7};
+        for (int i = 0; i < 6; ++i) CHECK(approx(ga[i], ea[i], 1e-5f) && approx(gb[i], eb[i], 1e-5f));
+    }
+    // nn::Linear shape contract (nn/linear_test.cpp:9-33) and gradient sizes
+    {
+        nn::Linear lin(3, 2);
+        Tensor x = upload({1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12}, Shape{4, 3});
+        Tensor y = lin.forward(x);
+        CHECK(y.shape()[0] == 4 && y.shape()[1] == 2);
+        auto g = lin.backward(x, y, upload(std::vector<float>(8, 1.f), Shape{4, 2}));
+        CHECK(g.grad_weight.numel() == 6 && g.grad_input.numel() == 12 && g.grad_bias.numel() == 2);
+        auto gb = download(g.grad_bias);
+        CHECK(approx(gb[0], 4.f, 1e-6f) && approx(gb[1], 4.f, 1e-6f));
+        CHECK(throws([&] { (void)lin.forward(upload({1, 2}, Shape{1, 2})); }));   // in_features mismatch
+    }
+    // Conv2d 1x1, weight 2: out = 2 * in; backward known answers
+    {
+        nn::Conv2d conv(1, 1, 1, 1, 1, 1, 0, 0, 1, 1, /*bias*/ false);
+        conv.weight() = upload({2.0f}, Shape{1, 1, 1, 1});
+        Tensor x = upload({1, 2, 3, 4}, Shape{1, 1, 2, 2});
+        auto y = download(conv.forward(x));
+        for (int i = 0; i < 4; ++i) CHECK(approx(y[i], 2.f * float(i + 1), 1e-5f));
+        auto gr = conv.backward(upload({0.1f, 0.2f, 0.3f, 0.4f}, Shape{1, 1, 2, 2}), x);
+        auto gi = download(gr.grad_input);
+        const float egi[4] = {0.2f, 0.4f, 0.6f, 0.8f};
+        for (int i = 0; i < 4; ++i) CHECK(approx(gi[i], egi[i], 1e-4f));
+        CHECK(approx(download(gr.grad_weight)[0], 3.0f, 1e-4f));
+        CHECK(approx(download(gr.grad_bias)[0], 0.0f, 1e-6f));   // no bias: zero-filled
+        // default constructor fill: weights 0.1, bias 0.05
+        nn::Conv2d dflt(2, 3, 3, 3, 1, 1, 1, 1);
+        CHECK(approx(download(dflt.weight())[7], 0.1f, 1e-7f) && approx(download(dflt.bias())[2], 0.05f, 1e-7f));
+    }
+    // allocator: a pool per device, memory really comes back
+    {
+        int ndev = 0;
+        tfb_device_count(&ndev);
+        uint64_t used0 = 0, used1 = 0, used2 = 0;
+        CudaStorageAllocator::instance().stats(0, nullptr, &used0);
+        {
+            Tensor big = Tensor::empty(Shape{1024, 1024}, Dtype::Float32, Device::cuda(0));
+            CudaStorageAllocator::instance().stats(0, nullptr, &used1);
+            CHECK(used1 >= used0 + 4u * 1024 * 1024);
+        }
+        DeviceContext::for_device(0).synchronize();
+        CudaStorageAllocator::instance().stats(0, nullptr, &used2);
+        CHECK(used2 <= used1 - 4u * 1024 * 1024);
+        if (ndev > 1) {
+            // tensors on another device: allocated from that device's pool, multiplied there
+            Tensor a1 = upload({1, 2, 3, 4}, Shape{2, 2}, Device::cuda(1)), b1 = upload({5, 6, 7, 8}, Shape{2, 2}, Device::cuda(1));
+            auto c1 = download(a1.matmul(b1));
+            for (int i = 0; i < 4; ++i) CHECK(approx(c1[i], expected[i], 1e-5f));
+            CHECK(throws([&] { (void)A.matmul(b1); }));   // operands on different devices
+        } else {
+            CHECK(throws([&] { (void)Tensor::empty(Shape{2}, Dtype::Float32, Device::cuda(1)); }));   // as tensor_cuda_dispatch_test.cpp:55-58
+        }
+    }
+    int code = -1;
+    CHECK(tfb_device_status(&code) == TFB_OK && code == 0);
+}
+
+int main(int argc, char** argv) {
+    const std::string mode = argc > 1 ? argv[1] : "cpu";
+    try {
+        cpu_checks();
+        if (mode == "gpu") gpu_checks();
+    } catch (const std::exception& e) {
+        std::printf("unexpected exception: %s\n", e.what());
+        return 2;
+    }
+    std::printf("%s checks: %s\n", mode.c_str(), g_failed == 0 ? "all passed" : "FAILED");
+    return g_failed == 0 ? 0 : 1;
+}

@@ -23,6 +23,13 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def shard_rows(global_rows, rank, world):
+    """Contiguous row range [begin, end) of the global batch that `rank` owns (sizes differ by at most 1)."""
+    base, extra = divmod(int(global_rows), int(world))
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
 class MLP:
     """dims = (d0, d1, ..., dL): L Linear layers, ReLU after all but the last."""
 
