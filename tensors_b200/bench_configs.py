@@ -1,0 +1,170 @@
+"""Timings of the named configurations other than the headline square GEMM (which bench.py covers):
+
+  config 1  FP32 GEMM 2048^3 through tfb_matmul
+  config 2  Linear 64x784 -> 256 forward + backward (bias, ReLU fused)
+  config 3  Conv2d 128x3x32x32 -> 64 -> 128, 3x3 pad 1: forward, backward per layer
+  config 4  square sweep 1024..16384, FP32 (3xTF32) and BF16
+  config 5  MLP 784-1024-1024-10 training step, batch 8192 / world size (NCCL all-reduce when > 1 rank)
+
+Run:  python -m tensors_b200.bench_configs [--configs 1,2,3,4,5] [--iters 20]
+      torchrun --nproc-per-node N -m tensors_b200.bench_configs --configs 5
+Prints one JSON line per measurement (CUDA events on the launching stream, median of `iters` after 3
+warm-up runs, as the reference's benches do: benchmarks/gemm_bench.cpp:99-124).
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for _p in (ROOT, os.path.join(ROOT, "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import refdata  # noqa: E402
+from tensors_b200 import capi  # noqa: E402
+from tensors_b200.mlp import MLP, shard_rows  # noqa: E402
+
+lib = capi.lib
+HBM_GBS = 6549.1
+
+
+def p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def time_us(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(times)
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def dev(a, dtype=torch.float32):
+    return torch.from_numpy(a).cuda().to(dtype)
+
+
+def config1(iters):
+    n = 2048
+    A, B = dev(refdata.uniform(0, (n, n))), dev(refdata.uniform(1, (n, n)))
+    C = torch.empty((n, n), device="cuda")
+    us = time_us(lambda: capi.check(lib.tfb_matmul(p(A), p(B), p(C), n, n, n, 0, 0, stream())), iters)
+    emit(config=1, what="FP32 GEMM 2048^3 via tfb_matmul (3 launches)", us=us, tflops=2 * n ** 3 / us / 1e6)
+
+
+def config2(iters):
+    batch, in_f, out_f = 64, 784, 256
+    X, W = dev(refdata.mnist_like(21, (batch, in_f))), dev(refdata.linear_weight(in_f, out_f))
+    b, G = torch.zeros(out_f, device="cuda"), dev(refdata.normal(22, (batch, out_f)))
+    Y, dX = torch.empty((batch, out_f), device="cuda"), torch.empty((batch, in_f), device="cuda")
+    dW, db = torch.empty((out_f, in_f), device="cuda"), torch.empty(out_f, device="cuda")
+    fwd = lambda: capi.check(lib.tfb_linear_forward(p(X), p(W), p(b), p(Y), batch, in_f, out_f, 1, 0, stream()))
+    bwd = lambda: capi.check(lib.tfb_linear_backward(p(X), p(W), p(Y), p(G), p(dX), p(dW), p(db), batch, in_f, out_f, 1, 0, stream()))
+    uf, ub = time_us(fwd, iters), time_us(bwd, iters)
+    fwd_bytes, bwd_bytes = 1.070e6, 2.14e6
+    emit(config=2, what="Linear 64x784->256 forward (bias+ReLU fused)", us=uf, gbs=fwd_bytes / uf / 1e3,
+         hbm_frac=fwd_bytes / uf / 1e3 / HBM_GBS, mflop=25.69)
+    emit(config=2, what="Linear backward (mask+split, dX, dW, db)", us=ub, gbs=bwd_bytes / ub / 1e3,
+         hbm_frac=bwd_bytes / ub / 1e3 / HBM_GBS, mflop=51.38)
+
+
+def config3(iters):
+    N = 128
+    x = dev(refdata.normal(31, (N, 3, 32, 32)))
+    for name, cin, cout, xin, alg_bytes, gflop in (("layer1 3->64", 3, 64, x, 35.1e6, 0.45298),
+                                                   ("layer2 64->128", 64, 128, None, 101.0e6, 19.33)):
+        if xin is None:
+            xin = dev(refdata.normal(32, (N, cin, 32, 32)))
+        w = dev(refdata.conv_weight(cin, cout, 3))
+        bias = torch.zeros(cout, device="cuda")
+        y = torch.empty((N, cout, 32, 32), device="cuda")
+        g = dev(refdata.normal(33, (N, cout, 32, 32)))
+        gi, gw, gb = torch.empty_like(xin), torch.empty_like(w), torch.empty(cout, device="cuda")
+        args = (N, cin, 32, 32, cout, 3, 3, 1, 1, 1, 1, 1, 1)
+        fwd = lambda: capi.check(lib.tfb_conv2d_forward(p(xin), p(w), p(bias), p(y), *args, 0, 0, stream()))
+        dgr = lambda: capi.check(lib.tfb_conv2d_backward(p(xin), p(w), p(g), p(gi), None, None, *args, 0, stream()))
+        wgr = lambda: capi.check(lib.tfb_conv2d_backward(p(xin), p(w), p(g), None, p(gw), p(gb), *args, 0, stream()))
+        for what, fn in (("forward", fwd), ("dgrad", dgr), ("wgrad+dbias", wgr)):
+            us = time_us(fn, iters)
+            emit(config=3, what=f"Conv2d {name} {what}, N=128 32x32 3x3 p1", us=us, tflops=gflop / us * 1e3,
+                 gbs=alg_bytes / us / 1e3)
+
+
+def config4(iters):
+    for n in (1024, 2048, 4096, 8192, 16384):
+        A, B = dev(refdata.uniform(2, (n, n))), dev(refdata.uniform(3, (n, n)))
+        C = torch.empty((n, n), device="cuda")
+        it = max(3, iters if n < 16384 else iters // 4)
+        us = time_us(lambda: capi.check(lib.tfb_matmul(p(A), p(B), p(C), n, n, n, 0, 0, stream())), it)
+        emit(config=4, what=f"FP32 (3xTF32) GEMM {n}^3", us=us, tflops=2 * n ** 3 / us / 1e6)
+        A16, B16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
+        del A, B
+        us = time_us(lambda: capi.check(lib.tfb_matmul(p(A16), p(B16), p(C), n, n, n, 2, 0, stream())), it)
+        emit(config=4, what=f"BF16 GEMM {n}^3 (FP32 accumulate/output)", us=us, tflops=2 * n ** 3 / us / 1e6)
+        del A16, B16, C
+        torch.cuda.empty_cache()
+
+
+def config5(iters):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    dims, batch = (784, 1024, 1024, 10), 8192
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    b, e = shard_rows(batch, rank, world)
+    X = dev(refdata.mnist_like(7, (batch, 784))[b:e])
+    labels = torch.from_numpy(refdata.labels(8, batch)[b:e]).cuda()
+    m = MLP(dims, ws)
+    step = lambda: m.train_step(X, labels, lr=0.1, momentum=0.9, global_rows=batch)
+    us = time_us(step, iters)
+    fb = time_us(lambda: m.forward_backward(X, labels, batch), iters)
+    ar = time_us(m.allreduce_grads, iters) if world > 1 else 0.0
+    if world > 1:
+        t = torch.tensor([us, fb, ar], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us, fb, ar = [float(v) for v in t.tolist()]
+    if rank == 0:
+        emit(config=5, what=f"MLP 784-1024-1024-10 step, global batch 8192 on {world} GPU(s)", us=us,
+             forward_backward_us=fb, allreduce_us=ar, tflops=78.35e9 / us / 1e6, loss=float(m.loss.item()))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--configs", default="1,2,3,4,5")
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    capi.check(lib.tfb_init())
+    for c in a.configs.split(","):
+        {"1": config1, "2": config2, "3": config3, "4": config4, "5": config5}[c.strip()](a.iters)
+    code = capi.device_status()
+    if code:
+        raise SystemExit(f"device error {code}")
+
+
+if __name__ == "__main__":
+    main()

@@ -165,10 +165,12 @@ int grid_for(long long work_items, int block, int sm_count) {
 // ---------------------------------------------------------------------------
 // Launch
 // ---------------------------------------------------------------------------
-template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN>
-int launch_variant(const CUtensorMap maps[4], const GemmArgs& args, int grid, cudaStream_t stream) {
-    using S = GemmSmem<KIND, BN, STAGES>;
-    auto kern = gemm_tcgen05_kernel<KIND, BN, STAGES, A_MN, B_MN>;
+// `workers`: CTAs of the persistent grid, or CTA pairs (clusters of two) when PAIR.
+template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR>
+int launch_variant(const CUtensorMap maps[5], const GemmArgs& args, int workers, cudaStream_t stream) {
+    using S = GemmSmem<KIND, BN, STAGES, PAIR>;
+    static_assert(S::TOTAL <= 232448, "stage ring + staging exceed the 227 KB shared-memory limit");
+    auto kern = gemm_tcgen05_kernel<KIND, BN, STAGES, A_MN, B_MN, PAIR>;
     static bool attr_set[64] = {false};
     int dev = 0;
     TFB_CUDA_OK(cudaGetDevice(&dev));
@@ -176,18 +178,29 @@ int launch_variant(const CUtensorMap maps[4], const GemmArgs& args, int grid, cu
         TFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
         attr_set[dev] = true;
     }
-    kern<<<grid, gemm_threads(KIND), S::TOTAL, stream>>>(maps[0], maps[1], maps[2], maps[3], args);
-    TFB_CUDA_OK(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(PAIR ? 2 * workers : workers));
+    cfg.blockDim = dim3((unsigned)gemm_threads(KIND));
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TFB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], args));
     return TFB_OK;
 }
 
-template <int KIND, int BN, int STAGES>
-int launch_layout(bool a_mn, bool b_mn, const CUtensorMap maps[4], const GemmArgs& args, int grid,
+template <int KIND, int BN, int STAGES, bool PAIR>
+int launch_layout(bool a_mn, bool b_mn, const CUtensorMap maps[5], const GemmArgs& args, int workers,
                   cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, false, false>(maps, args, grid, stream);
-    if (!a_mn && b_mn) return launch_variant<KIND, BN, STAGES, false, true>(maps, args, grid, stream);
-    if (a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, true, false>(maps, args, grid, stream);
-    return launch_variant<KIND, BN, STAGES, true, true>(maps, args, grid, stream);
+    if (!a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, false, false, PAIR>(maps, args, workers, stream);
+    if (!a_mn && b_mn) return launch_variant<KIND, BN, STAGES, false, true, PAIR>(maps, args, workers, stream);
+    if (a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, true, false, PAIR>(maps, args, workers, stream);
+    return launch_variant<KIND, BN, STAGES, true, true, PAIR>(maps, args, workers, stream);
 }
 
 int choose_bn(int64_t M, int64_t N, int sm_count) {
@@ -354,7 +367,14 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     int env_bn = 0, env_chunk = 0;
     if (const char* e = getenv("TFB_GEMM_BN")) env_bn = atoi(e);
     if (const char* e = getenv("TFB_GEMM_CHUNK_KB")) env_chunk = atoi(e);
-    const int bn = c.force_bn ? c.force_bn : (env_bn ? env_bn : choose_bn(c.M, c.N, st->sm_count));
+    int env_pair = -1;
+    if (const char* e = getenv("TFB_GEMM_PAIR")) env_pair = atoi(e);
+    // CTA pairs pay off once there are enough 256 x 256 tiles to occupy about half of the SM pairs
+    // (measured: faster from 2048^3 up, slower at 1024^3).
+    const long long pair_tiles = ((c.M + 255) / 256) * ((c.N + 255) / 256);
+    const bool use_pair = c.K > 0 && !c.force_bn && !env_bn &&
+                          (env_pair >= 0 ? env_pair != 0 : pair_tiles >= (st->sm_count / 4));
+    const int bn = use_pair ? 256 : (c.force_bn ? c.force_bn : (env_bn ? env_bn : choose_bn(c.M, c.N, st->sm_count)));
     if (bn != 64 && bn != 128 && bn != 256) return fail(TFB_ERR_INVALID_ARG, "gemm: tile N %d", bn);
     const int bk = 128 / es;
     const int t_mn = 128 / es;
@@ -362,7 +382,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     GemmArgs args;
     memset(&args, 0, sizeof(args));
     args.M = (int)c.M; args.N = (int)c.N; args.K = (int)c.K;
-    args.tiles_m = (int)((c.M + kBlockM - 1) / kBlockM);
+    args.tiles_m = use_pair ? (int)((c.M + 2 * kBlockM - 1) / (2 * kBlockM)) : (int)((c.M + kBlockM - 1) / kBlockM);
     args.tiles_n = (int)((c.N + bn - 1) / bn);
     args.num_tiles = args.tiles_m * args.tiles_n;
     args.k_blocks = (int)((c.K + bk - 1) / bk);
@@ -384,7 +404,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
         return TFB_OK;
     }
 
-    CUtensorMap maps[4];
+    CUtensorMap maps[5];
     memset(maps, 0, sizeof(maps));
     const int nplanes = f32 ? 2 : 1;
     for (int p = 0; p < nplanes; ++p) {
@@ -394,23 +414,39 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
             rc = make_map(&maps[p], c.in_dtype, a_ptr[p], (uint64_t)c.M, (uint64_t)c.K, (uint64_t)lda * es, t_mn, bk, f32);
         if (rc != TFB_OK) return rc;
         if (c.b_kmajor)
-            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.K, (uint64_t)c.N, (uint64_t)ldb * es, bk, bn);
+            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.K, (uint64_t)c.N, (uint64_t)ldb * es, bk,
+                          use_pair ? bn / 2 : bn);
         else
             rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.N, (uint64_t)c.K, (uint64_t)ldb * es, t_mn, bk, f32);
         if (rc != TFB_OK) return rc;
     }
     if (!f32) { maps[1] = maps[0]; maps[3] = maps[2]; }
+    // FP32 output with 16-byte aligned rows leaves through TMA stores of 32 x 32 blocks.
+    args.c_tma = (c.out_dtype == TFB_DTYPE_F32 && aligned16(c.C) && (c.ldc & 3) == 0) ? 1 : 0;
+    if (args.c_tma) {
+        rc = make_map(&maps[4], TFB_DTYPE_F32, c.C, (uint64_t)c.N, (uint64_t)c.M, (uint64_t)c.ldc * 4, 32, 32);
+        if (rc != TFB_OK) return rc;
+    } else {
+        maps[4] = maps[0];
+    }
 
     const int grid = args.num_tiles < st->sm_count ? args.num_tiles : st->sm_count;
     const bool a_mn = !c.a_kmajor, b_mn = !c.b_kmajor;
-    if (f32) {
-        if (bn == 256) return launch_layout<kKindTF32x3, 256, 2>(a_mn, b_mn, maps, args, grid, stream);
-        if (bn == 128) return launch_layout<kKindTF32x3, 128, 3>(a_mn, b_mn, maps, args, grid, stream);
-        return launch_layout<kKindTF32x3, 64, 4>(a_mn, b_mn, maps, args, grid, stream);
+    if (use_pair) {
+        args.group_m = 8;   // 8 pair tiles = 2048 rows, the same raster width as the single-CTA kernel
+        const int max_pairs = st->sm_count / 2;
+        const int pairs = args.num_tiles < max_pairs ? args.num_tiles : max_pairs;
+        if (f32) return launch_layout<kKindTF32x3, 256, 3, true>(a_mn, b_mn, maps, args, pairs, stream);
+        return launch_layout<kKind16, 256, 6, true>(a_mn, b_mn, maps, args, pairs, stream);
     }
-    if (bn == 256) return launch_layout<kKind16, 256, 4>(a_mn, b_mn, maps, args, grid, stream);
-    if (bn == 128) return launch_layout<kKind16, 128, 6>(a_mn, b_mn, maps, args, grid, stream);
-    return launch_layout<kKind16, 64, 8>(a_mn, b_mn, maps, args, grid, stream);
+    if (f32) {
+        if (bn == 256) return launch_layout<kKindTF32x3, 256, 2, false>(a_mn, b_mn, maps, args, grid, stream);
+        if (bn == 128) return launch_layout<kKindTF32x3, 128, 3, false>(a_mn, b_mn, maps, args, grid, stream);
+        return launch_layout<kKindTF32x3, 64, 4, false>(a_mn, b_mn, maps, args, grid, stream);
+    }
+    if (bn == 256) return launch_layout<kKind16, 256, 4, false>(a_mn, b_mn, maps, args, grid, stream);
+    if (bn == 128) return launch_layout<kKind16, 128, 6, false>(a_mn, b_mn, maps, args, grid, stream);
+    return launch_layout<kKind16, 64, 8, false>(a_mn, b_mn, maps, args, grid, stream);
 }
 
 }  // namespace tfb

@@ -2,17 +2,19 @@
 //
 //   D[M,N] (+bias, ReLU) = A · B      with FP32 accumulation in tensor memory.
 //
-// Roles inside one CTA (192 threads):
+// Roles inside one CTA (192 threads; 320 on the FP32 path):
 //   warp 0      TMA producer: fills a ring of shared-memory stages with 128-byte-swizzled
 //               operand tiles and signals `full[s]` by transaction bytes.
 //   warp 1      MMA issuer: one lane issues tcgen05.mma per 32-byte K step, releases a
 //               stage with tcgen05.commit -> `empty[s]`, and hands a finished accumulator
 //               to the epilogue with tcgen05.commit -> `tmem_full[b]`.  Also owns the
 //               TMEM allocation.
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its own 32 TMEM lanes),
+//   warps 2+    epilogue: tcgen05.ld the accumulator (each warp its own 32 TMEM lanes),
 //               apply bias / ReLU, convert and store, then release the accumulator with
 //               `tmem_empty[b]`.  Two accumulators let the epilogue of tile i overlap the
-//               main loop of tile i+1.
+//               main loop of tile i+1.  FP32 output leaves through a swizzled staging
+//               buffer and a TMA store per 32x32 block (whole 128-byte lines, clipped at
+//               the matrix edge by the tensor map); other cases store from registers.
 //
 // Operand layouts.  "K-major": the contraction index is contiguous in memory (A[M,K]
 // row-major, B given as [N,K] row-major).  "MN-major": the M (resp. N) index is
@@ -20,7 +22,7 @@
 // tensor core straight from the TMA tiles through the matching shared-memory
 // descriptor, so transposed products need no transpose copy.
 //
-// kTF32x3: every FP32 operand arrives pre-split as hi + lo (hi = x rounded to TF32,
+// kKindTF32x3: every FP32 operand arrives pre-split as hi + lo (hi = x rounded to TF32,
 // lo = x - hi).  Each K step issues lo·hi, hi·lo and hi·hi into the same FP32
 // accumulator, which restores FP32-level accuracy from TF32 tensor-core products.
 // The tensor core adds into its accumulator with truncation, an error that grows linearly
@@ -28,6 +30,22 @@
 // accumulator every `chunk_kb` K blocks and the (eight) epilogue warps sum those chunk
 // results in registers with round-to-nearest adds, which keeps the result within FP32
 // rounding noise of a sequential FP32 dot product for any K.
+//
+// PAIR = true: two CTAs of a cluster — a CTA pair on two SMs — compute one 256 x BN tile
+// with tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and only HALF of
+// the B tile (BN/2 rows); the tensor cores of both SMs read both halves, and each CTA's
+// TMEM receives the accumulator of its own 128 rows.  Per FLOP this halves the B bytes
+// that travel L2 -> shared memory.  Rank 0 of the pair is the leader; only its MMA lane
+// issues.
+//   full[s]       lives in the leader, which announces the bytes of both CTAs (one
+//                 arrive.expect_tx); both CTAs' TMA loads signal the leader's barrier.
+//                 (A per-stage remote arrive with cluster-scope release from the peer's
+//                 producer halved BF16 throughput and was dropped.)
+//   empty[s]      one copy per CTA; the leader's commit arrives on both copies.
+//   tmem_full[b]  one copy per CTA; the leader's commit arrives on both.
+//   tmem_empty[b] lives in the leader; the epilogue threads of both CTAs arrive remotely.
+// Cluster barriers bracket the kernel so that no CTA touches its peer's barriers before
+// they are initialised or leaves while its peer may still read its shared memory.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -54,28 +72,34 @@ struct GemmArgs {
     int bias_mode;        // BiasMode
     int relu;
     int is_bf16;          // kKind16 only: 1 = bf16 operands, 0 = f16
+    int c_tma;            // 1: FP32 output goes through the TMA-store path (tmC is valid)
     int* status;          // device error word (0 = ok)
 };
 
 constexpr int kBlockM = 128;
 // Two control warps (TMA, MMA) plus four epilogue warps, eight on the FP32 path.
 __host__ __device__ constexpr int gemm_threads(int kind) { return kind == kKindTF32x3 ? 320 : 192; }
+__host__ __device__ constexpr int gemm_epi_warps(int kind) { return kind == kKindTF32x3 ? 8 : 4; }
 
-template <int KIND, int BN, int STAGES>
+template <int KIND, int BN, int STAGES, bool PAIR>
 struct GemmSmem {
     static constexpr int ES = (KIND == kKindTF32x3) ? 4 : 2;   // operand element bytes
     static constexpr int NSPLIT = (KIND == kKindTF32x3) ? 2 : 1;
     static constexpr int BK = 128 / ES;                         // K elements per stage
+    static constexpr int BN_CTA = PAIR ? BN / 2 : BN;           // B rows staged by one CTA
     static constexpr int A_TILE = kBlockM * 128;                // bytes
-    static constexpr int B_TILE = BN * 128;
+    static constexpr int B_TILE = BN_CTA * 128;
     static constexpr int STAGE_BYTES = NSPLIT * (A_TILE + B_TILE);
+    // Epilogue staging: 32 rows x 128 B per buffer; two buffers per warp with four epilogue
+    // warps, one with eight, 32 KB either way.
+    static constexpr int STAGING_BUFS = (KIND == kKindTF32x3) ? 1 : 2;
+    static constexpr int STAGING_BYTES = gemm_epi_warps(KIND) * STAGING_BUFS * 4096;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int TOTAL = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int TOTAL = 1024 + STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES;
 };
 
-// Bias, ReLU, conversion and store of 32 consecutive output columns of one row.
-__device__ __forceinline__ void epilogue_store32(float (&v)[32], const GemmArgs& args, int row, int col0,
-                                                 float row_bias) {
+// Bias and ReLU on 32 consecutive output columns of one row.
+__device__ __forceinline__ void epilogue_apply32(float (&v)[32], const GemmArgs& args, int col0, float row_bias) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] += row_bias;
     if (args.bias_mode == kBiasPerCol) {
@@ -87,6 +111,10 @@ __device__ __forceinline__ void epilogue_store32(float (&v)[32], const GemmArgs&
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = v[i] > 0.f ? v[i] : 0.f;
     }
+}
+
+// Conversion and store of 32 consecutive output columns of one row straight from registers.
+__device__ __forceinline__ void epilogue_store32(const float (&v)[32], const GemmArgs& args, int row, int col0) {
     const bool full = (col0 + 32 <= args.N);
     if (args.out_type == kOutF32) {
         float* dst = static_cast<float*>(args.C) + (long long)row * args.ldc + col0;
@@ -128,6 +156,30 @@ __device__ __forceinline__ void epilogue_store32(float (&v)[32], const GemmArgs&
     }
 }
 
+// One warp's 32 rows x 32 FP32 columns through shared memory: lane r writes its row into a
+// 128-byte-swizzled 4 KB buffer (16-byte chunk j of row r at chunk j ^ (r & 7): conflict-free),
+// then one lane hands the block to the TMA store engine. Rows and columns beyond the matrix are
+// clipped by the tensor map. Lane 0 owns the bulk groups, so it also does the waiting.
+template <int NBUF>
+__device__ __forceinline__ void epilogue_store32_tma(const float (&v)[32], const CUtensorMap* tmC, uint8_t* staging,
+                                                     int& buf_idx, int lane, int row0, int col0) {
+    uint8_t* buf = staging + buf_idx * 4096;
+    // The buffer about to be overwritten must have been read by its previous store.
+    if (lane == 0) tma_store_wait_read<NBUF - 1>();
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(tmC, smem_u32(buf), col0, row0);
+        tma_store_commit();
+    }
+    buf_idx = (buf_idx + 1 == NBUF) ? 0 : buf_idx + 1;
+}
+
 __device__ __forceinline__ void tile_coords(int t, const GemmArgs& a, int& tm, int& tn) {
     const int group_sz = a.group_m * a.tiles_n;
     const int g = t / group_sz;
@@ -138,14 +190,25 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& a, int& tm, i
     tn = r / gm;
 }
 
-template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN>
+// One commit whose arrival is delivered to the barrier at the same shared-memory offset in every
+// CTA of `cta_mask` (both CTAs of a pair). A commit is not a copy: no data moves.
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
+template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(gemm_threads(KIND), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
-                    const GemmArgs args) {
-    using S = GemmSmem<KIND, BN, STAGES>;
+                    const __grid_constant__ CUtensorMap tmC, const GemmArgs args) {
+    using S = GemmSmem<KIND, BN, STAGES, PAIR>;
     constexpr int ES = S::ES;
     constexpr int BK = S::BK;
+    constexpr int BN_CTA = S::BN_CTA;
+    constexpr int CG = PAIR ? 2 : 1;
+    constexpr int TILE_M = PAIR ? 2 * kBlockM : kBlockM;   // rows of one scheduled tile
     constexpr bool TF32 = (KIND == kKindTF32x3);
     constexpr int UMMA_K = 32 / ES;          // K elements per tcgen05.mma
     constexpr int KSTEPS = BK / UMMA_K;      // 4
@@ -154,8 +217,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                    : (2 * BN <= 256) ? 256 : 512;
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
     static_assert(!A_MN || (kBlockM % T_MN == 0), "tile M must hold whole swizzle rows");
-    static_assert(!B_MN || (BN % T_MN == 0), "tile N must hold whole swizzle rows");
-    constexpr int EPI_WARPS = TF32 ? 8 : 4;
+    static_assert(!B_MN || (BN_CTA % T_MN == 0), "tile N must hold whole swizzle rows");
+    constexpr int EPI_WARPS = gemm_epi_warps(KIND);
     constexpr int COLS = BN / (EPI_WARPS / 4);   // accumulator columns handled per epilogue thread
     static_assert(COLS % 32 == 0, "each epilogue thread handles whole 32-column groups");
 
@@ -163,18 +226,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    const uint32_t bars = smem_base + STAGES * S::STAGE_BYTES;
+    uint8_t* staging_all = smem_gen + STAGES * S::STAGE_BYTES;
+    const uint32_t bars = smem_base + STAGES * S::STAGE_BYTES + S::STAGING_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
     auto tempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
-    volatile uint32_t* tmem_holder =
-        reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * S::STAGE_BYTES + 8 * (2 * STAGES + 4));
-    volatile int* abort_flag =
-        reinterpret_cast<volatile int*>(smem_gen + STAGES * S::STAGE_BYTES + 8 * (2 * STAGES + 4) + 4);
+    uint8_t* after_bars = smem_gen + STAGES * S::STAGE_BYTES + S::STAGING_BYTES + 8 * (2 * STAGES + 4);
+    volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(after_bars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(after_bars + 4);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // 0 = leader of the pair
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -183,7 +249,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 32 * EPI_WARPS);
+            mbar_init(tempty_bar(b), CG * 32 * EPI_WARPS);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -193,13 +259,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tma_prefetch_desc(&tmA2);
             tma_prefetch_desc(&tmB2);
         }
+        if (args.c_tma) tma_prefetch_desc(&tmC);
     }
     if (warp == 1) {
-        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
-        tmem_relinquish<1>();
+        tmem_alloc<CG>(smem_u32(const_cast<uint32_t*>(tmem_holder)), TMEM_COLS);
+        tmem_relinquish<CG>();
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
 
@@ -211,10 +282,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+            for (int t = worker; t < args.num_tiles && ok; t += num_workers) {
                 int tm, tn;
                 tile_coords(t, args, tm, tn);
-                const int m0 = tm * kBlockM, n0 = tn * BN;
+                const int m0 = tm * TILE_M + (int)rank * kBlockM, n0 = tn * BN + (int)rank * BN_CTA;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
                     if (!ok) break;
@@ -223,29 +294,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const uint32_t a_lo = st + S::A_TILE;
                     const uint32_t b_hi = st + S::NSPLIT * S::A_TILE;
                     const uint32_t b_lo = b_hi + S::B_TILE;
-                    const uint32_t fb = full_bar(s);
-                    mbar_arrive_expect_tx(fb, S::STAGE_BYTES);
+                    // Pair: the leader announces the bytes of both CTAs and every load signals the
+                    // leader's barrier; the peer only issues its loads.
+                    const uint32_t fb = PAIR ? mapa_shared(full_bar(s), 0) : full_bar(s);
+                    if (rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * S::STAGE_BYTES);
                     const int k0 = kb * BK;
+                    auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y) {
+                        if constexpr (PAIR) tma_load_2d_pair(dst, map, x, y, fb);
+                        else tma_load_2d(dst, map, x, y, fb);
+                    };
                     if constexpr (!A_MN) {
-                        tma_load_2d(a_hi, &tmA, k0, m0, fb);
-                        if constexpr (TF32) tma_load_2d(a_lo, &tmA2, k0, m0, fb);
+                        load(a_hi, &tmA, k0, m0);
+                        if constexpr (TF32) load(a_lo, &tmA2, k0, m0);
                     } else {
 #pragma unroll
                         for (int i = 0; i < kBlockM / T_MN; ++i) {
-                            tma_load_2d(a_hi + i * (BK * 128), &tmA, m0 + i * T_MN, k0, fb);
-                            if constexpr (TF32)
-                                tma_load_2d(a_lo + i * (BK * 128), &tmA2, m0 + i * T_MN, k0, fb);
+                            load(a_hi + i * (BK * 128), &tmA, m0 + i * T_MN, k0);
+                            if constexpr (TF32) load(a_lo + i * (BK * 128), &tmA2, m0 + i * T_MN, k0);
                         }
                     }
                     if constexpr (!B_MN) {
-                        tma_load_2d(b_hi, &tmB, k0, n0, fb);
-                        if constexpr (TF32) tma_load_2d(b_lo, &tmB2, k0, n0, fb);
+                        load(b_hi, &tmB, k0, n0);
+                        if constexpr (TF32) load(b_lo, &tmB2, k0, n0);
                     } else {
 #pragma unroll
-                        for (int i = 0; i < BN / T_MN; ++i) {
-                            tma_load_2d(b_hi + i * (BK * 128), &tmB, n0 + i * T_MN, k0, fb);
-                            if constexpr (TF32)
-                                tma_load_2d(b_lo + i * (BK * 128), &tmB2, n0 + i * T_MN, k0, fb);
+                        for (int i = 0; i < BN_CTA / T_MN; ++i) {
+                            load(b_hi + i * (BK * 128), &tmB, n0 + i * T_MN, k0);
+                            if constexpr (TF32) load(b_lo + i * (BK * 128), &tmB2, n0 + i * T_MN, k0);
                         }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
@@ -254,7 +329,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // Drain: every load this thread issued has landed once the stage it targeted
             // was consumed; on the normal path the final __syncthreads implies that. On an
             // aborted run wait (bounded) for the stages still in flight.
-            if (!ok || *abort_flag != 0) {
+            if (rank == 0 && (!ok || *abort_flag != 0)) {
                 for (int i = 0; i < STAGES; ++i) {
                     const uint64_t t0 = global_timer_ns();
                     while (!mbar_try_wait(full_bar(i), 0) && !mbar_try_wait(full_bar(i), 1)) {
@@ -268,9 +343,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             const uint32_t idesc = make_idesc(TF32 ? 2u : (args.is_bf16 ? 1u : 0u),
-                                              A_MN ? 1u : 0u, B_MN ? 1u : 0u, kBlockM, BN);
+                                              A_MN ? 1u : 0u, B_MN ? 1u : 0u, TILE_M, BN);
             // K-major: 128-byte swizzle, 8-row groups 1024 B apart, K step = +32 B inside the row.
             // MN-major, 16-bit: 128-byte swizzle; the 128-byte columns of a tile are one TMA box
             //   (BK*128 B) apart (leading offset), 8-row K groups 1024 B apart.
@@ -287,11 +362,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             constexpr uint32_t B_SWZ = B_MN ? MN_SWZ : 2u;
             constexpr uint32_t A_KSTEP = A_MN ? (uint32_t)(UMMA_K * 128) : 32u;
             constexpr uint32_t B_KSTEP = B_MN ? (uint32_t)(UMMA_K * 128) : 32u;
+            auto commit = [&](uint32_t bar) {
+                if constexpr (PAIR) umma_commit_pair_both(bar, (uint16_t)3);
+                else umma_commit<1>(bar);
+            };
             int s = 0;
             uint32_t ph = 0;
             uint32_t cit = 0;   // accumulator hand-offs so far (chunks, over all tiles)
             bool ok = true;
-            for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+            for (int t = worker; t < args.num_tiles && ok; t += num_workers) {
                 for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += args.chunk_kb, ++cit) {
                     const uint32_t buf = cit & 1u;
                     const uint32_t use = cit >> 1;
@@ -318,18 +397,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             if constexpr (TF32) {
                                 const uint64_t dal = make_smem_desc(a_lo + j * A_KSTEP, A_LBO, A_SBO, A_SWZ);
                                 const uint64_t dbl = make_smem_desc(b_lo + j * B_KSTEP, B_LBO, B_SBO, B_SWZ);
-                                umma_ss<1, true>(d_tmem, dal, db, idesc, acc);
-                                umma_ss<1, true>(d_tmem, da, dbl, idesc, 1u);
-                                umma_ss<1, true>(d_tmem, da, db, idesc, 1u);
+                                umma_ss<CG, true>(d_tmem, dal, db, idesc, acc);
+                                umma_ss<CG, true>(d_tmem, da, dbl, idesc, 1u);
+                                umma_ss<CG, true>(d_tmem, da, db, idesc, 1u);
                             } else {
-                                umma_ss<1, false>(d_tmem, da, db, idesc, acc);
+                                umma_ss<CG, false>(d_tmem, da, db, idesc, acc);
                             }
                         }
-                        umma_commit<1>(empty_bar(s));
+                        commit(empty_bar(s));
                         if (++s == STAGES) { s = 0; ph ^= 1u; }
                     }
                     if (!ok) break;
-                    umma_commit<1>(tfull_bar(buf));
+                    commit(tfull_bar(buf));
                 }
             }
         }
@@ -338,13 +417,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int ew = warp - 2;
         const int q = warp & 3;            // TMEM lanes [32q, 32q+32) are the ones this warp may read
         const int cbase = (ew >> 2) * COLS; // first accumulator column of this warp
+        uint8_t* staging = staging_all + ew * S::STAGING_BUFS * 4096;
+        int stage_buf = 0;
+        const bool c_tma = args.c_tma != 0;
+        auto release = [&](uint32_t buf) {
+            tc_fence_before_sync();
+            if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(tempty_bar(buf), 0));
+            else mbar_arrive(tempty_bar(buf));
+        };
         uint32_t cit = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
+        for (int t = worker; t < args.num_tiles && ok; t += num_workers) {
             int tm, tn;
             tile_coords(t, args, tm, tn);
-            const int m0 = tm * kBlockM, n0 = tn * BN + cbase;
-            const int row = m0 + q * 32 + lane;
+            const int m0 = tm * TILE_M + (int)rank * kBlockM, n0 = tn * BN + cbase;
+            const int row0 = m0 + q * 32;
+            const int row = row0 + lane;
             const bool row_ok = row < args.M;
             float row_bias = 0.f;
             if (args.bias_mode == kBiasPerRow && row_ok) row_bias = __ldg(args.bias + row);
@@ -371,19 +459,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
                         }
                     }
-                    tc_fence_before_sync();
-                    mbar_arrive(tempty_bar(buf));
+                    release(buf);
                 }
                 if (!ok) break;
-                if (row_ok) {
 #pragma unroll
-                    for (int c = 0; c < COLS / 32; ++c) {
-                        if (n0 + c * 32 < args.N) {
-                            float v[32];
+                for (int c = 0; c < COLS / 32; ++c) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 < args.N && (c_tma ? row0 < args.M : row_ok)) {
+                        float v[32];
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
-                            epilogue_store32(v, args, row, n0 + c * 32, row_bias);
-                        }
+                        for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
+                        epilogue_apply32(v, args, col0, row_bias);
+                        if (c_tma) epilogue_store32_tma<S::STAGING_BUFS>(v, &tmC, staging, stage_buf, lane, row0, col0);
+                        else epilogue_store32(v, args, row, col0);
                     }
                 }
             } else {
@@ -401,23 +489,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     uint32_t r[32];
                     tmem_ld_32x32(lane_addr + buf * (uint32_t)BN + (uint32_t)(c * 32), r);
                     tmem_ld_wait();
-                    if (!row_ok) continue;
+                    if (!(c_tma ? row0 < args.M : row_ok)) continue;   // warp-uniform on the TMA path
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                    epilogue_store32(v, args, row, col0, row_bias);
+                    epilogue_apply32(v, args, col0, row_bias);
+                    if (c_tma) epilogue_store32_tma<S::STAGING_BUFS>(v, &tmC, staging, stage_buf, lane, row0, col0);
+                    else epilogue_store32(v, args, row, col0);
                 }
-                tc_fence_before_sync();
-                mbar_arrive(tempty_bar(buf));
+                release(buf);
             }
         }
+        // The staging buffers must outlive the TMA engine's reads, and the stores must be complete
+        // before the grid is.
+        if (c_tma && lane == 0) tma_store_wait_all<0>();
     }
 
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) {
+        cluster_arrive();
+        cluster_wait();
+    }
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        tmem_dealloc<CG>(tmem_base, TMEM_COLS);
     }
 }
 
