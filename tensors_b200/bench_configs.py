@@ -88,11 +88,16 @@ def config2(iters):
          hbm_frac=bwd_bytes / ub / 1e3 / HBM_GBS, mflop=51.38)
 
 
+CONV_N, CONV_LAYERS, CONV_PASSES = 128, ("1", "2"), ("forward", "dgrad", "wgrad+dbias")
+
+
 def config3(iters):
-    N = 128
+    N = CONV_N
     x = dev(refdata.normal(31, (N, 3, 32, 32)))
-    for name, cin, cout, xin, alg_bytes, gflop in (("layer1 3->64", 3, 64, x, 35.1e6, 0.45298),
-                                                   ("layer2 64->128", 64, 128, None, 101.0e6, 19.33)):
+    for name, cin, cout, xin, alg_bytes, gflop in (("layer1 3->64", 3, 64, x, 35.1e6 * N / 128, 0.45298 * N / 128),
+                                                   ("layer2 64->128", 64, 128, None, 101.0e6 * N / 128, 19.33 * N / 128)):
+        if name[5] not in CONV_LAYERS:
+            continue
         if xin is None:
             xin = dev(refdata.normal(32, (N, cin, 32, 32)))
         w = dev(refdata.conv_weight(cin, cout, 3))
@@ -105,8 +110,10 @@ def config3(iters):
         dgr = lambda: capi.check(lib.tfb_conv2d_backward(p(xin), p(w), p(g), p(gi), None, None, *args, 0, stream()))
         wgr = lambda: capi.check(lib.tfb_conv2d_backward(p(xin), p(w), p(g), None, p(gw), p(gb), *args, 0, stream()))
         for what, fn in (("forward", fwd), ("dgrad", dgr), ("wgrad+dbias", wgr)):
+            if what not in CONV_PASSES:
+                continue
             us = time_us(fn, iters)
-            emit(config=3, what=f"Conv2d {name} {what}, N=128 32x32 3x3 p1", us=us, tflops=gflop / us * 1e3,
+            emit(config=3, what=f"Conv2d {name} {what}, N={N} 32x32 3x3 p1", us=us, tflops=gflop / us * 1e3,
                  gbs=alg_bytes / us / 1e3)
 
 
@@ -138,16 +145,18 @@ def config5(iters):
     labels = torch.from_numpy(refdata.labels(8, batch)[b:e]).cuda()
     m = MLP(dims, ws)
     step = lambda: m.train_step(X, labels, lr=0.1, momentum=0.9, global_rows=batch)
-    us = time_us(step, iters)
+    us_eager = time_us(step, iters)
     fb = time_us(lambda: m.forward_backward(X, labels, batch), iters)
+    replay = m.capture_train_step(X, labels, lr=0.1, momentum=0.9, global_rows=batch)
+    us = time_us(replay, iters)
     ar = time_us(m.allreduce_grads, iters) if world > 1 else 0.0
     if world > 1:
-        t = torch.tensor([us, fb, ar], device="cuda", dtype=torch.float64)
+        t = torch.tensor([us, fb, ar, us_eager], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us, fb, ar = [float(v) for v in t.tolist()]
+        us, fb, ar, us_eager = [float(v) for v in t.tolist()]
     if rank == 0:
-        emit(config=5, what=f"MLP 784-1024-1024-10 step, global batch 8192 on {world} GPU(s)", us=us,
-             forward_backward_us=fb, allreduce_us=ar, tflops=78.35e9 / us / 1e6, loss=float(m.loss.item()))
+        emit(config=5, what=f"MLP 784-1024-1024-10 step (CUDA graph replay), global batch 8192 on {world} GPU(s)", us=us,
+             eager_us=us_eager, forward_backward_us=fb, allreduce_us=ar, tflops=78.35e9 / us / 1e6, loss=float(m.loss.item()))
     if world > 1:
         dist.destroy_process_group()
 
@@ -156,7 +165,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="1,2,3,4,5")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--conv-n", type=int, default=128, help="config 3: batch size")
+    ap.add_argument("--conv-layers", default="1,2", help="config 3: which layers")
+    ap.add_argument("--conv-passes", default="forward,dgrad,wgrad+dbias", help="config 3: which passes")
     a = ap.parse_args()
+    global CONV_N, CONV_LAYERS, CONV_PASSES
+    CONV_N, CONV_LAYERS, CONV_PASSES = a.conv_n, tuple(a.conv_layers.split(",")), tuple(a.conv_passes.split(","))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     capi.check(lib.tfb_init())
     for c in a.configs.split(","):

@@ -71,7 +71,15 @@ __global__ void index_map_kernel(long long* __restrict__ out, const TapInfo* __r
         const int t = (int)(rem / args.pos_count);
         const int p = (int)(rem - (long long)t * args.pos_count);
         const int oy = p / args.pos_W, ox = p - oy * args.pos_W;
-        const int off = conv_src_offset<kConvFprop>(table[t], oy * args.mul_h, ox * args.mul_w, args);
+        const int y0 = oy * args.mul_h, x0 = ox * args.mul_w;
+        int off;
+        if (args.kH <= 32 && args.kW <= 32) {   // what the forward producers evaluate
+            const uint32_t ymask = conv_axis_mask(y0, args.ay0, args.ay_step, args.kH, args.src_H);
+            const uint32_t xmask = conv_axis_mask(x0, args.ax0, args.ax_step, args.kW, args.src_W);
+            off = conv_src_offset_fast(table[t], y0 * args.src_W + x0, ymask, xmask);
+        } else {
+            off = conv_src_offset<kConvFprop>(table[t], y0, x0, args);
+        }
         out[i] = off >= 0 ? (n0 + n) * sample_elems + off : -1;
     }
 }
@@ -125,18 +133,21 @@ int check_shape(const ConvShape& s) {
 
 // Tap table for gathers from a tensor with `planes` channels of plane_elems elements each:
 // forward form (ay = ki*d - pad) or gradient form (ay = pad - ki*d).
-std::vector<TapInfo> build_taps(int64_t planes, int64_t plane_elems, const ConvShape& s, bool gradient_form,
-                                bool ones_tap, int64_t table_len) {
+std::vector<TapInfo> build_taps(int64_t planes, int64_t plane_elems, int64_t src_W, const ConvShape& s,
+                                bool gradient_form, bool ones_tap, int64_t table_len) {
     std::vector<TapInfo> t((size_t)table_len);
     const int64_t khw = s.kH * s.kW;
     for (int64_t i = 0; i < table_len; ++i) {
         TapInfo ti;
-        ti.pad = 0;
+        ti.delta = 0;
+        ti.kidx = 0;
         if (i < planes * khw) {
             const int64_t ch = i / khw, r = i - ch * khw, ki = r / s.kW, kj = r - ki * s.kW;
             ti.plane_off = (int)(ch * plane_elems);
-            ti.ay = (int)(gradient_form ? s.ph - ki * s.dh : ki * s.dh - s.ph);
-            ti.ax = (int)(gradient_form ? s.pw - kj * s.dw : kj * s.dw - s.pw);
+            ti.ay = (short)(gradient_form ? s.ph - ki * s.dh : ki * s.dh - s.ph);
+            ti.ax = (short)(gradient_form ? s.pw - kj * s.dw : kj * s.dw - s.pw);
+            ti.delta = (int)(ti.plane_off + (int64_t)ti.ay * src_W + ti.ax);
+            ti.kidx = (int)(ki | (kj << 8));
         } else {
             ti.plane_off = (ones_tap && i == planes * khw) ? -2 : -1;
             ti.ay = ti.ax = 0;
@@ -151,6 +162,9 @@ void fill_forward_geometry(ConvArgs& a, const ConvShape& s, const float* x) {
     a.src_sample = s.Cin * s.H * s.W;
     a.src_H = (int)s.H; a.src_W = (int)s.W;
     a.div_h = a.div_w = 1;
+    a.kH = (int)s.kH; a.kW = (int)s.kW;
+    a.ay0 = (int)-s.ph; a.ay_step = (int)s.dh;
+    a.ax0 = (int)-s.pw; a.ax_step = (int)s.dw;
     a.mul_h = (int)s.sh; a.mul_w = (int)s.sw;
     a.pos_W = (int)s.outW;
     a.pos_count = (int)(s.outH * s.outW);
@@ -178,7 +192,7 @@ int conv2d_forward(const float* x, const float* w, const float* bias, float* out
     float* w_hi = reinterpret_cast<float*>(ws);
     float* w_lo = w_hi + s.Cout * ldw;
     TapInfo* table_d = reinterpret_cast<TapInfo*>(ws + w_bytes);
-    const std::vector<TapInfo> table = build_taps(s.Cin, s.H * s.W, s, false, false, table_len);
+    const std::vector<TapInfo> table = build_taps(s.Cin, s.H * s.W, s.W, s, false, false, table_len);
     TFB_CUDA_OK(cudaMemcpyAsync(table_d, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
     rc = split_operand(w, s.Cout, taps, taps, nullptr, w_hi, w_lo, ldw, stream);
     if (rc != TFB_OK) return rc;
@@ -247,7 +261,7 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
 
     if (want_dx) {
         TapInfo* table_d = reinterpret_cast<TapInfo*>(ws + o_dtab);
-        const std::vector<TapInfo> table = build_taps(s.Cout, P, s, true, false, d_table);
+        const std::vector<TapInfo> table = build_taps(s.Cout, P, s.outW, s, true, false, d_table);
         TFB_CUDA_OK(cudaMemcpyAsync(table_d, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
         float* wd_hi = reinterpret_cast<float*>(ws + o_wd);
         float* wd_lo = wd_hi + s.Cin * d_ld;
@@ -261,6 +275,9 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
         a.src_sample = s.Cout * P;
         a.src_H = (int)s.outH; a.src_W = (int)s.outW;
         a.div_h = (int)s.sh; a.div_w = (int)s.sw;
+        a.kH = (int)s.kH; a.kW = (int)s.kW;
+        a.ay0 = (int)s.ph; a.ay_step = (int)-s.dh;
+        a.ax0 = (int)s.pw; a.ax_step = (int)-s.dw;
         a.mul_h = a.mul_w = 1;
         a.pos_W = (int)s.W; a.pos_count = (int)(s.H * s.W);
         a.n_samples = (int)s.N;
@@ -284,7 +301,7 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
     }
     if (want_w) {
         TapInfo* table_d = reinterpret_cast<TapInfo*>(ws + o_wtab);
-        const std::vector<TapInfo> table = build_taps(s.Cin, s.H * s.W, s, false, true, w_table);
+        const std::vector<TapInfo> table = build_taps(s.Cin, s.H * s.W, s.W, s, false, true, w_table);
         TFB_CUDA_OK(cudaMemcpyAsync(table_d, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
         float* dy_hi = reinterpret_cast<float*>(ws + o_dy);
         float* dy_lo = dy_hi + s.N * s.Cout * ldp;
@@ -387,7 +404,7 @@ int tfb_im2col_index_map(int64_t* out, int64_t n_first, int64_t n_count, int64_t
     void* ws = nullptr;
     rc = workspace_get(stream, (size_t)table_len * sizeof(TapInfo), &ws);
     if (rc != TFB_OK) return rc;
-    const std::vector<TapInfo> table = build_taps(Cin, H * W, s, false, false, table_len);
+    const std::vector<TapInfo> table = build_taps(Cin, H * W, W, s, false, false, table_len);
     TFB_CUDA_OK(cudaMemcpyAsync(ws, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
     ConvArgs a;
     memset(&a, 0, sizeof(a));

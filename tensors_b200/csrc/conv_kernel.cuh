@@ -32,11 +32,12 @@ enum ConvMode : int { kConvFprop = 0, kConvDgrad = 1, kConvWgrad = 2 };
 
 // Where tap t reads relative to a position: plane offset inside one sample and the two
 // coordinate offsets. plane_off < 0 marks taps that do not exist (-1) or the all-ones tap (-2).
+// `delta` = plane_off + ay * src_W + ax and `kidx` = ki | kj << 8 serve the separable fast path.
 struct TapInfo {
     int plane_off;
-    int ay;
-    int ax;
-    int pad;
+    short ay, ax;
+    int delta;
+    int kidx;
 };
 
 struct ConvArgs {
@@ -44,6 +45,8 @@ struct ConvArgs {
     long long src_sample;      // elements per sample of src
     int src_H, src_W;          // plane extents of src
     int div_h, div_w;          // dgrad with stride > 1: coordinates must divide by these (else 1)
+    int kH, kW;                // filter extents
+    int ay0, ay_step, ax0, ax_step;   // tap (ki, kj) reads at y0 + ay0 + ki*ay_step, x0 + ax0 + kj*ax_step
     int mul_h, mul_w;          // position -> coordinate scale (stride for fprop / wgrad, 1 for dgrad)
     int pos_W, pos_count;      // width of the position grid and positions per sample
     int n_samples;
@@ -96,6 +99,23 @@ __device__ __forceinline__ int conv_src_offset(const TapInfo& ti, int y0, int x0
     }
     if ((unsigned)u >= (unsigned)args.src_H || (unsigned)v >= (unsigned)args.src_W) return -1;
     return ti.plane_off + u * args.src_W + v;
+}
+
+// Separable form of the same map, valid whenever no stride division is involved (fprop, wgrad, and
+// dgrad with stride 1): row validity depends only on (y0, ki) and column validity only on (x0, kj),
+// so a thread keeps one bit mask per axis and its own base offset y0 * src_W + x0; a tap then costs
+// one add (`delta`) and two bit tests. Kernels up to 32 x 32.
+__device__ __forceinline__ uint32_t conv_axis_mask(int c0, int a0, int a_step, int taps, int extent) {
+    uint32_t m = 0;
+    for (int k = 0; k < taps; ++k) {
+        const int u = c0 + a0 + k * a_step;
+        if ((unsigned)u < (unsigned)extent) m |= 1u << k;
+    }
+    return m;
+}
+__device__ __forceinline__ int conv_src_offset_fast(const TapInfo& ti, int thread_off, uint32_t ymask, uint32_t xmask) {
+    const uint32_t ok = (ymask >> (ti.kidx & 0xff)) & (xmask >> ((ti.kidx >> 8) & 0xff)) & 1u;
+    return ok ? thread_off + ti.delta : -1;
 }
 
 template <int MODE, int BN, int STAGES>
@@ -280,51 +300,75 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
             decode_tile(t, rt, ct, outer);
             k_range(outer, kb0, kb1);
             // fprop / dgrad: this thread's position is fixed for the tile.
-            int pos = 0, y0 = 0, x0 = 0;
+            int pos = 0, y0 = 0, x0 = 0, thread_off = 0;
+            uint32_t ymask = 0, xmask = 0;
             bool pos_ok = false;
             const float* base = args.src;
-            if constexpr (!WGRAD) {
-                pos = rt * 128 + pw * 32 + lane;
+            const bool fast = (args.div_h == 1 && args.div_w == 1 && args.kH <= 32 && args.kW <= 32);
+            auto locate = [&]() {
                 pos_ok = pos < args.pos_count;
                 const int oy = pos / args.pos_W, ox = pos - oy * args.pos_W;
                 y0 = oy * args.mul_h;
                 x0 = ox * args.mul_w;
+                thread_off = y0 * args.src_W + x0;
+                if (fast) {
+                    ymask = pos_ok ? conv_axis_mask(y0, args.ay0, args.ay_step, args.kH, args.src_H) : 0u;
+                    xmask = pos_ok ? conv_axis_mask(x0, args.ax0, args.ax_step, args.kW, args.src_W) : 0u;
+                }
+            };
+            if constexpr (!WGRAD) {
+                pos = rt * 128 + pw * 32 + lane;
+                locate();
                 base = args.src + (long long)outer * args.src_sample;
             }
-            for (int kb = kb0; kb < kb1; ++kb) {
-                ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                uint8_t* a_hi = smem_gen + s * S::STAGE_BYTES;
-                uint8_t* a_lo = a_hi + S::A_TILE;
+            // gather(kb, v): issue this thread's 32 loads of K block kb into registers, all in flight
+            // together and before the wait for a free stage, so their latencies overlap.
+            auto gather = [&](int kb, float (&v)[32]) {
                 int tap0;
-                uint32_t off0;   // byte offset of (tap index i = 0) for this thread, before swizzling
                 if constexpr (WGRAD) {
                     const int n = kb / args.pos_blocks, pb = kb - n * args.pos_blocks;
                     pos = pb * 32 + lane;
-                    pos_ok = pos < args.pos_count;
-                    const int oy = pos / args.pos_W, ox = pos - oy * args.pos_W;
-                    y0 = oy * args.mul_h;
-                    x0 = ox * args.mul_w;
+                    locate();
                     base = args.src + (long long)n * args.src_sample;
                     tap0 = rt * 128 + pw * 32;   // rows (taps) pw*32 .. +31 of the tile
-                    off0 = 0;
                 } else {
                     tap0 = kb * 32;              // K index = tap; this warp owns rows pw*32 .. +31
-                    off0 = (uint32_t)pw * 4096u + (uint32_t)(lane & 7) * 4u;
                 }
-#pragma unroll 4
-                for (int i = 0; i < 32; ++i) {
-                    const TapInfo ti = taps_sm[tap0 + i];
-                    float val = 0.f;
-                    if (ti.plane_off >= 0) {
-                        const int off = pos_ok ? conv_src_offset<MODE>(ti, y0, x0, args) : -1;
-                        if (off >= 0) val = __ldg(base + off);
-                    } else if (ti.plane_off == -2) {
-                        val = pos_ok ? 1.f : 0.f;
+                if (fast) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const TapInfo ti = taps_sm[tap0 + i];
+                        const int off = conv_src_offset_fast(ti, thread_off, ymask, xmask);
+                        float val = (ti.plane_off == -2 && pos_ok) ? 1.f : 0.f;
+                        if (ti.plane_off >= 0 && off >= 0) val = __ldg(base + off);
+                        v[i] = val;
                     }
-                    const float hi = tf32_rna_dev(val);
-                    const float lo = val - hi;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {   // fully unrolled so that v[] stays in registers
+                        const TapInfo ti = taps_sm[tap0 + i];
+                        float val = 0.f;
+                        if (ti.plane_off >= 0) {
+                            const int off = pos_ok ? conv_src_offset<MODE>(ti, y0, x0, args) : -1;
+                            if (off >= 0) val = __ldg(base + off);
+                        } else if (ti.plane_off == -2) {
+                            val = pos_ok ? 1.f : 0.f;
+                        }
+                        v[i] = val;
+                    }
+                }
+            };
+            // emit(v): wait for a free stage, split into hi / lo, write the operand tile, signal.
+            auto emit = [&](const float (&v)[32]) -> bool {
+                bool good = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
+                good = __all_sync(0xffffffffu, good);
+                if (!good) return false;
+                uint8_t* a_hi = smem_gen + s * S::STAGE_BYTES;
+                uint8_t* a_lo = a_hi + S::A_TILE;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float hi = tf32_rna_dev(v[i]);
+                    const float lo = v[i] - hi;
                     uint32_t off;
                     if constexpr (WGRAD) {
                         // row m = pw*32 + i, contraction index kk = lane: K-major, 128-byte swizzle
@@ -332,7 +376,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
                         off = m * 128u + ((((uint32_t)lane >> 2) ^ (m & 7u)) << 4) + ((uint32_t)lane & 3u) * 4u;
                     } else {
                         // row = position (lane), contraction index kk = i: MN-major, 32-byte atoms
-                        off = off0 + (uint32_t)i * 128u + ((((uint32_t)lane >> 3) ^ ((uint32_t)i & 3u)) << 5);
+                        off = (uint32_t)pw * 4096u + (uint32_t)(lane & 7) * 4u + (uint32_t)i * 128u +
+                              ((((uint32_t)lane >> 3) ^ ((uint32_t)i & 3u)) << 5);
                     }
                     *reinterpret_cast<float*>(a_hi + off) = hi;
                     *reinterpret_cast<float*>(a_lo + off) = lo;
@@ -340,6 +385,13 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
                 fence_proxy_async_smem();
                 mbar_arrive(full_a(s));
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
+                return true;
+            };
+            // (Issuing the gathers of block kb+1 before writing block kb was tried and measured slower.)
+            float va[32];
+            for (int kb = kb0; kb < kb1 && ok; ++kb) {
+                gather(kb, va);
+                ok = emit(va);
             }
         }
     } else {

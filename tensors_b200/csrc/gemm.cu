@@ -154,6 +154,25 @@ __global__ void empty_k_kernel(const GemmArgs a) {
     }
 }
 
+// C = epilogue(sum over splits, in split order, of the partial products).
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long M, long long N,
+                                     long long ld, long long split_stride, void* __restrict__ C, long long ldc,
+                                     int out_type, const float* __restrict__ bias, int bias_mode, int relu) {
+    const long long total = M * N;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / N, c = i - r * N;
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) v += partial[s * split_stride + r * ld + c];
+        if (bias_mode == kBiasPerCol) v += bias[c];
+        if (bias_mode == kBiasPerRow) v += bias[r];
+        if (relu) v = v > 0.f ? v : 0.f;
+        if (out_type == kOutF32) static_cast<float*>(C)[r * ldc + c] = v;
+        else if (out_type == kOutBF16) static_cast<__nv_bfloat16*>(C)[r * ldc + c] = __float2bfloat16_rn(v);
+        else static_cast<__half*>(C)[r * ldc + c] = __float2half_rn(v);
+    }
+}
+
 int grid_for(long long work_items, int block, int sm_count) {
     long long g = (work_items + block - 1) / block;
     const long long cap = (long long)sm_count * 16;
@@ -246,7 +265,56 @@ int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, cons
     return split_operand_on(st->sm_count, src, rows, cols, ld, mask, hi, lo, ld_out, stream);
 }
 
-size_t gemm_workspace_bytes(const GemmCall& c) {
+// Tile shape, CTA pairing and split-K of one call.
+struct GemmPlan {
+    int bn = 256;
+    bool pair = false;
+    int split_k = 1;
+    int kb_per_split = 0;
+    int k_blocks = 0;
+    int64_t rows_per_split = 0;   // rows of one split's partial output (whole tiles)
+    int64_t ld_partial = 0;       // its leading dimension (multiple of 4)
+    size_t partial_bytes = 0;
+};
+
+GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
+    GemmPlan p;
+    // TFB_GEMM_BN / TFB_GEMM_PAIR / TFB_GEMM_SPLITK: debugging overrides, read on every call.
+    int env_bn = 0, env_pair = -1, env_split = 0;
+    if (const char* e = getenv("TFB_GEMM_BN")) env_bn = atoi(e);
+    if (const char* e = getenv("TFB_GEMM_PAIR")) env_pair = atoi(e);
+    if (const char* e = getenv("TFB_GEMM_SPLITK")) env_split = atoi(e);
+    const int es = c.in_dtype == TFB_DTYPE_F32 ? 4 : 2;
+    p.k_blocks = (int)((c.K + 128 / es - 1) / (128 / es));
+    // CTA pairs pay off once there are enough 256 x 256 tiles to occupy about half of the SM pairs
+    // (measured: faster from 2048^3 up, slower at 1024^3).
+    const long long pair_tiles = ((c.M + 255) / 256) * ((c.N + 255) / 256);
+    p.pair = c.K > 0 && !c.force_bn && !env_bn &&
+             (env_pair >= 0 ? env_pair != 0 : pair_tiles >= (sm_count / 4));
+    p.bn = p.pair ? 256 : (c.force_bn ? c.force_bn : (env_bn ? env_bn : choose_bn(c.M, c.N, sm_count)));
+    p.kb_per_split = p.k_blocks;
+    if (!p.pair && c.K > 0) {
+        // Few output tiles but a long contraction (weight gradients: M, N ~ 1k, K = batch): share each
+        // tile's K range between several CTAs; partial sums go to scratch and are added in fixed order.
+        int bn = p.bn;
+        if (!c.force_bn && !env_bn && c.N >= 128) bn = c.N >= 256 ? 256 : 128;   // wide tiles feed the MMA better
+        const long long tiles = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + bn - 1) / bn);
+        long long s = env_split > 0 ? env_split : sm_count / tiles;
+        if (s > p.k_blocks / 8) s = p.k_blocks / 8;
+        if (s > 32) s = 32;
+        if (s >= 2 && (env_split > 0 || tiles * 2 <= sm_count)) {
+            p.bn = bn;
+            p.kb_per_split = (int)((p.k_blocks + s - 1) / s);
+            p.split_k = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+            p.rows_per_split = (c.M + kBlockM - 1) / kBlockM * kBlockM;
+            p.ld_partial = (c.N + 3) / 4 * 4;
+            p.partial_bytes = (size_t)p.split_k * p.rows_per_split * p.ld_partial * 4 + 256;
+        }
+    }
+    return p;
+}
+
+size_t gemm_workspace_bytes(const GemmCall& c, int sm_count) {
     size_t bytes = 0;
     const int64_t a_rows = c.a_kmajor ? c.M : c.K, a_cols = c.a_kmajor ? c.K : c.M;
     const int64_t b_rows = c.b_kmajor ? c.N : c.K, b_cols = c.b_kmajor ? c.K : c.N;
@@ -257,6 +325,7 @@ size_t gemm_workspace_bytes(const GemmCall& c) {
         if (!aligned16(c.A) || (c.lda & 7)) bytes += (size_t)(a_rows * round_up(a_cols, 8) * 2 + 256);
         if (!aligned16(c.B) || (c.ldb & 7)) bytes += (size_t)(b_rows * round_up(b_cols, 8) * 2 + 256);
     }
+    bytes += gemm_plan(c, sm_count).partial_bytes;
     return bytes;
 }
 
@@ -295,7 +364,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     const void* a_ptr[2] = {c.A, nullptr};
     const void* b_ptr[2] = {c.B, nullptr};
     int64_t lda = c.lda, ldb = c.ldb;
-    const size_t need = gemm_workspace_bytes(c);
+    const size_t need = gemm_workspace_bytes(c, st->sm_count);
     uint8_t* ws = nullptr;
     if (need > 0) {
         if (c.workspace != nullptr) {
@@ -362,19 +431,11 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     }
 
     // ---- tile shape and tensor maps ---------------------------------------------
-    // TFB_GEMM_BN / TFB_GEMM_CHUNK_KB: debugging overrides of the tile width and of the FP32
-    // accumulation chunk, read on every call.
-    int env_bn = 0, env_chunk = 0;
-    if (const char* e = getenv("TFB_GEMM_BN")) env_bn = atoi(e);
-    if (const char* e = getenv("TFB_GEMM_CHUNK_KB")) env_chunk = atoi(e);
-    int env_pair = -1;
-    if (const char* e = getenv("TFB_GEMM_PAIR")) env_pair = atoi(e);
-    // CTA pairs pay off once there are enough 256 x 256 tiles to occupy about half of the SM pairs
-    // (measured: faster from 2048^3 up, slower at 1024^3).
-    const long long pair_tiles = ((c.M + 255) / 256) * ((c.N + 255) / 256);
-    const bool use_pair = c.K > 0 && !c.force_bn && !env_bn &&
-                          (env_pair >= 0 ? env_pair != 0 : pair_tiles >= (st->sm_count / 4));
-    const int bn = use_pair ? 256 : (c.force_bn ? c.force_bn : (env_bn ? env_bn : choose_bn(c.M, c.N, st->sm_count)));
+    int env_chunk = 0;
+    if (const char* e = getenv("TFB_GEMM_CHUNK_KB")) env_chunk = atoi(e);   // debugging override
+    const GemmPlan plan = gemm_plan(c, st->sm_count);
+    const bool use_pair = plan.pair;
+    const int bn = plan.bn;
     if (bn != 64 && bn != 128 && bn != 256) return fail(TFB_ERR_INVALID_ARG, "gemm: tile N %d", bn);
     const int bk = 128 / es;
     const int t_mn = 128 / es;
@@ -388,7 +449,9 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     args.k_blocks = (int)((c.K + bk - 1) / bk);
     args.group_m = 16;
     // FP32: close the TMEM accumulator every 256 K elements (see gemm_kernel.cuh).
-    args.chunk_kb = f32 ? (c.chunk_kb > 0 ? c.chunk_kb : (env_chunk > 0 ? env_chunk : 8)) : args.k_blocks;
+    args.split_k = plan.split_k;
+    args.kb_per_split = plan.kb_per_split;
+    args.chunk_kb = f32 ? (c.chunk_kb > 0 ? c.chunk_kb : (env_chunk > 0 ? env_chunk : 8)) : plan.kb_per_split;
     if (args.chunk_kb < 1) args.chunk_kb = 1;
     args.C = c.C; args.ldc = c.ldc;
     args.out_type = c.out_dtype == TFB_DTYPE_F32 ? kOutF32 : (c.out_dtype == TFB_DTYPE_F16 ? kOutF16 : kOutBF16);
@@ -422,15 +485,32 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     }
     if (!f32) { maps[1] = maps[0]; maps[3] = maps[2]; }
     // FP32 output with 16-byte aligned rows leaves through TMA stores of 32 x 32 blocks.
-    args.c_tma = (c.out_dtype == TFB_DTYPE_F32 && aligned16(c.C) && (c.ldc & 3) == 0) ? 1 : 0;
-    if (args.c_tma) {
-        rc = make_map(&maps[4], TFB_DTYPE_F32, c.C, (uint64_t)c.N, (uint64_t)c.M, (uint64_t)c.ldc * 4, 32, 32);
+    float* partial = nullptr;
+    if (plan.split_k > 1) {
+        // Units write raw FP32 partial sums; the epilogue proper runs in the reduction kernel.
+        partial = reinterpret_cast<float*>(carve(plan.partial_bytes));
+        args.C = partial;
+        args.ldc = plan.ld_partial;
+        args.split_stride = plan.rows_per_split * plan.ld_partial;
+        args.out_type = kOutF32;
+        args.bias = nullptr; args.bias_mode = 0; args.relu = 0;
+        args.c_tma = 1;
+        rc = make_map(&maps[4], TFB_DTYPE_F32, partial, (uint64_t)c.N, (uint64_t)(plan.split_k * plan.rows_per_split),
+                      (uint64_t)plan.ld_partial * 4, 32, 32);
         if (rc != TFB_OK) return rc;
     } else {
-        maps[4] = maps[0];
+        args.split_stride = 0;
+        args.c_tma = (c.out_dtype == TFB_DTYPE_F32 && aligned16(c.C) && (c.ldc & 3) == 0) ? 1 : 0;
+        if (args.c_tma) {
+            rc = make_map(&maps[4], TFB_DTYPE_F32, c.C, (uint64_t)c.N, (uint64_t)c.M, (uint64_t)c.ldc * 4, 32, 32);
+            if (rc != TFB_OK) return rc;
+        } else {
+            maps[4] = maps[0];
+        }
     }
 
-    const int grid = args.num_tiles < st->sm_count ? args.num_tiles : st->sm_count;
+    const long long units = (long long)args.num_tiles * args.split_k;
+    const int grid = units < st->sm_count ? (int)units : st->sm_count;
     const bool a_mn = !c.a_kmajor, b_mn = !c.b_kmajor;
     if (use_pair) {
         args.group_m = 8;   // 8 pair tiles = 2048 rows, the same raster width as the single-CTA kernel
@@ -440,13 +520,22 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
         return launch_layout<kKind16, 256, 6, true>(a_mn, b_mn, maps, args, pairs, stream);
     }
     if (f32) {
-        if (bn == 256) return launch_layout<kKindTF32x3, 256, 2, false>(a_mn, b_mn, maps, args, grid, stream);
-        if (bn == 128) return launch_layout<kKindTF32x3, 128, 3, false>(a_mn, b_mn, maps, args, grid, stream);
-        return launch_layout<kKindTF32x3, 64, 4, false>(a_mn, b_mn, maps, args, grid, stream);
+        if (bn == 256) rc = launch_layout<kKindTF32x3, 256, 2, false>(a_mn, b_mn, maps, args, grid, stream);
+        else if (bn == 128) rc = launch_layout<kKindTF32x3, 128, 3, false>(a_mn, b_mn, maps, args, grid, stream);
+        else rc = launch_layout<kKindTF32x3, 64, 4, false>(a_mn, b_mn, maps, args, grid, stream);
+    } else {
+        if (bn == 256) rc = launch_layout<kKind16, 256, 4, false>(a_mn, b_mn, maps, args, grid, stream);
+        else if (bn == 128) rc = launch_layout<kKind16, 128, 6, false>(a_mn, b_mn, maps, args, grid, stream);
+        else rc = launch_layout<kKind16, 64, 8, false>(a_mn, b_mn, maps, args, grid, stream);
     }
-    if (bn == 256) return launch_layout<kKind16, 256, 4, false>(a_mn, b_mn, maps, args, grid, stream);
-    if (bn == 128) return launch_layout<kKind16, 128, 6, false>(a_mn, b_mn, maps, args, grid, stream);
-    return launch_layout<kKind16, 64, 8, false>(a_mn, b_mn, maps, args, grid, stream);
+    if (rc != TFB_OK || plan.split_k == 1) return rc;
+    const long long total = (long long)c.M * c.N;
+    splitk_reduce_kernel<<<grid_for(total, 256, st->sm_count), 256, 0, stream>>>(
+        partial, plan.split_k, c.M, c.N, plan.ld_partial, plan.rows_per_split * plan.ld_partial, c.C, c.ldc,
+        c.out_dtype == TFB_DTYPE_F32 ? kOutF32 : (c.out_dtype == TFB_DTYPE_F16 ? kOutF16 : kOutBF16), c.bias,
+        c.bias_mode, c.relu ? 1 : 0);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
 }
 
 }  // namespace tfb

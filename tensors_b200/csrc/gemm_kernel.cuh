@@ -64,6 +64,9 @@ struct GemmArgs {
     int M, N, K;
     int tiles_m, tiles_n, num_tiles, k_blocks;
     int chunk_kb;         // K blocks accumulated in TMEM before the epilogue drains them
+    int split_k;          // work units per output tile; unit u = split * num_tiles + tile
+    int kb_per_split;     // K blocks per unit (the last split may hold fewer)
+    long long split_stride;   // elements between the partial outputs of consecutive splits
     int group_m;          // M-tiles per rasterisation group (L2 reuse of B tiles)
     void* C;
     long long ldc;        // elements
@@ -190,6 +193,14 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& a, int& tm, i
     tn = r / gm;
 }
 
+// Work unit -> (tile, K-block range). With split_k == 1 a unit is a whole tile.
+__device__ __forceinline__ void unit_decode(int u, const GemmArgs& a, int& tile, int& split, int& kb0, int& kb1) {
+    split = u / a.num_tiles;
+    tile = u - split * a.num_tiles;
+    kb0 = split * a.kb_per_split;
+    kb1 = min(kb0 + a.kb_per_split, a.k_blocks);
+}
+
 // One commit whose arrival is delivered to the barrier at the same shared-memory offset in every
 // CTA of `cta_mask` (both CTAs of a pair). A commit is not a copy: no data moves.
 __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t cta_mask) {
@@ -274,7 +285,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
 
-    const int k_blocks = args.k_blocks;
+    const int num_units = args.num_tiles * args.split_k;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -282,11 +293,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int t = worker; t < args.num_tiles && ok; t += num_workers) {
-                int tm, tn;
+            for (int u = worker; u < num_units && ok; u += num_workers) {
+                int t, split, ub0, ub1, tm, tn;
+                unit_decode(u, args, t, split, ub0, ub1);
                 tile_coords(t, args, tm, tn);
                 const int m0 = tm * TILE_M + (int)rank * kBlockM, n0 = tn * BN + (int)rank * BN_CTA;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = ub0; kb < ub1; ++kb) {
                     ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
                     if (!ok) break;
                     const uint32_t st = smem_base + s * S::STAGE_BYTES;
@@ -370,8 +382,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t ph = 0;
             uint32_t cit = 0;   // accumulator hand-offs so far (chunks, over all tiles)
             bool ok = true;
-            for (int t = worker; t < args.num_tiles && ok; t += num_workers) {
-                for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += args.chunk_kb, ++cit) {
+            for (int u = worker; u < num_units && ok; u += num_workers) {
+                int t, split, ub0, ub1;
+                unit_decode(u, args, t, split, ub0, ub1);
+                for (int kb0 = ub0; kb0 < ub1 && ok; kb0 += args.chunk_kb, ++cit) {
                     const uint32_t buf = cit & 1u;
                     const uint32_t use = cit >> 1;
                     ok = mbar_wait(tempty_bar(buf), (use & 1u) ^ 1u, abort_flag, args.status,
@@ -379,7 +393,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * (uint32_t)BN;
-                    const int kb1 = min(kb0 + args.chunk_kb, k_blocks);
+                    const int kb1 = min(kb0 + args.chunk_kb, ub1);
                     for (int kb = kb0; kb < kb1; ++kb) {
                         ok = mbar_wait(full_bar(s), ph, abort_flag, args.status, kDevTimeoutFull);
                         if (!ok) break;
@@ -427,22 +441,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         };
         uint32_t cit = 0;
         bool ok = true;
-        for (int t = worker; t < args.num_tiles && ok; t += num_workers) {
-            int tm, tn;
+        for (int u = worker; u < num_units && ok; u += num_workers) {
+            int t, split, ub0, ub1, tm, tn;
+            unit_decode(u, args, t, split, ub0, ub1);
             tile_coords(t, args, tm, tn);
+            // Split-K partial outputs are stacked: split s writes rows [s * rows_per_split, ...) of the
+            // partial matrix (rows_per_split = split_stride / ldc covers whole tiles, so edge tiles of
+            // one split never reach into the next).
+            const int row_shift = (int)(args.split_stride / args.ldc) * split;
             const int m0 = tm * TILE_M + (int)rank * kBlockM, n0 = tn * BN + cbase;
-            const int row0 = m0 + q * 32;
+            const int row0 = m0 + q * 32 + row_shift;
             const int row = row0 + lane;
-            const bool row_ok = row < args.M;
+            const bool row_ok = (row - row_shift) < args.M;
             float row_bias = 0.f;
-            if (args.bias_mode == kBiasPerRow && row_ok) row_bias = __ldg(args.bias + row);
+            if (args.bias_mode == kBiasPerRow && row_ok) row_bias = __ldg(args.bias + row - row_shift);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)cbase;
 
             if constexpr (TF32) {
                 float acc[COLS];
 #pragma unroll
                 for (int i = 0; i < COLS; ++i) acc[i] = 0.f;
-                for (int kb0 = 0; kb0 < k_blocks; kb0 += args.chunk_kb, ++cit) {
+                for (int kb0 = ub0; kb0 < ub1; kb0 += args.chunk_kb, ++cit) {
                     const uint32_t buf = cit & 1u;
                     const uint32_t use = cit >> 1;
                     ok = mbar_wait(tfull_bar(buf), use & 1u, abort_flag, args.status, kDevTimeoutTmemFull);
@@ -465,7 +484,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                 for (int c = 0; c < COLS / 32; ++c) {
                     const int col0 = n0 + c * 32;
-                    if (col0 < args.N && (c_tma ? row0 < args.M : row_ok)) {
+                    if (col0 < args.N && (c_tma ? (row0 - row_shift) < args.M : row_ok)) {
                         float v[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
@@ -489,7 +508,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     uint32_t r[32];
                     tmem_ld_32x32(lane_addr + buf * (uint32_t)BN + (uint32_t)(c * 32), r);
                     tmem_ld_wait();
-                    if (!(c_tma ? row0 < args.M : row_ok)) continue;   // warp-uniform on the TMA path
+                    if (!(c_tma ? (row0 - row_shift) < args.M : row_ok)) continue;   // warp-uniform on the TMA path
                     float v[32];
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);

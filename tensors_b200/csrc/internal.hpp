@@ -67,8 +67,9 @@ int gemm_run(const GemmCall& call, cudaStream_t stream);
 // Same, with the device facts (SM count, status word) supplied by the caller instead of the
 // lazily created per-device state.
 int gemm_run_on(const GemmCall& call, cudaStream_t stream, const DeviceState* st);
-// Scratch bytes gemm_run needs for this call (0 for aligned 16-bit inputs).
-size_t gemm_workspace_bytes(const GemmCall& call);
+// Scratch bytes gemm_run needs for this call on a device with sm_count SMs: split / re-packed
+// operands plus split-K partial sums (0 for aligned 16-bit inputs with enough output tiles).
+size_t gemm_workspace_bytes(const GemmCall& call, int sm_count);
 
 // 2-D tensor map over a row-major matrix (`inner` contiguous elements per row, `outer` rows,
 // rows row_stride_bytes apart) with a box of box_inner x box_outer elements and the 128-byte

@@ -15,7 +15,7 @@ namespace tfb {
 
 namespace {
 
-constexpr int kColsumRowsPerBlock = 128;
+constexpr int kColsumRowsPerBlock = 32;
 
 __device__ __forceinline__ float tf32_rna(float x) {
     uint32_t r;
@@ -153,8 +153,8 @@ int linear_backward(const void* X, const void* W, const void* Y, const void* dY,
 
     const size_t dz_bytes = align256((size_t)(batch * ldz) * (f32 ? 8 : 2));
     const size_t partial_bytes = db != nullptr ? align256((size_t)(row_blocks * ldz) * 4) : 0;
-    const size_t gx_bytes = dX != nullptr ? gemm_workspace_bytes(gx) : 0;
-    const size_t gw_bytes = dW != nullptr ? gemm_workspace_bytes(gw) : 0;
+    const size_t gx_bytes = dX != nullptr ? gemm_workspace_bytes(gx, st->sm_count) : 0;
+    const size_t gw_bytes = dW != nullptr ? gemm_workspace_bytes(gw, st->sm_count) : 0;
     const size_t gemm_bytes = align256(gx_bytes > gw_bytes ? gx_bytes : gw_bytes);
     void* ws_v = nullptr;
     rc = workspace_get(stream, dz_bytes + partial_bytes + gemm_bytes + 256, &ws_v);

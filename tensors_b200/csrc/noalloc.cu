@@ -78,15 +78,15 @@ int tfb_matmul_f32_static(const float* A, const float* B, float* C, int64_t M, i
     c.lda = K; c.ldb = N; c.ldc = N;
     c.a_kmajor = true; c.b_kmajor = false;
     c.in_dtype = TFB_DTYPE_F32; c.out_dtype = TFB_DTYPE_F32;
-    const size_t need = gemm_workspace_bytes(c);
+    StaticState* s = nullptr;
+    int rc = static_state(&s);
+    if (rc != TFB_OK) return rc;
+    const size_t need = gemm_workspace_bytes(c, s->dev.sm_count);
     if (need > kStaticScratchBytes)
         return fail(TFB_ERR_TOO_LARGE,
                     "matmul_f32_static: the split operands need %zu bytes of scratch, the built-in array holds %zu "
                     "(roughly M*K + K*N <= 2 Mi elements); use tfb_matmul for larger products",
                     need, kStaticScratchBytes);
-    StaticState* s = nullptr;
-    int rc = static_state(&s);
-    if (rc != TFB_OK) return rc;
     // Nothing in the array has to start at zero: the split pass rewrites every byte it later reads,
     // padding columns included.
     c.workspace = s->scratch;

@@ -110,6 +110,25 @@ class MLP:
         capi.check(lib.tfb_sgd_momentum(_p(self.params), _p(self.velocity), _p(self.grads), self.numel,
                                         float(lr), float(momentum), 1.0, _stream()))
 
+    def capture_train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None, warmup=2):
+        """Records one training step (forward, backward, all-reduce, SGD) into a CUDA graph and returns
+        a callable that replays it: the step's ~40 launches then cost one graph launch on the host.
+        X and labels are captured by address — refill them in place for the next batch. The warm-up
+        steps run eagerly first so that every scratch buffer and NCCL channel exists before capture."""
+        for _ in range(max(1, warmup)):
+            self.train_step(X, labels, lr, momentum, global_rows)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.train_step(X, labels, lr, momentum, global_rows)
+
+        def replay():
+            graph.replay()
+            return self.loss
+
+        replay.graph = graph
+        return replay
+
     def train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None):
         self.forward_backward(X, labels, global_rows)
         self.allreduce_grads()

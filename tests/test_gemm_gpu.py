@@ -192,3 +192,24 @@ def test_square_sweep_sampled_rows_and_columns(oracle, n):
     assert_device_ok()
     want = oracle.matmul_rows(a16.float().cpu().numpy(), b16.float().cpu().numpy(), rows[:16])
     assert rel_err(Cb[torch.from_numpy(rows[:16]).cuda()].cpu().numpy(), want) < BF16_TOL
+
+
+@pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True)])
+@pytest.mark.parametrize("shape", [(512, 384, 8192), (1024, 1024, 4096), (100, 130, 3000), (256, 10, 8192)])
+def test_split_k_shapes_against_oracle(oracle, shape, trans_a, trans_b, in_dtype):
+    # Few output tiles and a long contraction: the K range of each tile is shared between CTAs and the
+    # partial sums are added in a second kernel; bias and ReLU must still land exactly once.
+    M, N, K = shape
+    tdt = torch.float32 if in_dtype == capi.DTYPE_F32 else torch.bfloat16
+    a16, b16 = dev(refdata.uniform(7, (M, K)), tdt), dev(refdata.uniform(8, (K, N)), tdt)
+    bias = refdata.normal(9, (N,))
+    want = np.maximum(oracle.matmul(a16.float().cpu().numpy(), b16.float().cpu().numpy()) + bias[None, :], 0)
+    A = a16.t().contiguous() if trans_a else a16
+    B = b16.t().contiguous() if trans_b else b16
+    C = gemm_ex(A, B, M, N, K, trans_a, trans_b, in_dtype=in_dtype, bias=dev(bias),
+                flags=capi.EPI_BIAS_COL | capi.EPI_RELU)
+    assert_device_ok()
+    got = C.cpu().numpy()
+    assert not np.isnan(got).any()
+    assert rel_err(got, want) < FP32_TOL

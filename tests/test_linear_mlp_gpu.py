@@ -138,3 +138,21 @@ def test_mlp_step_config5_shapes_reduced_batch(oracle):
         assert rel_err(m.bias(i, m.grads).cpu().numpy(), odb[i]) < 2e-5, i
     # velocity starts at zero: p1 = p0 - lr * g
     assert torch.allclose(m.params, p0 - 0.1 * m.grads, rtol=0, atol=1e-7)
+
+
+def test_mlp_graph_replay_matches_eager_steps(oracle):
+    # three eager steps and three replays of the captured step must walk the same trajectory
+    from tensors_b200.mlp import MLP
+    dims = (784, 128, 64, 10)
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    X, L = dev(refdata.mnist_like(7, (512, 784))), torch.from_numpy(refdata.labels(8, 512)).cuda()
+    eager = MLP(dims, ws)
+    for _ in range(5):
+        eager.train_step(X, L, lr=0.1, momentum=0.9)
+    graphed = MLP(dims, ws)
+    replay = graphed.capture_train_step(X, L, lr=0.1, momentum=0.9, warmup=2)   # 2 eager + 1 captured (not run)
+    for _ in range(3):
+        replay()
+    assert_device_ok()
+    assert torch.equal(eager.params, graphed.params)
+    assert float(eager.loss.item()) == float(graphed.loss.item())
