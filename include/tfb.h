@@ -104,6 +104,16 @@ int tfb_gemm_presplit(const float* A_hi, const float* A_lo, const float* B_hi, c
                       int64_t ldc, int trans_a, int trans_b, const float* bias, int epilogue_flags,
                       void* stream);
 
+/* C = A · B with all three matrices in HOST memory (row-major, dense; C is FP32): the call uploads B,
+ * streams A through in row panels and downloads C panel by panel, overlapping host-to-device copies,
+ * the products and device-to-host copies on three streams. Completion is ordered on `stream`
+ * (synchronise it before reading C). Use pinned host memory for the copies to overlap; pageable
+ * memory works but serialises them. Device buffers come from the stream-ordered pool and are
+ * released by the call. ref: the CPU-tensor use of Tensor::matmul (tensor/Tensor.cpp:334-368) plus
+ * the Tensor::to(Device) round trip a CUDA caller would add (tensor/Tensor.hpp:78-84). */
+int tfb_matmul_host(const void* A_host, const void* B_host, void* C_host, int64_t M, int64_t N, int64_t K,
+                    int dtype, void* stream);
+
 /* FP32 C[M,N] = A[M,K] · B[K,N] (row-major, dense) that never allocates: for hosts that may not
  * call cudaMalloc where they call us — inside a latency-critical loop that cannot take the
  * allocator's locks or its device-wide synchronisation, under a runtime that owns all device

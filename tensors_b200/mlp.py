@@ -101,8 +101,7 @@ class MLP:
         return self.loss
 
     def allreduce_grads(self):
-        if self.group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
-                                      and torch.distributed.get_world_size() > 1):
+        if self._distributed():
             torch.distributed.all_reduce(self.grads, group=self.group)
             torch.distributed.all_reduce(self.loss, group=self.group)
 
@@ -110,23 +109,38 @@ class MLP:
         capi.check(lib.tfb_sgd_momentum(_p(self.params), _p(self.velocity), _p(self.grads), self.numel,
                                         float(lr), float(momentum), 1.0, _stream()))
 
+    def _distributed(self):
+        return self.group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
+                                          and torch.distributed.get_world_size() > 1)
+
     def capture_train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None, warmup=2):
-        """Records one training step (forward, backward, all-reduce, SGD) into a CUDA graph and returns
-        a callable that replays it: the step's ~40 launches then cost one graph launch on the host.
-        X and labels are captured by address — refill them in place for the next batch. The warm-up
-        steps run eagerly first so that every scratch buffer and NCCL channel exists before capture."""
+        """Records one training step into CUDA graphs and returns a callable that replays it: the
+        step's ~40 launches then cost one or two graph launches on the host. Forward + backward and the
+        SGD update are captured; with more than one rank the NCCL all-reduce stays an ordinary call
+        between the two graphs (a collective is not recorded into a graph here). X and labels are
+        captured by address — refill them in place for the next batch. The warm-up steps run eagerly
+        first so that every scratch buffer exists before capture."""
         for _ in range(max(1, warmup)):
             self.train_step(X, labels, lr, momentum, global_rows)
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            self.train_step(X, labels, lr, momentum, global_rows)
+        distributed = self._distributed()
+        g_fb, g_sgd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_fb):
+            self.forward_backward(X, labels, global_rows)
+            if not distributed:
+                self.sgd_step(lr, momentum)
+        if distributed:
+            with torch.cuda.graph(g_sgd):
+                self.sgd_step(lr, momentum)
 
         def replay():
-            graph.replay()
+            g_fb.replay()
+            if distributed:
+                self.allreduce_grads()
+                g_sgd.replay()
             return self.loss
 
-        replay.graph = graph
+        replay.graphs = (g_fb, g_sgd)
         return replay
 
     def train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None):

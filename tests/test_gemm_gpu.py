@@ -213,3 +213,25 @@ def test_split_k_shapes_against_oracle(oracle, shape, trans_a, trans_b, in_dtype
     got = C.cpu().numpy()
     assert not np.isnan(got).any()
     assert rel_err(got, want) < FP32_TOL
+
+
+@pytest.mark.parametrize("pinned", [True, False])
+@pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
+def test_matmul_on_host_buffers(oracle, in_dtype, pinned):
+    # three row panels (the last one ragged), copies overlapped with the products inside the call
+    import ctypes
+    M, N, K = 2500, 300, 200
+    tdt = torch.float32 if in_dtype == capi.DTYPE_F32 else torch.bfloat16
+    a = torch.from_numpy(refdata.uniform(1, (M, K))).to(tdt)
+    b = torch.from_numpy(refdata.uniform(2, (K, N))).to(tdt)
+    c = torch.full((M, N), float("nan"))
+    if pinned:
+        a, b, c = a.pin_memory(), b.pin_memory(), c.pin_memory()
+    for _ in range(2):   # twice: buffers and streams are reused
+        capi.check(lib.tfb_matmul_host(ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()),
+                                       ctypes.c_void_p(c.data_ptr()), M, N, K, in_dtype, stream_ptr()))
+        torch.cuda.current_stream().synchronize()
+        assert_device_ok()
+        want = oracle.matmul(a.float().numpy(), b.float().numpy())
+        assert rel_err(c.numpy(), want) < FP32_TOL
+        c.fill_(float("nan"))
