@@ -305,14 +305,18 @@ def ours(args, rank, world, local_rank):
                    "n": n, "l2": "operands and output (268 MB each) exceed the 126 MB L2; no flush needed",
                    "parallelism": f"row-panels x{world}"},
         "roofline": {"bound": "tensor", "achieved": flops / (msk * 1e-3) / 1e12, "peak": tf32_peak, "unit": "TFLOP/s",
-                     "frac": flops / (msk * 1e-3) / 1e12 / tf32_peak, "traffic": None,
-                     "kernel": "gemm_tcgen05_kernel<TF32x3,BN=256> alone, operands pre-split",
+                     "frac": flops / (msk * 1e-3) / 1e12 / tf32_peak,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch at n = 8192, from the ncu
+                     # capture summarised in profiles/bench_8192_launch_list_and_dram.md (algorithmic: 1.34e9)
+                     "traffic": (7.36e9 + 0.268e9) if n == 8192 else None,
+                     "kernel": "gemm_tcgen05_kernel<TF32x3,BN=256,CTA pair> alone, operands pre-split",
                      "peak_source": f"{peak_src} bf16_tflops {peaks['bf16_tflops']} / 6 (TF32 issues at half the BF16 "
                                     f"rate and three products make one FP32 product)",
                      "kernel_ms": msk},
         "bf16": {"value": world * flops / (ms16 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms16,
                  "dtype": "bf16 in, f32 accumulate and out",
                  "roofline": {"bound": "tensor", "achieved": flops / (ms16 * 1e-3) / 1e12,
+                              "traffic": (1.10e9 + 0.252e9) if n == 8192 else None,
                               "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                               "frac": flops / (ms16 * 1e-3) / 1e12 / peaks["bf16_tflops"],
                               "peak_source": f"{peak_src} bf16_tflops (burst)"},
