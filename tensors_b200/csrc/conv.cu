@@ -76,7 +76,13 @@ __global__ void index_map_kernel(long long* __restrict__ out, const TapInfo* __r
         if (args.kH <= 32 && args.kW <= 32) {   // what the forward producers evaluate
             const uint32_t ymask = conv_axis_mask(y0, args.ay0, args.ay_step, args.kH, args.src_H);
             const uint32_t xmask = conv_axis_mask(x0, args.ax0, args.ax_step, args.kW, args.src_W);
-            off = conv_src_offset_fast(table[t], y0 * args.src_W + x0, ymask, xmask);
+            if (args.kH * args.kW <= 30) {
+                const uint32_t vmask = conv_combined_mask(ymask, xmask, args.kH, args.kW, true);
+                const bool valid = ((vmask >> ((uint32_t)table[t].kidx >> 16)) & 1u) != 0;
+                off = valid ? y0 * args.src_W + x0 + table[t].delta : -1;
+            } else {
+                off = conv_src_offset_fast(table[t], y0 * args.src_W + x0, ymask, xmask);
+            }
         } else {
             off = conv_src_offset<kConvFprop>(table[t], y0, x0, args);
         }
@@ -132,29 +138,41 @@ int check_shape(const ConvShape& s) {
 }
 
 // Tap table for gathers from a tensor with `planes` channels of plane_elems elements each:
-// forward form (ay = ki*d - pad) or gradient form (ay = pad - ki*d).
-std::vector<TapInfo> build_taps(int64_t planes, int64_t plane_elems, int64_t src_W, const ConvShape& s,
-                                bool gradient_form, bool ones_tap, int64_t table_len) {
-    std::vector<TapInfo> t((size_t)table_len);
-    const int64_t khw = s.kH * s.kW;
-    for (int64_t i = 0; i < table_len; ++i) {
+// forward form (ay = ki*d - pad) or gradient form (ay = pad - ki*d). Built on the device so that a
+// convolution call enqueues no host-to-device copy.
+struct TapParams {
+    int planes, plane_elems, src_W, kH, kW, ph, pw, dh, dw, gradient_form, ones_tap, table_len;
+};
+
+__global__ void build_taps_kernel(TapInfo* __restrict__ table, const TapParams p) {
+    const int khw = p.kH * p.kW;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < p.table_len; i += gridDim.x * blockDim.x) {
         TapInfo ti;
         ti.delta = 0;
-        ti.kidx = 0;
-        if (i < planes * khw) {
-            const int64_t ch = i / khw, r = i - ch * khw, ki = r / s.kW, kj = r - ki * s.kW;
-            ti.plane_off = (int)(ch * plane_elems);
-            ti.ay = (short)(gradient_form ? s.ph - ki * s.dh : ki * s.dh - s.ph);
-            ti.ax = (short)(gradient_form ? s.pw - kj * s.dw : kj * s.dw - s.pw);
-            ti.delta = (int)(ti.plane_off + (int64_t)ti.ay * src_W + ti.ax);
-            ti.kidx = (int)(ki | (kj << 8));
+        ti.kidx = 31 << 16;
+        if (i < p.planes * khw) {
+            const int ch = i / khw, r = i - ch * khw, ki = r / p.kW, kj = r - ki * p.kW;
+            ti.plane_off = ch * p.plane_elems;
+            ti.ay = (short)(p.gradient_form ? p.ph - ki * p.dh : ki * p.dh - p.ph);
+            ti.ax = (short)(p.gradient_form ? p.pw - kj * p.dw : kj * p.dw - p.pw);
+            ti.delta = ti.plane_off + (int)ti.ay * p.src_W + (int)ti.ax;
+            ti.kidx = ki | (kj << 8) | ((khw <= 30 ? ki * p.kW + kj : 31) << 16);
         } else {
-            ti.plane_off = (ones_tap && i == planes * khw) ? -2 : -1;
+            ti.plane_off = (p.ones_tap && i == p.planes * khw) ? -2 : -1;
+            if (ti.plane_off == -2) ti.kidx = 30 << 16;
             ti.ay = ti.ax = 0;
         }
-        t[(size_t)i] = ti;
+        table[i] = ti;
     }
-    return t;
+}
+
+int build_taps(TapInfo* table_d, int64_t planes, int64_t plane_elems, int64_t src_W, const ConvShape& s,
+               bool gradient_form, bool ones_tap, int64_t table_len, cudaStream_t stream) {
+    TapParams p{(int)planes, (int)plane_elems, (int)src_W, (int)s.kH, (int)s.kW, (int)s.ph, (int)s.pw,
+                (int)s.dh, (int)s.dw, gradient_form ? 1 : 0, ones_tap ? 1 : 0, (int)table_len};
+    build_taps_kernel<<<(unsigned)((table_len + 255) / 256), 256, 0, stream>>>(table_d, p);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
 }
 
 void fill_forward_geometry(ConvArgs& a, const ConvShape& s, const float* x) {
@@ -192,8 +210,8 @@ int conv2d_forward(const float* x, const float* w, const float* bias, float* out
     float* w_hi = reinterpret_cast<float*>(ws);
     float* w_lo = w_hi + s.Cout * ldw;
     TapInfo* table_d = reinterpret_cast<TapInfo*>(ws + w_bytes);
-    const std::vector<TapInfo> table = build_taps(s.Cin, s.H * s.W, s.W, s, false, false, table_len);
-    TFB_CUDA_OK(cudaMemcpyAsync(table_d, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
+    rc = build_taps(table_d, s.Cin, s.H * s.W, s.W, s, false, false, table_len, stream);
+    if (rc != TFB_OK) return rc;
     rc = split_operand(w, s.Cout, taps, taps, nullptr, w_hi, w_lo, ldw, stream);
     if (rc != TFB_OK) return rc;
 
@@ -261,8 +279,8 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
 
     if (want_dx) {
         TapInfo* table_d = reinterpret_cast<TapInfo*>(ws + o_dtab);
-        const std::vector<TapInfo> table = build_taps(s.Cout, P, s.outW, s, true, false, d_table);
-        TFB_CUDA_OK(cudaMemcpyAsync(table_d, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
+        rc = build_taps(table_d, s.Cout, P, s.outW, s, true, false, d_table, stream);
+        if (rc != TFB_OK) return rc;
         float* wd_hi = reinterpret_cast<float*>(ws + o_wd);
         float* wd_lo = wd_hi + s.Cin * d_ld;
         const int total = (int)(s.Cin * d_ld);
@@ -301,8 +319,8 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
     }
     if (want_w) {
         TapInfo* table_d = reinterpret_cast<TapInfo*>(ws + o_wtab);
-        const std::vector<TapInfo> table = build_taps(s.Cin, s.H * s.W, s.W, s, false, true, w_table);
-        TFB_CUDA_OK(cudaMemcpyAsync(table_d, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
+        rc = build_taps(table_d, s.Cin, s.H * s.W, s.W, s, false, true, w_table, stream);
+        if (rc != TFB_OK) return rc;
         float* dy_hi = reinterpret_cast<float*>(ws + o_dy);
         float* dy_lo = dy_hi + s.N * s.Cout * ldp;
         rc = split_operand(dY, s.N * s.Cout, P, P, nullptr, dy_hi, dy_lo, ldp, stream);
@@ -404,8 +422,8 @@ int tfb_im2col_index_map(int64_t* out, int64_t n_first, int64_t n_count, int64_t
     void* ws = nullptr;
     rc = workspace_get(stream, (size_t)table_len * sizeof(TapInfo), &ws);
     if (rc != TFB_OK) return rc;
-    const std::vector<TapInfo> table = build_taps(Cin, H * W, W, s, false, false, table_len);
-    TFB_CUDA_OK(cudaMemcpyAsync(ws, table.data(), table.size() * sizeof(TapInfo), cudaMemcpyHostToDevice, stream));
+    rc = build_taps(static_cast<TapInfo*>(ws), Cin, H * W, W, s, false, false, table_len, stream);
+    if (rc != TFB_OK) return rc;
     ConvArgs a;
     memset(&a, 0, sizeof(a));
     fill_forward_geometry(a, s, nullptr);

@@ -19,8 +19,8 @@
 // In all three the producer's lanes run over 32 consecutive spatial positions (coalesced global
 // reads, conflict-free shared-memory writes) for one tap at a time.
 //
-// Warp roles (320 threads): 0 = TMA for the B operand, 1 = MMA issuer + TMEM owner,
-// 2..5 = gather producers, 6..9 = epilogue. The TMEM accumulator is closed every `chunk_kb`
+// Warp roles (448 threads): 0 = TMA for the B operand, 1 = MMA issuer + TMEM owner,
+// 2..9 = gather producers, 10..13 = epilogue. The TMEM accumulator is closed every `chunk_kb`
 // K blocks and summed in registers with round-to-nearest adds (see gemm_kernel.cuh).
 #pragma once
 
@@ -32,7 +32,8 @@ enum ConvMode : int { kConvFprop = 0, kConvDgrad = 1, kConvWgrad = 2 };
 
 // Where tap t reads relative to a position: plane offset inside one sample and the two
 // coordinate offsets. plane_off < 0 marks taps that do not exist (-1) or the all-ones tap (-2).
-// `delta` = plane_off + ay * src_W + ax and `kidx` = ki | kj << 8 serve the separable fast path.
+// `delta` = plane_off + ay * src_W + ax and `kidx` = ki | kj << 8 | (ki * kW + kj) << 16 serve the
+// separable fast paths; the flat filter index is 31 for taps that do not exist and 30 for the ones tap.
 struct TapInfo {
     int plane_off;
     short ay, ax;
@@ -68,7 +69,12 @@ struct ConvArgs {
     int* status;
 };
 
-constexpr int kConvThreads = 320;
+// Warps: 0 TMA, 1 MMA, kConvProducerWarps gather producers, then 4 epilogue warps.
+constexpr int kConvProducerWarps = 8;
+// The producers form two groups of four warps that take alternate K blocks (stages), so the global-load
+// latency of one block overlaps with the shared-memory stores of the other.
+constexpr int kConvElems = 32;   // operand elements per producer thread and K block
+constexpr int kConvThreads = 32 * (2 + kConvProducerWarps + 4);
 
 template <int BN, int STAGES>
 struct ConvSmem {
@@ -118,6 +124,16 @@ __device__ __forceinline__ int conv_src_offset_fast(const TapInfo& ti, int threa
     return ok ? thread_off + ti.delta : -1;
 }
 
+// Filters of at most 30 taps per channel (3x3, 5x5): one combined validity mask per thread, bit
+// ki * kW + kj, bit 30 = "position exists" (the ones tap), bit 31 = 0 (absent taps). A tap then costs
+// one shift-and-test and one add.
+__device__ __forceinline__ uint32_t conv_combined_mask(uint32_t ymask, uint32_t xmask, int kH, int kW, bool pos_ok) {
+    uint32_t m = pos_ok ? (1u << 30) : 0u;
+    for (int ki = 0; ki < kH; ++ki)
+        if ((ymask >> ki) & 1u) m |= (xmask & ((1u << kW) - 1u)) << (ki * kW);
+    return m;
+}
+
 template <int MODE, int BN, int STAGES>
 __global__ void __launch_bounds__(kConvThreads, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
@@ -146,13 +162,13 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_a(s), 128);
+            mbar_init(full_a(s), 4);     // one arrival per warp of a producer group
             mbar_init(full_b(s), 1);
             mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 128);
+            mbar_init(tempty_bar(b), 4);     // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -289,11 +305,12 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
                 }
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 2 + kConvProducerWarps) {
         // ------------------------------ gather producers ------------------------------------
-        const int pw = warp - 2;   // 0..3
-        int s = 0;
-        uint32_t ph = 0;
+        const int pw = warp - 2;                       // producer warp
+        const int pgrp = pw & 3;                       // which 32 rows of the tile this warp writes
+        const uint32_t group = (uint32_t)(pw >> 2);    // which of the alternating K blocks this warp takes
+        uint32_t seq = 0;   // K blocks so far, over all tiles: block seq lives in stage seq % STAGES
         bool ok = true;
         for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
             int rt, ct, outer, kb0, kb1;
@@ -301,10 +318,11 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
             k_range(outer, kb0, kb1);
             // fprop / dgrad: this thread's position is fixed for the tile.
             int pos = 0, y0 = 0, x0 = 0, thread_off = 0;
-            uint32_t ymask = 0, xmask = 0;
+            uint32_t ymask = 0, xmask = 0, vmask = 0;
             bool pos_ok = false;
             const float* base = args.src;
             const bool fast = (args.div_h == 1 && args.div_w == 1 && args.kH <= 32 && args.kW <= 32);
+            const bool fast2 = fast && args.kH * args.kW <= 30;
             auto locate = [&]() {
                 pos_ok = pos < args.pos_count;
                 const int oy = pos / args.pos_W, ox = pos - oy * args.pos_W;
@@ -314,29 +332,41 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
                 if (fast) {
                     ymask = pos_ok ? conv_axis_mask(y0, args.ay0, args.ay_step, args.kH, args.src_H) : 0u;
                     xmask = pos_ok ? conv_axis_mask(x0, args.ax0, args.ax_step, args.kW, args.src_W) : 0u;
+                    if (fast2) vmask = conv_combined_mask(ymask, xmask, args.kH, args.kW, pos_ok);
                 }
             };
             if constexpr (!WGRAD) {
-                pos = rt * 128 + pw * 32 + lane;
+                pos = rt * 128 + pgrp * 32 + lane;
                 locate();
                 base = args.src + (long long)outer * args.src_sample;
             }
             // gather(kb, v): issue this thread's 32 loads of K block kb into registers, all in flight
             // together and before the wait for a free stage, so their latencies overlap.
-            auto gather = [&](int kb, float (&v)[32]) {
+            auto gather = [&](int kb, float (&v)[kConvElems]) {
                 int tap0;
                 if constexpr (WGRAD) {
                     const int n = kb / args.pos_blocks, pb = kb - n * args.pos_blocks;
                     pos = pb * 32 + lane;
                     locate();
                     base = args.src + (long long)n * args.src_sample;
-                    tap0 = rt * 128 + pw * 32;   // rows (taps) pw*32 .. +31 of the tile
+                    tap0 = rt * 128 + pgrp * 32;   // rows (taps) of the tile this warp writes
                 } else {
-                    tap0 = kb * 32;              // K index = tap; this warp owns rows pw*32 .. +31
+                    tap0 = kb * 32;                // K index = tap
                 }
-                if (fast) {
+                if (fast2) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < kConvElems; ++i) {
+                        const TapInfo ti = taps_sm[tap0 + i];
+                        const uint32_t kf = (uint32_t)ti.kidx >> 16;
+                        const bool valid = ((vmask >> kf) & 1u) != 0;
+                        float val = 0.f;
+                        if (WGRAD && kf == 30u) val = valid ? 1.f : 0.f;
+                        else if (valid) val = __ldg(base + thread_off + ti.delta);
+                        v[i] = val;
+                    }
+                } else if (fast) {
+#pragma unroll
+                    for (int i = 0; i < kConvElems; ++i) {
                         const TapInfo ti = taps_sm[tap0 + i];
                         const int off = conv_src_offset_fast(ti, thread_off, ymask, xmask);
                         float val = (ti.plane_off == -2 && pos_ok) ? 1.f : 0.f;
@@ -345,7 +375,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {   // fully unrolled so that v[] stays in registers
+                    for (int i = 0; i < kConvElems; ++i) {   // fully unrolled so that v[] stays in registers
                         const TapInfo ti = taps_sm[tap0 + i];
                         float val = 0.f;
                         if (ti.plane_off >= 0) {
@@ -359,44 +389,48 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
                 }
             };
             // emit(v): wait for a free stage, split into hi / lo, write the operand tile, signal.
-            auto emit = [&](const float (&v)[32]) -> bool {
-                bool good = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
+            auto emit = [&](int s, uint32_t ph, const float (&v)[kConvElems]) -> bool {
+                // One lane polls (a barrier polled and arrived on by 128 threads serialises on its word).
+                bool good = true;
+                if (lane == 0) good = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
                 good = __all_sync(0xffffffffu, good);
                 if (!good) return false;
                 uint8_t* a_hi = smem_gen + s * S::STAGE_BYTES;
                 uint8_t* a_lo = a_hi + S::A_TILE;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < kConvElems; ++i) {
                     const float hi = tf32_rna_dev(v[i]);
                     const float lo = v[i] - hi;
                     uint32_t off;
                     if constexpr (WGRAD) {
-                        // row m = pw*32 + i, contraction index kk = lane: K-major, 128-byte swizzle
-                        const uint32_t m = (uint32_t)(pw * 32 + i);
+                        // row m = tap, contraction index kk = lane: K-major, 128-byte swizzle
+                        const uint32_t m = (uint32_t)(pgrp * 32 + i);
                         off = m * 128u + ((((uint32_t)lane >> 2) ^ (m & 7u)) << 4) + ((uint32_t)lane & 3u) * 4u;
                     } else {
-                        // row = position (lane), contraction index kk = i: MN-major, 32-byte atoms
-                        off = (uint32_t)pw * 4096u + (uint32_t)(lane & 7) * 4u + (uint32_t)i * 128u +
-                              ((((uint32_t)lane >> 3) ^ ((uint32_t)i & 3u)) << 5);
+                        // row = position (lane), contraction index kk: MN-major, 32-byte atoms
+                        const uint32_t kk = (uint32_t)i;
+                        off = (uint32_t)pgrp * 4096u + (uint32_t)(lane & 7) * 4u + kk * 128u +
+                              ((((uint32_t)lane >> 3) ^ (kk & 3u)) << 5);
                     }
                     *reinterpret_cast<float*>(a_hi + off) = hi;
                     *reinterpret_cast<float*>(a_lo + off) = lo;
                 }
-                fence_proxy_async_smem();
-                mbar_arrive(full_a(s));
-                if (++s == STAGES) { s = 0; ph ^= 1u; }
+                fence_proxy_async_smem();   // every writer makes its stores visible to the tensor core's proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a(s));
                 return true;
             };
             // (Issuing the gathers of block kb+1 before writing block kb was tried and measured slower.)
-            float va[32];
-            for (int kb = kb0; kb < kb1 && ok; ++kb) {
+            float va[kConvElems];
+            for (int kb = kb0; kb < kb1 && ok; ++kb, ++seq) {
+                if ((seq & 1u) != group) continue;
                 gather(kb, va);
-                ok = emit(va);
+                ok = emit((int)(seq % STAGES), (seq / STAGES) & 1u, va);
             }
         }
     } else {
         // ------------------------------ epilogue ----------------------------------------------
-        const int q = warp & 3;   // warps 6..9 -> TMEM lane quarters 2, 3, 0, 1
+        const int q = warp & 3;   // TMEM lane quarter this warp may read
         uint32_t cit = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < args.num_tiles && ok; t += gridDim.x) {
@@ -413,7 +447,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
             for (int c0 = kb0; c0 < kb1; c0 += args.chunk_kb, ++cit) {
                 const uint32_t buf = cit & 1u;
                 const uint32_t use = cit >> 1;
-                ok = mbar_wait(tfull_bar(buf), use & 1u, abort_flag, args.status, kDevTimeoutTmemFull);
+                if (lane == 0) ok = mbar_wait(tfull_bar(buf), use & 1u, abort_flag, args.status, kDevTimeoutTmemFull);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -428,7 +462,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant
                     }
                 }
                 tc_fence_before_sync();
-                mbar_arrive(tempty_bar(buf));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(buf));
             }
             if (!ok) break;
             if (row_ok) {

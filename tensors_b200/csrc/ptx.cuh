@@ -61,12 +61,31 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
                  : "memory");
 }
 
+// One poll. The warp may be suspended by the hardware for up to `kSuspendNs` while the phase is
+// incomplete (it is woken as soon as the phase completes), so waiting warps do not burn the issue
+// slots that working warps of the same SM partition need.
+constexpr uint32_t kSuspendNs = 20000;
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(kSuspendNs)
+        : "memory");
+    return done;
+}
+
+// Non-suspending poll (mbarrier.test_wait): for the few waits on a latency-critical handshake path.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(done)
@@ -90,7 +109,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     uint32_t polls = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (((++polls) & 0x3ffu) == 0) {
+        if (((++polls) & 0xfu) == 0) {
+            if (*abort_flag != 0) return false;
+            if (global_timer_ns() - t0 > kWaitBudgetNs) {
+                *abort_flag = err_code;
+                if (status != nullptr) atomicCAS(status, 0, err_code);
+                return false;
+            }
+        }
+    }
+}
+
+// Same contract as mbar_wait, polling without suspension.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int err_code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t polls = 0;
+    while (true) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if (((++polls) & 0xfffu) == 0) {
             if (*abort_flag != 0) return false;
             if (global_timer_ns() - t0 > kWaitBudgetNs) {
                 *abort_flag = err_code;

@@ -16,6 +16,7 @@ DeviceState g_dev[64];
 struct Scratch {
     void* ptr = nullptr;
     size_t bytes = 0;
+    bool in_graph = false;   // handed to a stream capture: a CUDA graph may hold this address forever
 };
 std::map<std::pair<int, cudaStream_t>, Scratch> g_scratch;
 }  // namespace
@@ -64,14 +65,34 @@ int device_state(DeviceState** out) {
 int workspace_get(cudaStream_t stream, size_t bytes, void** out) {
     int dev = -1;
     TFB_CUDA_OK(cudaGetDevice(&dev));
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    TFB_CUDA_OK(cudaStreamIsCapturing(stream, &cap));
     std::lock_guard<std::mutex> lock(g_mu);
+    if (cap != cudaStreamCaptureStatusNone) {
+        // Inside a stream capture nothing may be allocated or freed on behalf of later replays. Hand
+        // out the largest buffer an ordinary call has already created on this device and keep it
+        // alive from now on. (Graph replays and ordinary calls that run at the same time on different
+        // streams then share scratch: order them.)
+        Scratch* best = nullptr;
+        for (auto& kv : g_scratch)
+            if (kv.first.first == dev && (best == nullptr || kv.second.bytes > best->bytes)) best = &kv.second;
+        if (best == nullptr || best->bytes < bytes)
+            return fail(TFB_ERR_UNSUPPORTED,
+                        "this call needs %zu bytes of scratch but is being captured into a CUDA graph and only %zu "
+                        "exist: run the same call once outside the capture first",
+                        bytes, best ? best->bytes : (size_t)0);
+        best->in_graph = true;
+        *out = best->ptr;
+        return TFB_OK;
+    }
     Scratch& s = g_scratch[std::make_pair(dev, stream)];
     if (s.bytes < bytes) {
-        // Stream-ordered: the old buffer is released after the work already queued on this
-        // stream, the new one is usable by work queued after this point.
-        if (s.ptr != nullptr) TFB_CUDA_OK(cudaFreeAsync(s.ptr, stream));
+        // Stream-ordered: the old buffer is released after the work already queued on this stream, the
+        // new one is usable by work queued after this point. A buffer a graph may reference is kept.
+        if (s.ptr != nullptr && !s.in_graph) TFB_CUDA_OK(cudaFreeAsync(s.ptr, stream));
         s.ptr = nullptr;
         s.bytes = 0;
+        s.in_graph = false;
         size_t want = bytes + (bytes >> 2);   // head-room so alternating sizes do not thrash
         want = (want + 0xfffff) & ~(size_t)0xfffff;
         void* p = nullptr;
