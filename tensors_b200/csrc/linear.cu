@@ -95,14 +95,24 @@ __global__ void mask_colsum16_kernel(const T* __restrict__ dY, const T* __restri
     if (partial != nullptr) partial[(long long)blockIdx.y * ld_out + c] = s;
 }
 
-// db[c] = sum over row blocks (ascending) of partial[b][c].
+// db[c] = sum over row blocks of partial[b][c], in a fixed order: a block of 32 columns x 8 row
+// groups; group g adds blocks g, g+8, ... in ascending order, then the eight group sums are added
+// in ascending order.
 __global__ void colsum_finish_kernel(const float* __restrict__ partial, long long blocks, long long cols,
                                      long long ld, float* __restrict__ out) {
-    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
+    __shared__ float sm[8][33];
+    const long long c = (long long)blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
-    for (long long b = 0; b < blocks; ++b) s += partial[b * ld + c];
-    out[c] = s;
+    if (c < cols)
+        for (long long b = threadIdx.y; b < blocks; b += 8) s += partial[b * ld + c];
+    sm[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) t += sm[g][threadIdx.x];
+        out[c] = t;
+    }
 }
 
 inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
@@ -186,7 +196,7 @@ int linear_backward(const void* X, const void* W, const void* Y, const void* dY,
     }
     TFB_CUDA_OK(cudaGetLastError());
     if (db != nullptr) {
-        colsum_finish_kernel<<<(unsigned)((out_f + 127) / 128), 128, 0, stream>>>(partial, row_blocks, out_f, ldz, db);
+        colsum_finish_kernel<<<(unsigned)((out_f + 31) / 32), dim3(32, 8), 0, stream>>>(partial, row_blocks, out_f, ldz, db);
         TFB_CUDA_OK(cudaGetLastError());
     }
     gx.A = gw.A = dz;
