@@ -155,6 +155,18 @@ int tfb_linear_backward(const void* X, const void* W, const void* Y, const void*
                         float* dbias, int64_t batch, int64_t in_features, int64_t out_features, int relu,
                         int dtype, void* stream);
 
+/* tfb_linear_backward for FP32 with X and W given as the hi / lo planes tfb_split_tf32 wrote
+ * (leading dimensions ldx, ldw: multiples of 4, >= in_features; 16-byte aligned bases). A training
+ * step that keeps the planes it made for the forward product (tfb_gemm_presplit with trans_b = 1 and
+ * TFB_EPI_BIAS_COL | TFB_EPI_RELU is the forward of such a layer) does not split X and W again. The
+ * X planes are read only when dW != NULL, the W planes only when dX != NULL. Results are bit-identical
+ * to tfb_linear_backward on the unsplit operands. ref: the tensors MatmulBackward saves,
+ * autograd/ops/MatmulBackward.hpp:21-24 — here saved in the form the tensor core consumes. */
+int tfb_linear_backward_presplit(const float* X_hi, const float* X_lo, int64_t ldx, const float* W_hi,
+                                 const float* W_lo, int64_t ldw, const float* Y, const float* dY, float* dX,
+                                 float* dW, float* dbias, int64_t batch, int64_t in_features,
+                                 int64_t out_features, int relu, void* stream);
+
 /* ---- nn::Conv2d (implicit GEMM; the im2col / col2im matrices are never materialised) ---- */
 
 /* Output extent of a convolution axis: (in + 2·pad − dilation·(k−1) − 1) / stride + 1.

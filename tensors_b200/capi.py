@@ -44,6 +44,8 @@ PROTOTYPES = {
     "tfb_matmul_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tfb_linear_forward": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_linear_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tfb_linear_backward_presplit": (_i32, [_vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                                            _i32, _vp]),
     "tfb_conv_out_dim": (_i64, [_i64, _i64, _i64, _i64, _i64]),
     "tfb_conv2d_forward": (_i32, [_vp, _vp, _vp, _vp] + [_i64] * 13 + [_i32, _i32, _vp]),
     "tfb_conv2d_backward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp] + [_i64] * 13 + [_i32, _vp]),

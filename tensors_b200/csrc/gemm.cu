@@ -296,19 +296,29 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
     if (!p.pair && c.K > 0) {
         // Few output tiles but a long contraction (weight gradients: M, N ~ 1k, K = batch): share each
         // tile's K range between several CTAs; partial sums go to scratch and are added in fixed order.
-        int bn = p.bn;
-        if (!c.force_bn && !env_bn && c.N >= 128) bn = c.N >= 256 ? 256 : 128;   // wide tiles feed the MMA better
-        const long long tiles = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + bn - 1) / bn);
-        long long s = env_split > 0 ? env_split : sm_count / tiles;
-        if (s > p.k_blocks / 8) s = p.k_blocks / 8;
-        if (s > 32) s = 32;
-        if (s >= 2 && (env_split > 0 || tiles * 2 <= sm_count)) {
-            p.bn = bn;
+        auto split_plan = [&](long long workers, long long tiles, int tile_rows) {
+            long long s = env_split > 0 ? env_split : workers / tiles;
+            if (s > p.k_blocks / 8) s = p.k_blocks / 8;
+            if (s > 32) s = 32;
+            if (s < 2 || !(env_split > 0 || tiles * 2 <= workers)) return false;
             p.kb_per_split = (int)((p.k_blocks + s - 1) / s);
             p.split_k = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
-            p.rows_per_split = (c.M + kBlockM - 1) / kBlockM * kBlockM;
+            p.rows_per_split = (c.M + tile_rows - 1) / tile_rows * tile_rows;
             p.ld_partial = (c.N + 3) / 4 * 4;
             p.partial_bytes = (size_t)p.split_k * p.rows_per_split * p.ld_partial * 4 + 256;
+            return true;
+        };
+        // CTA pairs keep the tensor pipe fuller than single CTAs (deeper ring per MMA), so prefer them
+        // whenever whole 256 x 256 tiles exist.
+        const bool pair_ok = !c.force_bn && !env_bn && env_pair != 0 && c.M >= 256 && c.N >= 256;
+        if (pair_ok && split_plan(sm_count / 2, pair_tiles, 2 * kBlockM)) {
+            p.pair = true;
+            p.bn = 256;
+        } else {
+            int bn = p.bn;
+            if (!c.force_bn && !env_bn && c.N >= 128) bn = c.N >= 256 ? 256 : 128;   // wide tiles feed the MMA better
+            const long long tiles = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + bn - 1) / bn);
+            if (split_plan(sm_count, tiles, kBlockM)) p.bn = bn;
         }
     }
     return p;
@@ -515,11 +525,10 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     if (use_pair) {
         args.group_m = 8;   // 8 pair tiles = 2048 rows, the same raster width as the single-CTA kernel
         const int max_pairs = st->sm_count / 2;
-        const int pairs = args.num_tiles < max_pairs ? args.num_tiles : max_pairs;
-        if (f32) return launch_layout<kKindTF32x3, 256, 3, true>(a_mn, b_mn, maps, args, pairs, stream);
-        return launch_layout<kKind16, 256, 6, true>(a_mn, b_mn, maps, args, pairs, stream);
-    }
-    if (f32) {
+        const int pairs = units < max_pairs ? (int)units : max_pairs;
+        if (f32) rc = launch_layout<kKindTF32x3, 256, 3, true>(a_mn, b_mn, maps, args, pairs, stream);
+        else rc = launch_layout<kKind16, 256, 6, true>(a_mn, b_mn, maps, args, pairs, stream);
+    } else if (f32) {
         if (bn == 256) rc = launch_layout<kKindTF32x3, 256, 2, false>(a_mn, b_mn, maps, args, grid, stream);
         else if (bn == 128) rc = launch_layout<kKindTF32x3, 128, 3, false>(a_mn, b_mn, maps, args, grid, stream);
         else rc = launch_layout<kKindTF32x3, 64, 4, false>(a_mn, b_mn, maps, args, grid, stream);

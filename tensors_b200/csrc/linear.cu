@@ -133,9 +133,16 @@ int linear_forward(const void* X, const void* W, const float* bias, void* Y, int
     return gemm_run(c, stream);
 }
 
-int linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
-                    float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
-                    cudaStream_t stream) {
+// Planes of an FP32 operand that the caller split beforehand (null hi = not supplied).
+struct SavedPlanes {
+    const float* hi = nullptr;
+    const float* lo = nullptr;
+    int64_t ld = 0;
+};
+
+static int linear_backward_impl(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+                                float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
+                                cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved) {
     DeviceState* st = nullptr;
     int rc = device_state(&st);
     if (rc != TFB_OK) return rc;
@@ -160,6 +167,12 @@ int linear_backward(const void* X, const void* W, const void* Y, const void* dY,
     gx.a_lo_off = gw.a_lo_off = batch * ldz;
     // Placeholders so that the scratch computation sees aligned A operands.
     gx.A = gw.A = reinterpret_cast<const void*>(static_cast<uintptr_t>(256));
+    if (wsaved.hi != nullptr) {
+        gx.B = wsaved.hi; gx.ldb = wsaved.ld; gx.b_presplit = true; gx.b_lo_off = wsaved.lo - wsaved.hi;
+    }
+    if (xs.hi != nullptr) {
+        gw.B = xs.hi; gw.ldb = xs.ld; gw.b_presplit = true; gw.b_lo_off = xs.lo - xs.hi;
+    }
 
     const size_t dz_bytes = align256((size_t)(batch * ldz) * (f32 ? 8 : 2));
     const size_t partial_bytes = db != nullptr ? align256((size_t)(row_blocks * ldz) * 4) : 0;
@@ -213,6 +226,13 @@ int linear_backward(const void* X, const void* W, const void* Y, const void* dY,
     return TFB_OK;
 }
 
+int linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+                    float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
+                    cudaStream_t stream) {
+    return linear_backward_impl(X, W, Y, dY, dX, dW, db, batch, in_f, out_f, relu, dtype, stream, SavedPlanes(),
+                                SavedPlanes());
+}
+
 }  // namespace tfb
 
 extern "C" {
@@ -240,6 +260,33 @@ int tfb_linear_backward(const void* X, const void* W, const void* Y, const void*
     if (dW != nullptr && X == nullptr) return fail(TFB_ERR_INVALID_ARG, "linear_backward: dW needs X");
     return linear_backward(X, W, Y, dY, dX, dW, dbias, batch, in_features, out_features, relu != 0, dtype,
                            static_cast<cudaStream_t>(stream));
+}
+
+int tfb_linear_backward_presplit(const float* X_hi, const float* X_lo, int64_t ldx, const float* W_hi,
+                                 const float* W_lo, int64_t ldw, const float* Y, const float* dY, float* dX,
+                                 float* dW, float* dbias, int64_t batch, int64_t in_features,
+                                 int64_t out_features, int relu, void* stream) {
+    using namespace tfb;
+    if (batch < 0 || in_features < 0 || out_features < 0)
+        return fail(TFB_ERR_INVALID_ARG, "linear_backward_presplit: negative extent");
+    if (dY == nullptr) return fail(TFB_ERR_INVALID_ARG, "linear_backward_presplit: null upstream gradient");
+    if (dX != nullptr && (W_hi == nullptr || W_lo == nullptr))
+        return fail(TFB_ERR_INVALID_ARG, "linear_backward_presplit: dX needs the planes of W");
+    if (dW != nullptr && (X_hi == nullptr || X_lo == nullptr))
+        return fail(TFB_ERR_INVALID_ARG, "linear_backward_presplit: dW needs the planes of X");
+    SavedPlanes xs, wsaved;
+    if (dW != nullptr) { xs.hi = X_hi; xs.lo = X_lo; xs.ld = ldx; }
+    if (dX != nullptr) { wsaved.hi = W_hi; wsaved.lo = W_lo; wsaved.ld = ldw; }
+    for (const SavedPlanes& pl : {xs, wsaved}) {
+        if (pl.hi == nullptr) continue;
+        if ((pl.ld & 3) || pl.ld < in_features)
+            return fail(TFB_ERR_UNSUPPORTED,
+                        "linear_backward_presplit: plane leading dimensions must be multiples of 4 and >= in_features");
+        if ((reinterpret_cast<uintptr_t>(pl.hi) | reinterpret_cast<uintptr_t>(pl.lo)) & 15u)
+            return fail(TFB_ERR_UNSUPPORTED, "linear_backward_presplit: planes must be 16-byte aligned");
+    }
+    return linear_backward_impl(nullptr, nullptr, Y, dY, dX, dW, dbias, batch, in_features, out_features,
+                                relu != 0, TFB_DTYPE_F32, static_cast<cudaStream_t>(stream), xs, wsaved);
 }
 
 }  // extern "C"

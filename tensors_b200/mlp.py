@@ -56,6 +56,7 @@ class MLP:
                 self.bias(i).copy_(torch.as_tensor(biases[i], dtype=torch.float32))
         self.loss = torch.zeros(1, device=device, dtype=torch.float32)
         self._acts = None
+        self._plane_bufs = {}
 
     def _seg(self, buf, k, shape):
         n = 1
@@ -69,15 +70,38 @@ class MLP:
     def bias(self, i, buf=None):
         return self._seg(self.params if buf is None else buf, 2 * i + 1, (self.dims[i + 1],))
 
+    def _planes(self, key, rows, cols, device):
+        """Persistent hi / lo plane buffer [2, rows, ld] for a rows x cols FP32 operand."""
+        ld = (cols + 3) // 4 * 4
+        buf = self._plane_bufs.get(key)
+        if buf is None or buf.shape != (2, rows, ld) or buf.device != device:
+            buf = torch.empty((2, rows, ld), device=device, dtype=torch.float32)
+            self._plane_bufs[key] = buf
+        return buf, ld
+
+    def _split(self, key, t):
+        rows, cols = t.shape
+        buf, ld = self._planes(key, rows, cols, t.device)
+        capi.check(lib.tfb_split_tf32(_p(t), rows, cols, cols, _p(buf[0]), _p(buf[1]), ld, _stream()))
+        return buf, ld
+
     def forward(self, X):
+        """Each operand is split into its TF32 hi / lo planes once per step; the planes made for the
+        forward products are kept for the backward ones."""
         batch = X.shape[0]
         acts = [X]
+        self._xs, self._ws = [], []
         for i in range(self.L):
+            xs, ldx = self._split(("x", i), acts[-1])
+            ws, ldw = self._split(("w", i), self.weight(i))
             Y = torch.empty((batch, self.dims[i + 1]), device=X.device, dtype=torch.float32)
-            capi.check(lib.tfb_linear_forward(_p(acts[-1]), _p(self.weight(i)), _p(self.bias(i)), _p(Y), batch,
-                                              self.dims[i], self.dims[i + 1], int(i < self.L - 1),
-                                              capi.DTYPE_F32, _stream()))
+            flags = capi.EPI_BIAS_COL | (capi.EPI_RELU if i < self.L - 1 else 0)
+            capi.check(lib.tfb_gemm_presplit(_p(xs[0]), _p(xs[1]), _p(ws[0]), _p(ws[1]), _p(Y), batch,
+                                             self.dims[i + 1], self.dims[i], ldx, ldw, self.dims[i + 1], 0, 1,
+                                             _p(self.bias(i)), flags, _stream()))
             acts.append(Y)
+            self._xs.append((xs, ldx))
+            self._ws.append((ws, ldw))
         self._acts = acts
         return acts[-1]
 
@@ -94,9 +118,11 @@ class MLP:
         for i in reversed(range(self.L)):
             relu = i < self.L - 1
             dX = torch.empty_like(acts[i]) if i > 0 else None
-            capi.check(lib.tfb_linear_backward(_p(acts[i]), _p(self.weight(i)), _p(acts[i + 1]), _p(upstream), _p(dX),
-                                               _p(self.weight(i, self.grads)), _p(self.bias(i, self.grads)), batch,
-                                               self.dims[i], self.dims[i + 1], int(relu), capi.DTYPE_F32, _stream()))
+            (xs, ldx), (ws, ldw) = self._xs[i], self._ws[i]
+            capi.check(lib.tfb_linear_backward_presplit(
+                _p(xs[0]), _p(xs[1]), ldx, _p(ws[0]), _p(ws[1]), ldw, _p(acts[i + 1]), _p(upstream), _p(dX),
+                _p(self.weight(i, self.grads)), _p(self.bias(i, self.grads)), batch, self.dims[i],
+                self.dims[i + 1], int(relu), _stream()))
             upstream = dX
         return self.loss
 

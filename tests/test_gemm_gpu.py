@@ -196,7 +196,8 @@ def test_square_sweep_sampled_rows_and_columns(oracle, n):
 
 @pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
 @pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True)])
-@pytest.mark.parametrize("shape", [(512, 384, 8192), (1024, 1024, 4096), (100, 130, 3000), (256, 10, 8192)])
+@pytest.mark.parametrize("shape", [(512, 384, 8192), (1024, 1024, 4096), (1024, 784, 8192), (100, 130, 3000),
+                                   (256, 10, 8192)])
 def test_split_k_shapes_against_oracle(oracle, shape, trans_a, trans_b, in_dtype):
     # Few output tiles and a long contraction: the K range of each tile is shared between CTAs and the
     # partial sums are added in a second kernel; bias and ReLU must still land exactly once.

@@ -64,6 +64,39 @@ def test_linear_with_bias_against_oracle(oracle, shape, relu):
     assert rel_err(db, odb) < FP32_TOL
 
 
+@pytest.mark.parametrize("shape", [(64, 784, 256), (33, 50, 10), (4096, 1024, 1024), (200, 10, 300)])
+def test_linear_backward_on_saved_planes_is_bit_identical(shape):
+    # forward product and backward on hi / lo planes the caller made once == the unsplit entry points
+    batch, in_f, out_f = shape
+    x, w = refdata.normal(1, (batch, in_f)), refdata.linear_weight(in_f, out_f)
+    b, g = refdata.normal(2, (out_f,)) * np.float32(0.1), refdata.normal(3, (batch, out_f))
+    Y0, dX0, dW0, db0 = linear_fwd_bwd(x, w, b, g, relu=True)
+    X, W, G, B = dev(x), dev(w), dev(g), dev(b)
+    ld = (in_f + 3) // 4 * 4
+    xs = torch.full((2, batch, ld), float("nan"), device="cuda")
+    ws = torch.full((2, out_f, ld), float("nan"), device="cuda")
+    capi.check(lib.tfb_split_tf32(ptr(X), batch, in_f, in_f, ptr(xs[0]), ptr(xs[1]), ld, stream_ptr()))
+    capi.check(lib.tfb_split_tf32(ptr(W), out_f, in_f, in_f, ptr(ws[0]), ptr(ws[1]), ld, stream_ptr()))
+    Y = torch.full((batch, out_f), float("nan"), device="cuda")
+    capi.check(lib.tfb_gemm_presplit(ptr(xs[0]), ptr(xs[1]), ptr(ws[0]), ptr(ws[1]), ptr(Y), batch, out_f, in_f, ld, ld,
+                                     out_f, 0, 1, ptr(B), capi.EPI_BIAS_COL | capi.EPI_RELU, stream_ptr()))
+    dX = torch.full((batch, in_f), float("nan"), device="cuda")
+    dW = torch.full((out_f, in_f), float("nan"), device="cuda")
+    db = torch.full((out_f,), float("nan"), device="cuda")
+    capi.check(lib.tfb_linear_backward_presplit(ptr(xs[0]), ptr(xs[1]), ld, ptr(ws[0]), ptr(ws[1]), ld, ptr(Y), ptr(G),
+                                                ptr(dX), ptr(dW), ptr(db), batch, in_f, out_f, 1, stream_ptr()))
+    assert_device_ok()
+    for got, want in ((Y, Y0), (dX, dX0), (dW, dW0), (db, db0)):
+        assert np.array_equal(got.cpu().numpy(), want)
+    # only the gradient that is asked for needs its operand
+    capi.check(lib.tfb_linear_backward_presplit(None, None, 0, ptr(ws[0]), ptr(ws[1]), ld, ptr(Y), ptr(G), ptr(dX),
+                                                None, None, batch, in_f, out_f, 1, stream_ptr()))
+    assert_device_ok()
+    assert np.array_equal(dX.cpu().numpy(), dX0)
+    assert lib.tfb_linear_backward_presplit(None, None, 0, ptr(ws[0]), ptr(ws[1]), ld, ptr(Y), ptr(G), ptr(dX),
+                                            ptr(dW), None, batch, in_f, out_f, 1, stream_ptr()) == -1   # TFB_ERR_INVALID_ARG: dW asked for without the planes of X
+
+
 @pytest.mark.parametrize("dtype", [capi.DTYPE_BF16, capi.DTYPE_F16])
 def test_linear_16bit(oracle, dtype):
     batch, in_f, out_f = 64, 784, 256
