@@ -1,7 +1,6 @@
 // Host side of the implicit-GEMM convolution: tap tables, operand preparation, tiling, launches,
 // and the extern "C" entry points of nn::Conv2d forward / backward.
 #include <cstring>
-#include <vector>
 
 #include "conv_kernel.cuh"
 #include "internal.hpp"
@@ -9,10 +8,6 @@
 namespace tfb {
 
 namespace {
-
-struct ConvShape {
-    int64_t N, Cin, H, W, Cout, kH, kW, sh, sw, ph, pw, dh, dw, outH, outW;
-};
 
 inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -196,6 +191,7 @@ int conv2d_forward(const float* x, const float* w, const float* bias, float* out
     int rc = check_shape(s);
     if (rc != TFB_OK) return rc;
     if (s.N == 0) return TFB_OK;
+    if (conv_tma_eligible(s, s.Cin)) return conv_tma_forward(x, w, bias, out, s, relu, stream);
     DeviceState* st = nullptr;
     rc = device_state(&st);
     if (rc != TFB_OK) return rc;
@@ -249,6 +245,18 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
         if (dW != nullptr) TFB_CUDA_OK(cudaMemsetAsync(dW, 0, (size_t)(s.Cout * s.Cin * khw) * 4, stream));
         if (db != nullptr) TFB_CUDA_OK(cudaMemsetAsync(db, 0, (size_t)s.Cout * 4, stream));
         return TFB_OK;
+    }
+    {
+        // Each product goes to the TMA-fed path or stays on the gather kernel by its own contraction.
+        const bool t_dx = dX != nullptr && conv_tma_eligible(s, s.Cout);
+        const bool t_w = (dW != nullptr || db != nullptr) && conv_tma_eligible(s, s.Cin);
+        if (t_dx || t_w) {
+            rc = conv_tma_backward(x, w, dY, t_dx ? dX : nullptr, t_w ? dW : nullptr, t_w ? db : nullptr, s, stream);
+            if (rc != TFB_OK) return rc;
+            if (t_dx) dX = nullptr;
+            if (t_w) dW = nullptr, db = nullptr;
+            if (dX == nullptr && dW == nullptr && db == nullptr) return TFB_OK;
+        }
     }
     // ---- scratch layout -------------------------------------------------------------------
     const int64_t d_taps = s.Cout * khw, d_ld = round_up(d_taps, 4), d_table = round_up(d_taps, 128);

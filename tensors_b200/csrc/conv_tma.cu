@@ -1,0 +1,425 @@
+// Stride-1 convolutions on the TMA-fed tcgen05 GEMM kernel.
+//
+// A pre-pass rewrites the activation tensor (NCHW) as NHWC TF32 hi / lo planes. In that layout the
+// slice of the im2col matrix that one K block needs — 32 channels of one filter tap for a rectangle
+// of output positions — is a single 4-D box of the tensor, shifted by the tap's offset, and the
+// padding halo is the box's out-of-range part, which the TMA unit fills with zeros. So the im2col
+// index map costs no instructions and the main loop is the plain GEMM pipeline:
+//
+//   forward          rows = positions, columns = Cout, K = (tap, Cin)       A: x planes   B: W[co][tap][ci]
+//   input gradient   rows = positions, columns = Cin,  K = (tap, Cout)      A: dY planes  B: W[ci][tap][co]
+//                    gather form: source row = y + pad - ki * dilation
+//   weight gradient  rows = Cout, columns = (tap, Cin), K = positions of all samples, split between CTAs
+//                    A: dY planes (MN-major boxes)  B: x planes shifted by the tap (MN-major boxes)
+//   bias gradient    column sums taken by the dY pre-pass
+//
+// Outputs are written NCHW (forward, input gradient) by the kernel's epilogue.
+#include <cstdlib>
+#include <cstring>
+
+#include "gemm_kernel.cuh"
+#include "internal.hpp"
+
+namespace tfb {
+
+namespace {
+
+inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+__device__ __forceinline__ float tf32_rna_c(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// src[n][c][p] (NCHW, p = y * W + x) -> hi / lo[n][p][cp] (NHWC, channels padded with zeros to cp).
+// One block transposes a 32-channel x 32-position tile through shared memory: reads are contiguous
+// in p, writes contiguous in c. If colsum != nullptr, colsum[(n * pblocks + pb) * cp + c] receives the
+// sum of the tile's 32 positions in ascending order (the bias-gradient partial sums).
+__global__ void nhwc_split_kernel(const float* __restrict__ src, int C, int P, int cp, float* __restrict__ hi,
+                                  float* __restrict__ lo, float* __restrict__ colsum) {
+    __shared__ float tile[32][33];
+    const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const float* s = src + (long long)n * C * P;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c = c0 + ty + 8 * k, p = p0 + tx;
+        tile[ty + 8 * k][tx] = (c < C && p < P) ? s[(long long)c * P + p] : 0.f;
+    }
+    __syncthreads();
+    const int c = c0 + tx;
+    if (c < cp) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int pl = ty + 8 * k, p = p0 + pl;
+            if (p < P) {
+                const float v = tile[tx][pl];
+                const float h = tf32_rna_c(v);
+                const long long o = ((long long)n * P + p) * cp + c;
+                hi[o] = h;
+                lo[o] = v - h;
+            }
+        }
+        if (colsum != nullptr && ty == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int pl = 0; pl < 32; ++pl) t += tile[tx][pl];
+            colsum[((long long)n * gridDim.x + blockIdx.x) * cp + c] = t;
+        }
+    }
+}
+
+// Filter planes for the spatial feed: out[j][tap][c] (c padded to cp) with
+//   forward (by_cin == 0): j = output channel, c = input channel
+//   gradient (by_cin == 1): j = input channel,  c = output channel
+// both reading W[co][ci][tap].
+__global__ void filter_planes_kernel(const float* __restrict__ W, int Cout, int Cin, int khw, int cp, int by_cin,
+                                     float* __restrict__ hi, float* __restrict__ lo) {
+    const int J = by_cin ? Cin : Cout, Cc = by_cin ? Cout : Cin;
+    const long long total = (long long)J * khw * cp;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cp);
+        const long long r = i / cp;
+        const int tap = (int)(r % khw), j = (int)(r / khw);
+        float v = 0.f;
+        if (c < Cc) {
+            const int co = by_cin ? c : j, ci = by_cin ? j : c;
+            v = W[((long long)co * Cin + ci) * khw + tap];
+        }
+        const float h = tf32_rna_c(v);
+        hi[i] = h;
+        lo[i] = v - h;
+    }
+}
+
+// dW[co][ci][tap] = sum over splits (ascending) of partial[s][co][tap * cp32 + ci].
+__global__ void wgrad_planes_reduce_kernel(const float* __restrict__ partial, int splits, long long split_stride,
+                                           long long ld, int Cout, int Cin, int khw, int cp32,
+                                           float* __restrict__ dW) {
+    const long long total = (long long)Cout * Cin * khw;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int tap = (int)(i % khw);
+        const long long r = i / khw;
+        const int ci = (int)(r % Cin), co = (int)(r / Cin);
+        const float* p = partial + (long long)co * ld + (long long)tap * cp32 + ci;
+        float s = 0.f;
+        for (int k = 0; k < splits; ++k) s += p[(long long)k * split_stride];
+        dW[i] = s;
+    }
+}
+
+// out[g][c] = sum of partial[b][c] over the rows b = g, g + groups, g + 2 * groups, ... in ascending
+// order (groups = gridDim.y * 8): a block covers 32 columns and 8 row groups. Run once with many groups
+// and once more with 8 to finish; the order of every addition is fixed by the launch shape.
+__global__ void colsum_stage_kernel(const float* __restrict__ partial, long long blocks, int cols, int ld,
+                                    float* __restrict__ out, int out_ld) {
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    const long long groups = (long long)gridDim.y * 8;
+    const long long g = (long long)blockIdx.y * 8 + threadIdx.y;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (long long b = g; b < blocks; b += groups) s += partial[b * ld + c];
+    out[g * out_ld + c] = s;
+}
+
+// db[c] = sum of the 8 * stage_blocks group sums in ascending order.
+__global__ void colsum_last_kernel(const float* __restrict__ sums, int groups, int cols, int ld,
+                                   float* __restrict__ out) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    float t = 0.f;
+    for (int g = 0; g < groups; ++g) t += sums[(long long)g * ld + c];
+    out[c] = t;
+}
+
+template <int BN, int STAGES, bool PAIR, int CONV>
+int launch_feed(const CUtensorMap maps[5], const GemmArgs& args, int workers, cudaStream_t stream) {
+    using S = GemmSmem<kKindTF32x3, BN, STAGES, PAIR>;
+    static_assert(S::TOTAL <= 232448, "stage ring + staging exceed the 227 KB shared-memory limit");
+    constexpr bool MN = (CONV == kConvWgrad);
+    auto kern = gemm_tcgen05_kernel<kKindTF32x3, BN, STAGES, MN, MN, PAIR, CONV>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    TFB_CUDA_OK(cudaGetDevice(&dev));
+    if (!attr_set[dev]) {
+        TFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(PAIR ? 2 * workers : workers));
+    cfg.blockDim = dim3((unsigned)gemm_threads(kKindTF32x3));
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TFB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], args));
+    return TFB_OK;
+}
+
+unsigned grid_1d(long long total) {
+    const long long blocks = (total + 255) / 256;
+    return (unsigned)(blocks < 1184 ? (blocks < 1 ? 1 : blocks) : 1184);
+}
+
+int pow2_ceil_log2(int64_t v) {
+    int l = 0;
+    while ((1ll << l) < v) ++l;
+    return l;
+}
+
+int to_nhwc_planes(const float* src, int64_t N, int64_t C, int64_t P, int64_t cp, float* hi, float* lo,
+                   float* colsum, cudaStream_t stream) {
+    dim3 grid((unsigned)((P + 31) / 32), (unsigned)((cp + 31) / 32), (unsigned)N), block(32, 8);
+    nhwc_split_kernel<<<grid, block, 0, stream>>>(src, (int)C, (int)P, (int)cp, hi, lo, colsum);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+// 4-D maps (channel, x, y, sample) over NHWC hi / lo planes with a box of 32 channels x bw x bh positions.
+int plane_maps(CUtensorMap out[2], const float* hi, const float* lo, int64_t cp, int64_t W, int64_t H, int64_t N,
+               uint32_t bw, uint32_t bh, bool atom32) {
+    const uint64_t dims[4] = {(uint64_t)cp, (uint64_t)W, (uint64_t)H, (uint64_t)N};
+    const uint64_t strides[3] = {(uint64_t)cp * 4, (uint64_t)(W * cp) * 4, (uint64_t)(H * W * cp) * 4};
+    const uint32_t box[4] = {32, bw, bh, 1};
+    int rc = make_map_nd(&out[0], hi, 4, dims, strides, box, atom32);
+    if (rc != TFB_OK) return rc;
+    return make_map_nd(&out[1], lo, 4, dims, strides, box, atom32);
+}
+
+constexpr int kBiasStageBlocks = 16;   // x 8 row groups = 128 partial sums per column after the first stage
+
+struct SpatialCall {
+    const float* src_hi; const float* src_lo;   // NHWC planes of the tensor the taps are gathered from
+    int64_t src_c, src_cp, src_H, src_W;        // its channels (contraction), padded channels, extent
+    const float* f_hi; const float* f_lo;       // filter planes [J][taps][src_cp]
+    int64_t J;                                  // output channels of this product
+    int64_t out_H, out_W;                       // position grid = extent of the stored tensor
+    int ay0, ay_step, ax0, ax_step;
+    float* dst; const float* bias; bool relu;
+};
+
+int run_spatial(const SpatialCall& c, const ConvShape& s, const DeviceState* st, cudaStream_t stream) {
+    const int64_t khw = s.kH * s.kW;
+    const int cblks = (int)((c.src_c + 31) / 32);
+    int env_pair = -1;
+    if (const char* e = getenv("TFB_CONV_PAIR")) env_pair = atoi(e);   // debugging override
+    const int tw_log2 = pow2_ceil_log2(c.out_W < 128 ? c.out_W : 128);
+    const int tw = 1 << tw_log2, th = 128 / tw;
+    const int64_t tiles_x = (c.out_W + tw - 1) / tw;
+    const int64_t single_tiles = s.N * tiles_x * ((c.out_H + th - 1) / th);
+    const bool pair = c.J > 64 && (env_pair >= 0 ? env_pair != 0 : single_tiles >= st->sm_count);
+    const int cg = pair ? 2 : 1;
+    const int bn = c.J <= 64 ? 64 : 128;
+    const int64_t tiles_y = (c.out_H + cg * th - 1) / (cg * th);
+
+    GemmArgs a;
+    memset(&a, 0, sizeof(a));
+    a.tiles_m = (int)(s.N * tiles_x * tiles_y);
+    a.tiles_n = (int)((c.J + bn - 1) / bn);
+    a.num_tiles = a.tiles_m * a.tiles_n;
+    a.M = a.tiles_m * cg * kBlockM; a.N = (int)c.J; a.K = (int)(khw * cblks * 32);
+    a.k_blocks = (int)(khw * cblks);
+    a.chunk_kb = 8; a.split_k = 1; a.kb_per_split = a.k_blocks; a.split_stride = 0;
+    if (const char* e = getenv("TFB_CONV_CHUNK_KB")) a.chunk_kb = atoi(e) > 0 ? atoi(e) : 8;   // debugging override
+    if (const char* e = getenv("TFB_CONV_DBG")) a.cv.dbg = atoi(e);
+    a.group_m = 16;
+    a.C = c.dst; a.ldc = 0; a.out_type = kOutF32;
+    a.bias = c.bias; a.bias_mode = c.bias != nullptr ? kBiasPerCol : kBiasNone; a.relu = c.relu ? 1 : 0;
+    a.c_tma = 0; a.status = st->status;
+    a.cv.tw_log2 = tw_log2; a.cv.th = th;
+    a.cv.tiles_x = (int)tiles_x; a.cv.tiles_y = (int)tiles_y;
+    a.cv.out_h = (int)c.out_H; a.cv.out_w = (int)c.out_W;
+    a.cv.cblks = cblks; a.cv.kw = (int)s.kW; a.cv.taps = (int)khw;
+    a.cv.ay0 = c.ay0; a.cv.ay_step = c.ay_step; a.cv.ax0 = c.ax0; a.cv.ax_step = c.ax_step;
+    a.cv.n_samples = (int)s.N;
+
+    CUtensorMap maps[5];
+    memset(maps, 0, sizeof(maps));
+    int rc = plane_maps(&maps[0], c.src_hi, c.src_lo, c.src_cp, c.src_W, c.src_H, s.N, (uint32_t)tw, (uint32_t)th, false);
+    if (rc != TFB_OK) return rc;
+    const uint64_t fdims[3] = {(uint64_t)c.src_cp, (uint64_t)khw, (uint64_t)c.J};
+    const uint64_t fstr[2] = {(uint64_t)c.src_cp * 4, (uint64_t)(khw * c.src_cp) * 4};
+    const uint32_t fbox[3] = {32, 1, (uint32_t)(pair ? bn / 2 : bn)};
+    rc = make_map_nd(&maps[2], c.f_hi, 3, fdims, fstr, fbox, false);
+    if (rc != TFB_OK) return rc;
+    rc = make_map_nd(&maps[3], c.f_lo, 3, fdims, fstr, fbox, false);
+    if (rc != TFB_OK) return rc;
+    maps[4] = maps[0];   // no TMA store on this path
+
+    if (pair) {
+        const int max_pairs = st->sm_count / 2;
+        const int pairs = a.num_tiles < max_pairs ? a.num_tiles : max_pairs;
+        return launch_feed<128, 4, true, kConvSpatial>(maps, a, pairs, stream);
+    }
+    const int grid = a.num_tiles < st->sm_count ? a.num_tiles : st->sm_count;
+    if (bn == 64) return launch_feed<64, 4, false, kConvSpatial>(maps, a, grid, stream);
+    return launch_feed<128, 3, false, kConvSpatial>(maps, a, grid, stream);
+}
+
+}  // namespace
+
+bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels) {
+    int mode = 1;
+    if (const char* e = getenv("TFB_CONV_TMA")) mode = atoi(e);   // debugging override: 0 never, 2 whenever possible
+    if (mode == 0) return false;
+    // A K block holds 32 channels of one tap: with few channels most of it is zero fill and the
+    // gather kernel, which packs taps densely, is faster.
+    if (mode == 1 && contraction_channels < 16) return false;
+    // Stride 1 only (a box of positions must be a box of the source); tensor-map extents and
+    // 32-bit tile arithmetic bound the rest.
+    return s.sh == 1 && s.sw == 1 && s.N >= 1 && s.N < 65536 && s.H < (1 << 15) && s.W < (1 << 15) &&
+           s.Cin < (1 << 15) && s.Cout < (1 << 15) && s.kH * s.kW * ((s.Cin + 31) / 32) < (1 << 20) &&
+           s.kH * s.kW * ((s.Cout + 31) / 32) < (1 << 20);
+}
+
+int conv_tma_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
+                     cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    const int64_t khw = s.kH * s.kW, P = s.H * s.W, cp = round_up(s.Cin, 4);
+    const size_t x_bytes = align256((size_t)(2 * s.N * P * cp) * 4);
+    const size_t f_bytes = align256((size_t)(2 * s.Cout * khw * cp) * 4);
+    void* ws_v = nullptr;
+    rc = workspace_get(stream, x_bytes + f_bytes, &ws_v);
+    if (rc != TFB_OK) return rc;
+    float* x_hi = static_cast<float*>(ws_v);
+    float* x_lo = x_hi + s.N * P * cp;
+    float* f_hi = reinterpret_cast<float*>(static_cast<uint8_t*>(ws_v) + x_bytes);
+    float* f_lo = f_hi + s.Cout * khw * cp;
+    rc = to_nhwc_planes(x, s.N, s.Cin, P, cp, x_hi, x_lo, nullptr, stream);
+    if (rc != TFB_OK) return rc;
+    const long long ftotal = (long long)s.Cout * khw * cp;
+    filter_planes_kernel<<<grid_1d(ftotal), 256, 0, stream>>>(
+        w, (int)s.Cout, (int)s.Cin, (int)khw, (int)cp, 0, f_hi, f_lo);
+    TFB_CUDA_OK(cudaGetLastError());
+    SpatialCall c;
+    c.src_hi = x_hi; c.src_lo = x_lo; c.src_c = s.Cin; c.src_cp = cp; c.src_H = s.H; c.src_W = s.W;
+    c.f_hi = f_hi; c.f_lo = f_lo; c.J = s.Cout; c.out_H = s.outH; c.out_W = s.outW;
+    c.ay0 = (int)-s.ph; c.ay_step = (int)s.dh; c.ax0 = (int)-s.pw; c.ax_step = (int)s.dw;
+    c.dst = out; c.bias = bias; c.relu = relu;
+    return run_spatial(c, s, st, stream);
+}
+
+int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX, float* dW, float* db,
+                      const ConvShape& s, cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    const int64_t khw = s.kH * s.kW, P = s.H * s.W, Po = s.outH * s.outW;
+    const int64_t cp = round_up(s.Cin, 4), cop = round_up(s.Cout, 4);
+    const int64_t pblocks = (Po + 31) / 32;
+    const bool want_dx = dX != nullptr, want_dw = dW != nullptr, want_db = db != nullptr;
+
+    // weight-gradient tiling
+    const int cblks = (int)((s.Cin + 31) / 32), cp32 = cblks * 32;
+    const int64_t ncols = khw * cp32, ld_part = ncols;
+    const int bn_w = 128;
+    const int kw_log2 = pow2_ceil_log2(s.outW < 32 ? s.outW : 32);
+    const int kbw = 1 << kw_log2, kbh = 32 / kbw;
+    const int64_t kblk_x = (s.outW + kbw - 1) / kbw, kblk_y = (s.outH + kbh - 1) / kbh;
+    const int64_t k_blocks = s.N * kblk_x * kblk_y;
+    const int64_t w_tiles_m = (s.Cout + kBlockM - 1) / kBlockM, w_tiles_n = (ncols + bn_w - 1) / bn_w;
+    int64_t splits = st->sm_count / (w_tiles_m * w_tiles_n);
+    if (splits > k_blocks / 8) splits = k_blocks / 8;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    const int64_t kb_per = (k_blocks + splits - 1) / splits;
+    splits = (k_blocks + kb_per - 1) / kb_per;
+    const int64_t rows_per_split = w_tiles_m * kBlockM;
+
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
+    const size_t o_dy = take((size_t)(2 * s.N * Po * cop) * 4);
+    const size_t o_bsum = want_db ? take((size_t)(s.N * pblocks * cop) * 4) : 0;
+    const size_t o_bstage = want_db ? take((size_t)(kBiasStageBlocks * 8 * cop) * 4) : 0;
+    const size_t o_fd = want_dx ? take((size_t)(2 * s.Cin * khw * cop) * 4) : 0;
+    const size_t o_x = want_dw ? take((size_t)(2 * s.N * P * cp) * 4) : 0;
+    const size_t o_part = want_dw ? take((size_t)(splits * rows_per_split * ld_part) * 4) : 0;
+    void* ws_v = nullptr;
+    rc = workspace_get(stream, off + 256, &ws_v);
+    if (rc != TFB_OK) return rc;
+    uint8_t* ws = static_cast<uint8_t*>(ws_v);
+
+    float* dy_hi = reinterpret_cast<float*>(ws + o_dy);
+    float* dy_lo = dy_hi + s.N * Po * cop;
+    float* bsum = want_db ? reinterpret_cast<float*>(ws + o_bsum) : nullptr;
+    rc = to_nhwc_planes(dY, s.N, s.Cout, Po, cop, dy_hi, dy_lo, bsum, stream);
+    if (rc != TFB_OK) return rc;
+    if (want_db) {
+        float* stage = reinterpret_cast<float*>(ws + o_bstage);
+        colsum_stage_kernel<<<dim3((unsigned)((s.Cout + 31) / 32), kBiasStageBlocks), dim3(32, 8), 0, stream>>>(
+            bsum, s.N * pblocks, (int)s.Cout, (int)cop, stage, (int)cop);
+        TFB_CUDA_OK(cudaGetLastError());
+        colsum_last_kernel<<<(unsigned)((s.Cout + 127) / 128), 128, 0, stream>>>(stage, kBiasStageBlocks * 8, (int)s.Cout,
+                                                                                 (int)cop, db);
+        TFB_CUDA_OK(cudaGetLastError());
+    }
+    if (want_dx) {
+        float* f_hi = reinterpret_cast<float*>(ws + o_fd);
+        float* f_lo = f_hi + s.Cin * khw * cop;
+        const long long ftotal = (long long)s.Cin * khw * cop;
+        filter_planes_kernel<<<grid_1d(ftotal), 256, 0, stream>>>(
+            w, (int)s.Cout, (int)s.Cin, (int)khw, (int)cop, 1, f_hi, f_lo);
+        TFB_CUDA_OK(cudaGetLastError());
+        SpatialCall c;
+        c.src_hi = dy_hi; c.src_lo = dy_lo; c.src_c = s.Cout; c.src_cp = cop; c.src_H = s.outH; c.src_W = s.outW;
+        c.f_hi = f_hi; c.f_lo = f_lo; c.J = s.Cin; c.out_H = s.H; c.out_W = s.W;
+        c.ay0 = (int)s.ph; c.ay_step = (int)-s.dh; c.ax0 = (int)s.pw; c.ax_step = (int)-s.dw;
+        c.dst = dX; c.bias = nullptr; c.relu = false;
+        rc = run_spatial(c, s, st, stream);
+        if (rc != TFB_OK) return rc;
+    }
+    if (want_dw) {
+        float* x_hi = reinterpret_cast<float*>(ws + o_x);
+        float* x_lo = x_hi + s.N * P * cp;
+        rc = to_nhwc_planes(x, s.N, s.Cin, P, cp, x_hi, x_lo, nullptr, stream);
+        if (rc != TFB_OK) return rc;
+        float* partial = reinterpret_cast<float*>(ws + o_part);
+
+        GemmArgs a;
+        memset(&a, 0, sizeof(a));
+        a.M = (int)s.Cout; a.N = (int)ncols; a.K = (int)(k_blocks * 32);
+        a.tiles_m = (int)w_tiles_m; a.tiles_n = (int)w_tiles_n; a.num_tiles = a.tiles_m * a.tiles_n;
+        a.k_blocks = (int)k_blocks; a.chunk_kb = 8;
+        a.split_k = (int)splits; a.kb_per_split = (int)kb_per;
+        a.split_stride = rows_per_split * ld_part;
+        a.group_m = 16;
+        a.C = partial; a.ldc = ld_part; a.out_type = kOutF32;
+        a.bias = nullptr; a.bias_mode = kBiasNone; a.relu = 0; a.c_tma = 1; a.status = st->status;
+        a.cv.cblks = cblks; a.cv.kw = (int)s.kW; a.cv.taps = (int)khw;
+        a.cv.ay0 = (int)-s.ph; a.cv.ay_step = (int)s.dh; a.cv.ax0 = (int)-s.pw; a.cv.ax_step = (int)s.dw;
+        a.cv.kblk_w_log2 = kw_log2; a.cv.kblk_h = kbh; a.cv.kblk_x = (int)kblk_x; a.cv.kblk_y = (int)kblk_y;
+        a.cv.n_samples = (int)s.N;
+
+        CUtensorMap maps[5];
+        memset(maps, 0, sizeof(maps));
+        rc = plane_maps(&maps[0], dy_hi, dy_lo, cop, s.outW, s.outH, s.N, (uint32_t)kbw, (uint32_t)kbh, true);
+        if (rc != TFB_OK) return rc;
+        rc = plane_maps(&maps[2], x_hi, x_lo, cp, s.W, s.H, s.N, (uint32_t)kbw, (uint32_t)kbh, true);
+        if (rc != TFB_OK) return rc;
+        rc = make_map(&maps[4], TFB_DTYPE_F32, partial, (uint64_t)ncols, (uint64_t)(splits * rows_per_split),
+                      (uint64_t)ld_part * 4, 32, 32);
+        if (rc != TFB_OK) return rc;
+        const long long units = (long long)a.num_tiles * a.split_k;
+        const int grid = units < st->sm_count ? (int)units : st->sm_count;
+        rc = launch_feed<128, 3, false, kConvWgrad>(maps, a, grid, stream);
+        if (rc != TFB_OK) return rc;
+        const long long total = (long long)s.Cout * s.Cin * khw;
+        wgrad_planes_reduce_kernel<<<grid_1d(total), 256, 0, stream>>>(
+            partial, (int)splits, rows_per_split * ld_part, ld_part, (int)s.Cout, (int)s.Cin, (int)khw, cp32, dW);
+        TFB_CUDA_OK(cudaGetLastError());
+    }
+    return TFB_OK;
+}
+
+}  // namespace tfb

@@ -67,6 +67,31 @@ int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint
     return TFB_OK;
 }
 
+int make_map_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                const uint32_t* box, bool atom32) {
+    int rc0 = resolve_encoder();
+    if (rc0 != TFB_OK) return rc0;
+    if (rank < 2 || rank > 5) return fail(TFB_ERR_INVALID_ARG, "tensor map rank %d", rank);
+    cuuint64_t gdim[5];
+    cuuint64_t gstride[4];
+    cuuint32_t bx[5], estr[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        estr[i] = 1;
+        if (i > 0) gstride[i - 1] = strides_bytes[i - 1];
+    }
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gdim,
+                          gstride, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TFB_ERR_CUDA, "cuTensorMapEncodeTiled (rank %d) failed with %d (dims %llu %llu %llu, box %u %u %u)",
+                    rank, (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                    (unsigned long long)(rank > 2 ? dims[2] : 0), box[0], box[1], rank > 2 ? box[2] : 0u);
+    return TFB_OK;
+}
+
 namespace {
 
 // ---------------------------------------------------------------------------

@@ -60,6 +60,28 @@ enum GemmKind : int { kKind16 = 0, kKindTF32x3 = 2 };
 enum OutType : int { kOutF32 = 0, kOutF16 = 1, kOutBF16 = 2 };
 enum BiasMode : int { kBiasNone = 0, kBiasPerCol = 1, kBiasPerRow = 2 };
 
+// Convolution feeds of the same kernel (CONV template parameter). Both tensors of a convolution are
+// read as NHWC hi / lo planes through 4-D tensor maps (channel, x, y, sample), so a box of positions
+// shifted by a filter tap is one TMA load and the padding halo is the load's out-of-range zero fill.
+//   kConvSpatial (forward, input gradient; stride 1): rows = a th x tw rectangle of output positions
+//     of one sample, columns = output channels, K blocks = (tap, 32 input channels). A from the
+//     activation planes, B from weights laid out [column][tap][channel]; the result is stored NCHW.
+//   kConvWgrad (weight gradient; stride 1): rows = output channels, columns = (tap, input channel),
+//     K blocks = 32 positions (kblk_h x kblk_w) of one sample; both operands MN-major boxes.
+enum ConvFeed : int { kConvNone = 0, kConvSpatial = 1, kConvWgrad = 2 };
+struct ConvGeom {
+    int tw_log2, th;                  // spatial tile: th rows of 2^tw_log2 positions (128 per CTA)
+    int tiles_x, tiles_y;             // scheduled tiles per sample along x and y
+    int out_h, out_w;                 // extent of the position grid (= of the stored tensor)
+    int cblks;                        // 32-channel blocks per tap
+    int kw, taps;                     // filter width, number of taps (tap = ki * kw + kj)
+    int ay0, ay_step, ax0, ax_step;   // source row = position row + ay0 + ki * ay_step (x alike)
+    int kblk_w_log2, kblk_h;          // kConvWgrad: K block = kblk_h rows of 2^kblk_w_log2 positions
+    int kblk_x, kblk_y;               // K blocks per sample along x and y
+    int n_samples;
+    int dbg;
+};
+
 struct GemmArgs {
     int M, N, K;
     int tiles_m, tiles_n, num_tiles, k_blocks;
@@ -77,6 +99,7 @@ struct GemmArgs {
     int is_bf16;          // kKind16 only: 1 = bf16 operands, 0 = f16
     int c_tma;            // 1: FP32 output goes through the TMA-store path (tmC is valid)
     int* status;          // device error word (0 = ok)
+    ConvGeom cv;          // only read when CONV != kConvNone
 };
 
 constexpr int kBlockM = 128;
@@ -209,7 +232,7 @@ __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t cta
         ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
-template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR>
+template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR, int CONV = kConvNone>
 __global__ void __launch_bounds__(gemm_threads(KIND), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
@@ -232,6 +255,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr int EPI_WARPS = gemm_epi_warps(KIND);
     constexpr int COLS = BN / (EPI_WARPS / 4);   // accumulator columns handled per epilogue thread
     static_assert(COLS % 32 == 0, "each epilogue thread handles whole 32-column groups");
+    static_assert(CONV == kConvNone || TF32, "the convolution feeds exist for FP32 operands only");
+    static_assert(CONV != kConvSpatial || (!A_MN && !B_MN), "spatial feed: both operands K-major");
+    static_assert(CONV != kConvWgrad || (A_MN && B_MN), "weight-gradient feed: both operands MN-major");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -298,6 +324,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 unit_decode(u, args, t, split, ub0, ub1);
                 tile_coords(t, args, tm, tn);
                 const int m0 = tm * TILE_M + (int)rank * kBlockM, n0 = tn * BN + (int)rank * BN_CTA;
+                // Convolution feeds: where this tile sits in the position grid / the column boxes.
+                const ConvGeom& cv = args.cv;
+                [[maybe_unused]] int cs_n = 0, cs_x0 = 0, cs_y0 = 0;                  // kConvSpatial
+                [[maybe_unused]] int cw_c[BN_CTA / 32], cw_dx[BN_CTA / 32], cw_dy[BN_CTA / 32], cw_ok[BN_CTA / 32];   // kConvWgrad
+                if constexpr (CONV == kConvSpatial) {
+                    const int tx = tm % cv.tiles_x, r = tm / cv.tiles_x;
+                    const int ty = r % cv.tiles_y;
+                    cs_n = r / cv.tiles_y;
+                    cs_x0 = tx << cv.tw_log2;
+                    cs_y0 = (ty * CG + (int)rank) * cv.th;
+                }
+                if constexpr (CONV == kConvWgrad) {
+#pragma unroll
+                    for (int i = 0; i < BN_CTA / 32; ++i) {
+                        const int jb = (n0 >> 5) + i;
+                        const int tap = jb / cv.cblks, ki = tap / cv.kw;
+                        cw_c[i] = (jb - tap * cv.cblks) * 32;
+                        cw_dy[i] = cv.ay0 + ki * cv.ay_step;
+                        cw_dx[i] = cv.ax0 + (tap - ki * cv.kw) * cv.ax_step;
+                        cw_ok[i] = tap < cv.taps;
+                    }
+                }
                 for (int kb = ub0; kb < ub1; ++kb) {
                     ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, args.status, kDevTimeoutEmpty);
                     if (!ok) break;
@@ -315,6 +363,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         if constexpr (PAIR) tma_load_2d_pair(dst, map, x, y, fb);
                         else tma_load_2d(dst, map, x, y, fb);
                     };
+                    if constexpr (CONV == kConvSpatial) {
+                        const int tap = kb / cv.cblks, c0 = (kb - tap * cv.cblks) * 32;
+                        const int ki = tap / cv.kw, kj = tap - ki * cv.kw;
+                        const int sy = cs_y0 + cv.ay0 + ki * cv.ay_step, sx = cs_x0 + cv.ax0 + kj * cv.ax_step;
+                        if (cv.dbg & 2) {
+                            tma_load_4d<PAIR>(a_hi, &tmA, 0, 0, 0, 0, fb);
+                            tma_load_4d<PAIR>(a_lo, &tmA2, 0, 0, 0, 0, fb);
+                        } else {
+                        tma_load_4d<PAIR>(a_hi, &tmA, c0, sx, sy, cs_n, fb);
+                        tma_load_4d<PAIR>(a_lo, &tmA2, c0, sx, sy, cs_n, fb);
+                        }
+                        if (cv.dbg & 4) {
+                            tma_load_3d<PAIR>(b_hi, &tmB, 0, 0, 0, fb);
+                            tma_load_3d<PAIR>(b_lo, &tmB2, 0, 0, 0, fb);
+                        } else {
+                        tma_load_3d<PAIR>(b_hi, &tmB, c0, tap, n0, fb);
+                        tma_load_3d<PAIR>(b_lo, &tmB2, c0, tap, n0, fb);
+                        }
+                    } else if constexpr (CONV == kConvWgrad) {
+                        const int per = cv.kblk_x * cv.kblk_y;
+                        const int n = kb / per, r = kb - n * per;
+                        const int by = r / cv.kblk_x, bx = r - by * cv.kblk_x;
+                        const int px = bx << cv.kblk_w_log2, py = by * cv.kblk_h;
+#pragma unroll
+                        for (int i = 0; i < kBlockM / T_MN; ++i) {
+                            tma_load_4d<PAIR>(a_hi + i * (BK * 128), &tmA, m0 + i * T_MN, px, py, n, fb);
+                            tma_load_4d<PAIR>(a_lo + i * (BK * 128), &tmA2, m0 + i * T_MN, px, py, n, fb);
+                        }
+#pragma unroll
+                        for (int i = 0; i < BN_CTA / T_MN; ++i) {
+                            // column boxes past the last tap read a sample index beyond the tensor: zeros
+                            const int nn = cw_ok[i] ? n : cv.n_samples;
+                            tma_load_4d<PAIR>(b_hi + i * (BK * 128), &tmB, cw_c[i], px + cw_dx[i], py + cw_dy[i], nn, fb);
+                            tma_load_4d<PAIR>(b_lo + i * (BK * 128), &tmB2, cw_c[i], px + cw_dx[i], py + cw_dy[i], nn, fb);
+                        }
+                    } else {
                     if constexpr (!A_MN) {
                         load(a_hi, &tmA, k0, m0);
                         if constexpr (TF32) load(a_lo, &tmA2, k0, m0);
@@ -334,6 +418,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             load(b_hi + i * (BK * 128), &tmB, n0 + i * T_MN, k0);
                             if constexpr (TF32) load(b_lo + i * (BK * 128), &tmB2, n0 + i * T_MN, k0);
                         }
+                    }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
@@ -405,6 +490,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const uint32_t b_lo = b_hi + S::B_TILE;
 #pragma unroll
                         for (int j = 0; j < KSTEPS; ++j) {
+                            if (CONV != kConvNone && (args.cv.dbg & 8) && !(kb == kb0 && j == 0)) continue;
                             const uint32_t acc = (kb > kb0 || j > 0) ? 1u : 0u;
                             const uint64_t da = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_SWZ);
                             const uint64_t db = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_SWZ);
@@ -481,16 +567,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     release(buf);
                 }
                 if (!ok) break;
+                if constexpr (CONV == kConvSpatial) {
+                    // Row r of the CTA's 128 is position (y0 + r / tw, x0 + r % tw) of sample n; column j
+                    // goes to dst[n][j][y][x] (NCHW): lanes are consecutive x, so each store
+                    // instruction writes whole lines.
+                    const ConvGeom& cv = args.cv;
+                    const int tx = tm % cv.tiles_x, rr = tm / cv.tiles_x;
+                    const int ty = rr % cv.tiles_y, n = rr / cv.tiles_y;
+                    const int r = q * 32 + lane;
+                    const int oy = (ty * CG + (int)rank) * cv.th + (r >> cv.tw_log2);
+                    const int ox = (tx << cv.tw_log2) + (r & ((1 << cv.tw_log2) - 1));
+                    const bool valid = oy < cv.out_h && ox < cv.out_w;
+                    const long long plane = (long long)cv.out_h * cv.out_w;
+                    float* dst = static_cast<float*>(args.C) + (long long)n * args.N * plane +
+                                 (long long)oy * cv.out_w + ox;
 #pragma unroll
-                for (int c = 0; c < COLS / 32; ++c) {
-                    const int col0 = n0 + c * 32;
-                    if (col0 < args.N && (c_tma ? (row0 - row_shift) < args.M : row_ok)) {
-                        float v[32];
+                    for (int c = 0; c < COLS / 32; ++c) {
+                        const int col0 = n0 + c * 32;
+                        if (col0 < args.N) {
+                            float v[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
-                        epilogue_apply32(v, args, col0, row_bias);
-                        if (c_tma) epilogue_store32_tma<S::STAGING_BUFS>(v, &tmC, staging, stage_buf, lane, row0, col0);
-                        else epilogue_store32(v, args, row, col0);
+                            for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
+                            epilogue_apply32(v, args, col0, 0.f);
+                            if (valid && !(cv.dbg & 1)) {
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    if (col0 + i < args.N) dst[(long long)(col0 + i) * plane] = v[i];
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < COLS / 32; ++c) {
+                        const int col0 = n0 + c * 32;
+                        if (col0 < args.N && (c_tma ? (row0 - row_shift) < args.M : row_ok)) {
+                            float v[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
+                            epilogue_apply32(v, args, col0, row_bias);
+                            if (c_tma) epilogue_store32_tma<S::STAGING_BUFS>(v, &tmC, staging, stage_buf, lane, row0, col0);
+                            else epilogue_store32(v, args, row, col0);
+                        }
                     }
                 }
             } else {

@@ -77,6 +77,11 @@ size_t gemm_workspace_bytes(const GemmCall& call, int sm_count);
 int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint64_t outer,
              uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool atom32 = false);
 
+// FP32 tensor map of rank 2..5: dims[0] is the contiguous dimension, strides_bytes[i] is the stride of
+// dims[i + 1] (multiples of 16), box the tile; 128-byte swizzle (with 32-byte atoms if atom32).
+int make_map_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                const uint32_t* box, bool atom32);
+
 // Splits a row-major FP32 matrix (rows x cols, leading dimension ld) into TF32 hi / lo
 // planes with leading dimension ld_out (multiple of 4, padding zero-filled).
 int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
@@ -90,5 +95,21 @@ int linear_forward(const void* X, const void* W, const float* bias, void* Y, int
 int linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
                     float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
                     cudaStream_t stream);
+
+// ---------------------------------------------------------------------------
+// nn::Conv2d (conv.cu: gather kernel, entry points; conv_tma.cu: stride-1 path on the GEMM kernel)
+// ---------------------------------------------------------------------------
+struct ConvShape {
+    int64_t N, Cin, H, W, Cout, kH, kW, sh, sw, ph, pw, dh, dw, outH, outW;
+};
+// True when a product of this convolution should run on the TMA-fed path: stride 1, extents within
+// tensor-map limits, and enough channels in the contraction (forward and weight gradient: Cin; input
+// gradient: Cout) to fill the 32-channel K blocks.
+bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels);
+int conv_tma_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
+                     cudaStream_t stream);
+// dX, dW, db may each be null.
+int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX, float* dW, float* db,
+                      const ConvShape& s, cudaStream_t stream);
 
 }  // namespace tfb

@@ -181,6 +181,41 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
+// 3-D and 4-D tiled loads (x innermost, 16-byte rule as above; the outer coordinates may lie outside
+// the tensor, where the load delivers zeros). PAIR selects the form a CTA pair uses.
+template <bool PAIR>
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* desc, int x, int y, int z,
+                                            uint32_t bar) {
+    if constexpr (PAIR)
+        asm volatile(
+            "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%2, %3, %4}], [%5];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(x), "r"(y), "r"(z), "r"(bar)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%2, %3, %4}], [%5];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(x), "r"(y), "r"(z), "r"(bar)
+            : "memory");
+}
+template <bool PAIR>
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* desc, int x, int y, int z, int w,
+                                            uint32_t bar) {
+    if constexpr (PAIR)
+        asm volatile(
+            "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%2, %3, %4, %5}], [%6];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+            : "memory");
+    else
+        asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+            " [%0], [%1, {%2, %3, %4, %5}], [%6];"
+            ::"r"(dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+            : "memory");
+}
+
 // 2-D tiled store shared -> global (bulk-group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* desc, uint32_t src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

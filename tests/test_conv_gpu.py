@@ -1,5 +1,7 @@
 """Parity of the implicit-GEMM Conv2d (forward, dgrad, wgrad, bias gradient) with the oracle, with the
 reference's own known answers and golden outputs, and the bit-exact im2col index map."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -43,7 +45,26 @@ def conv_backward(x, w, g, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
     return gi.cpu().numpy(), gw.cpu().numpy(), gb.cpu().numpy()
 
 
-def test_reference_known_answers():
+@pytest.fixture(params=["default", "tma_feed", "gather_kernel"])
+def feed(request):
+    """By default a stride-1 product with at least 16 contraction channels runs on the TMA-fed GEMM
+    kernel and everything else on the kernel with software gather producers. TFB_CONV_TMA=2 sends every
+    stride-1 product to the former, TFB_CONV_TMA=0 everything to the latter, so both get every case."""
+    old = os.environ.get("TFB_CONV_TMA")
+    if request.param == "gather_kernel":
+        os.environ["TFB_CONV_TMA"] = "0"
+    elif request.param == "tma_feed":
+        os.environ["TFB_CONV_TMA"] = "2"
+    else:
+        os.environ.pop("TFB_CONV_TMA", None)
+    yield request.param
+    if old is None:
+        os.environ.pop("TFB_CONV_TMA", None)
+    else:
+        os.environ["TFB_CONV_TMA"] = old
+
+
+def test_reference_known_answers(feed):
     # nn/conv2d_forward_test.cpp:112-137 and nn/conv2d_backward_test.cpp:110-160
     x = np.array([1, 2, 3, 4], np.float32).reshape(1, 1, 2, 2)
     w = np.array([2.0], np.float32).reshape(1, 1, 1, 1)
@@ -55,7 +76,7 @@ def test_reference_known_answers():
     np.testing.assert_allclose(gb.ravel(), [1.0], rtol=1e-4)
 
 
-def test_reference_backward_test_patterns(oracle):
+def test_reference_backward_test_patterns(oracle, feed):
     # the fill patterns of nn/conv2d_backward_test.cpp:162-300, tolerance of those tests (1e-3) or tighter
     f = np.float32
     cases = []
@@ -105,8 +126,16 @@ def test_forward_against_reference_golden(golden):
     (1, 130, 6, 5, 140, 1, 1, (1, 1), (0, 0), (1, 1)),
     (2, 2, 40, 40, 3, 5, 5, (3, 3), (2, 2), (1, 1)),
     (1, 1, 1, 1, 1, 1, 1, (1, 1), (0, 0), (1, 1)),
+    # stride 1 with ragged extents: widths that are no power of two, wider than one tile, dilation,
+    # asymmetric padding, channel counts with a tail block, more than one column tile
+    (2, 8, 28, 28, 16, 5, 5, (1, 1), (2, 2), (1, 1)),
+    (1, 3, 5, 150, 4, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (2, 6, 12, 10, 9, 3, 3, (1, 1), (2, 2), (2, 2)),
+    (1, 40, 9, 7, 150, 2, 3, (1, 1), (0, 2), (1, 1)),
+    (3, 70, 16, 16, 70, 3, 3, (1, 1), (1, 1), (1, 1)),
+    (2, 4, 6, 6, 5, 3, 3, (1, 1), (0, 0), (1, 1)),
 ])
-def test_forward_backward_against_oracle(oracle, case):
+def test_forward_backward_against_oracle(oracle, case, feed):
     N, Cin, H, W, Cout, kH, kW, stride, pad, dil = case
     x = refdata.normal(1, (N, Cin, H, W))
     w = refdata.kaiming_uniform((Cout, Cin, kH, kW), Cin * kH * kW)
