@@ -114,6 +114,18 @@ int tfb_gemm_presplit(const float* A_hi, const float* A_lo, const float* B_hi, c
 int tfb_matmul_host(const void* A_host, const void* B_host, void* C_host, int64_t M, int64_t N, int64_t K,
                     int dtype, void* stream);
 
+/* One large product sharded over the GPUs of this process by row panels: device devices[g] computes
+ * C_panels[g][panel_rows[g], N] = A_panels[g][panel_rows[g], K] · B_replicas[g][K, N] on streams[g]
+ * (streams == NULL, or a NULL entry: that device's default stream). Every pointer of entry g is
+ * memory of device devices[g]; B is replicated, nothing crosses between GPUs and there is no
+ * collective. The call enqueues on every device and returns; synchronise each stream before reading
+ * its panel. The calling thread's current device is restored. A device may appear more than once
+ * (with different streams). ref: no counterpart — the reference runs on device 0 only
+ * (cuda/CudaContext.cpp:57-60; cuda/memory/CudaStorageAllocator.cpp:111-115). */
+int tfb_matmul_row_panels(int n_devices, const int* devices, const void* const* A_panels,
+                          const void* const* B_replicas, void* const* C_panels, const int64_t* panel_rows,
+                          int64_t N, int64_t K, int in_dtype, int out_dtype, void* const* streams);
+
 /* FP32 C[M,N] = A[M,K] · B[K,N] (row-major, dense) that never allocates: for hosts that may not
  * call cudaMalloc where they call us — inside a latency-critical loop that cannot take the
  * allocator's locks or its device-wide synchronisation, under a runtime that owns all device

@@ -44,6 +44,40 @@ int tfb_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_
     return tfb_matmul(A, B, C, M, N, K, dtype, dtype, stream);
 }
 
+int tfb_matmul_row_panels(int n_devices, const int* devices, const void* const* A_panels,
+                          const void* const* B_replicas, void* const* C_panels, const int64_t* panel_rows,
+                          int64_t N, int64_t K, int in_dtype, int out_dtype, void* const* streams) {
+    if (n_devices < 0 || N < 0 || K < 0) return fail(TFB_ERR_INVALID_ARG, "matmul_row_panels: negative extent");
+    if (n_devices == 0) return TFB_OK;
+    if (devices == nullptr || A_panels == nullptr || B_replicas == nullptr || C_panels == nullptr ||
+        panel_rows == nullptr)
+        return fail(TFB_ERR_INVALID_ARG, "matmul_row_panels: null argument array");
+    int visible = 0;
+    TFB_CUDA_OK(cudaGetDeviceCount(&visible));
+    for (int g = 0; g < n_devices; ++g) {
+        if (devices[g] < 0 || devices[g] >= visible)
+            return fail(TFB_ERR_INVALID_ARG, "matmul_row_panels: device %d is not one of the %d visible", devices[g],
+                        visible);
+        if (panel_rows[g] < 0) return fail(TFB_ERR_INVALID_ARG, "matmul_row_panels: negative panel height");
+    }
+    int before = 0;
+    TFB_CUDA_OK(cudaGetDevice(&before));
+    int rc = TFB_OK;
+    // One enqueue per device, none of them waited for: the panels run concurrently.
+    for (int g = 0; g < n_devices && rc == TFB_OK; ++g) {
+        if (panel_rows[g] == 0) continue;
+        cudaError_t e = cudaSetDevice(devices[g]);
+        if (e != cudaSuccess) {
+            rc = fail(TFB_ERR_CUDA, "matmul_row_panels: cudaSetDevice(%d): %s", devices[g], cudaGetErrorString(e));
+            break;
+        }
+        rc = tfb_matmul(A_panels[g], B_replicas[g], C_panels[g], panel_rows[g], N, K, in_dtype, out_dtype,
+                        streams != nullptr ? streams[g] : nullptr);
+    }
+    (void)cudaSetDevice(before);
+    return rc;
+}
+
 int tfb_split_tf32(const float* src, int64_t rows, int64_t cols, int64_t ld, float* hi, float* lo,
                    int64_t ld_out, void* stream) {
     if (rows < 0 || cols < 0) return fail(TFB_ERR_INVALID_ARG, "split_tf32: negative extent");

@@ -220,6 +220,8 @@ int run_spatial(const SpatialCall& c, const ConvShape& s, const DeviceState* st,
     const int cg = pair ? 2 : 1;
     const int bn = c.J <= 64 ? 64 : 128;
     const int64_t tiles_y = (c.out_H + cg * th - 1) / (cg * th);
+    if (s.N * tiles_x * tiles_y * cg * kBlockM >= (1ll << 31))
+        return fail(TFB_ERR_TOO_LARGE, "conv2d: more output tiles than the 32-bit tile index holds");
 
     GemmArgs a;
     memset(&a, 0, sizeof(a));
@@ -229,8 +231,6 @@ int run_spatial(const SpatialCall& c, const ConvShape& s, const DeviceState* st,
     a.M = a.tiles_m * cg * kBlockM; a.N = (int)c.J; a.K = (int)(khw * cblks * 32);
     a.k_blocks = (int)(khw * cblks);
     a.chunk_kb = 8; a.split_k = 1; a.kb_per_split = a.k_blocks; a.split_stride = 0;
-    if (const char* e = getenv("TFB_CONV_CHUNK_KB")) a.chunk_kb = atoi(e) > 0 ? atoi(e) : 8;   // debugging override
-    if (const char* e = getenv("TFB_CONV_DBG")) a.cv.dbg = atoi(e);
     a.group_m = 16;
     a.C = c.dst; a.ldc = 0; a.out_type = kOutF32;
     a.bias = c.bias; a.bias_mode = c.bias != nullptr ? kBiasPerCol : kBiasNone; a.relu = c.relu ? 1 : 0;

@@ -79,7 +79,6 @@ struct ConvGeom {
     int kblk_w_log2, kblk_h;          // kConvWgrad: K block = kblk_h rows of 2^kblk_w_log2 positions
     int kblk_x, kblk_y;               // K blocks per sample along x and y
     int n_samples;
-    int dbg;
 };
 
 struct GemmArgs {
@@ -367,20 +366,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const int tap = kb / cv.cblks, c0 = (kb - tap * cv.cblks) * 32;
                         const int ki = tap / cv.kw, kj = tap - ki * cv.kw;
                         const int sy = cs_y0 + cv.ay0 + ki * cv.ay_step, sx = cs_x0 + cv.ax0 + kj * cv.ax_step;
-                        if (cv.dbg & 2) {
-                            tma_load_4d<PAIR>(a_hi, &tmA, 0, 0, 0, 0, fb);
-                            tma_load_4d<PAIR>(a_lo, &tmA2, 0, 0, 0, 0, fb);
-                        } else {
                         tma_load_4d<PAIR>(a_hi, &tmA, c0, sx, sy, cs_n, fb);
                         tma_load_4d<PAIR>(a_lo, &tmA2, c0, sx, sy, cs_n, fb);
-                        }
-                        if (cv.dbg & 4) {
-                            tma_load_3d<PAIR>(b_hi, &tmB, 0, 0, 0, fb);
-                            tma_load_3d<PAIR>(b_lo, &tmB2, 0, 0, 0, fb);
-                        } else {
                         tma_load_3d<PAIR>(b_hi, &tmB, c0, tap, n0, fb);
                         tma_load_3d<PAIR>(b_lo, &tmB2, c0, tap, n0, fb);
-                        }
                     } else if constexpr (CONV == kConvWgrad) {
                         const int per = cv.kblk_x * cv.kblk_y;
                         const int n = kb / per, r = kb - n * per;
@@ -490,7 +479,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const uint32_t b_lo = b_hi + S::B_TILE;
 #pragma unroll
                         for (int j = 0; j < KSTEPS; ++j) {
-                            if (CONV != kConvNone && (args.cv.dbg & 8) && !(kb == kb0 && j == 0)) continue;
                             const uint32_t acc = (kb > kb0 || j > 0) ? 1u : 0u;
                             const uint64_t da = make_smem_desc(a_hi + j * A_KSTEP, A_LBO, A_SBO, A_SWZ);
                             const uint64_t db = make_smem_desc(b_hi + j * B_KSTEP, B_LBO, B_SBO, B_SWZ);
@@ -589,7 +577,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
                             epilogue_apply32(v, args, col0, 0.f);
-                            if (valid && !(cv.dbg & 1)) {
+                            if (valid) {
 #pragma unroll
                                 for (int i = 0; i < 32; ++i)
                                     if (col0 + i < args.N) dst[(long long)(col0 + i) * plane] = v[i];

@@ -236,3 +236,45 @@ def test_matmul_on_host_buffers(oracle, in_dtype, pinned):
         want = oracle.matmul(a.float().numpy(), b.float().numpy())
         assert rel_err(c.numpy(), want) < FP32_TOL
         c.fill_(float("nan"))
+
+
+@pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
+def test_row_panels_over_the_devices_of_one_process(oracle, in_dtype):
+    # Every visible GPU gets a panel (twice over when there is only one GPU: two entries on device 0 with
+    # their own streams); panels are ragged, one is empty; B is replicated per device; no collective.
+    import ctypes
+    ndev = torch.cuda.device_count()
+    devices = list(range(ndev)) * (2 if ndev == 1 else 1) + [0]
+    rows = [(130 + 77 * g) for g in range(len(devices) - 1)] + [0]
+    N, K = 200, 300
+    tdt = torch.float32 if in_dtype == capi.DTYPE_F32 else torch.bfloat16
+    a_full = torch.from_numpy(refdata.uniform(5, (sum(rows), K))).to(tdt)
+    b = torch.from_numpy(refdata.uniform(6, (K, N))).to(tdt)
+    want = oracle.matmul(a_full.float().numpy(), b.float().numpy())
+    A, B, C, S = [], [], [], []
+    r0 = 0
+    for d, r in zip(devices, rows):
+        A.append(a_full[r0:r0 + r].contiguous().to(f"cuda:{d}"))
+        B.append(b.to(f"cuda:{d}"))
+        C.append(torch.full((r, N), float("nan"), device=f"cuda:{d}"))
+        S.append(torch.cuda.Stream(device=d))
+        r0 += r
+    n = len(devices)
+    arr = lambda ts: (ctypes.c_void_p * n)(*[t.data_ptr() if t.numel() else None for t in ts])
+    streams = (ctypes.c_void_p * n)(*[s.cuda_stream for s in S])
+    before = torch.cuda.current_device()
+    capi.check(lib.tfb_matmul_row_panels(n, (ctypes.c_int * n)(*devices), arr(A), arr(B), arr(C),
+                                         (ctypes.c_int64 * n)(*rows), N, K, in_dtype, capi.DTYPE_F32, streams))
+    assert torch.cuda.current_device() == before
+    for s in S:
+        s.synchronize()
+    got = np.concatenate([c.cpu().numpy() for c in C], axis=0)
+    assert not np.isnan(got).any()
+    assert rel_err(got, want) < (FP32_TOL if in_dtype == capi.DTYPE_F32 else BF16_TOL)
+    for d in set(devices):
+        with torch.cuda.device(d):
+            assert_device_ok()
+    # a device index that does not exist is refused before anything is enqueued
+    bad = (ctypes.c_int * n)(*([devices[0]] * (n - 1) + [ndev + 3]))
+    assert lib.tfb_matmul_row_panels(n, bad, arr(A), arr(B), arr(C), (ctypes.c_int64 * n)(*rows), N, K, in_dtype,
+                                     capi.DTYPE_F32, streams) == -1
