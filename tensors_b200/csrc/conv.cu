@@ -36,14 +36,21 @@ __global__ void dgrad_weight_kernel(const float* __restrict__ W, float* __restri
     }
 }
 
-// dW[co][t] = Σ_s partial[s][co][t] (s ascending) for t < taps; db[co] = Σ_s partial[s][co][taps].
+// dW[co][t] = Σ_s partial[s][co][t] for t < taps; db[co] = Σ_s partial[s][co][taps], in a fixed order.
 __global__ void wgrad_reduce_kernel(const float* __restrict__ partial, int splits, int Cout, int taps,
                                     int taps_total, float* __restrict__ dW, float* __restrict__ db) {
     const int total = Cout * taps_total;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int co = i / taps_total, t = i - co * taps_total;
-        float s = 0.f;
-        for (int k = 0; k < splits; ++k) s += partial[(long long)k * total + i];
+        // eight independent running sums (splits k, k + 8, ... each) keep eight loads in flight; they
+        // are combined in a fixed order, so the result does not depend on the launch
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < splits; k += 8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (k + j < splits) acc[j] += partial[(long long)(k + j) * total + i];
+        }
+        const float s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
         if (t < taps) {
             if (dW != nullptr) dW[(long long)co * taps + t] = s;
         } else if (t == taps && db != nullptr) {

@@ -112,28 +112,33 @@ __global__ void wgrad_planes_reduce_kernel(const float* __restrict__ partial, in
     }
 }
 
-// out[g][c] = sum of partial[b][c] over the rows b = g, g + groups, g + 2 * groups, ... in ascending
-// order (groups = gridDim.y * 8): a block covers 32 columns and 8 row groups. Run once with many groups
-// and once more with 8 to finish; the order of every addition is fixed by the launch shape.
-__global__ void colsum_stage_kernel(const float* __restrict__ partial, long long blocks, int cols, int ld,
-                                    float* __restrict__ out, int out_ld) {
+// out[blockIdx.y][c] = sum of partial[b][c] over the block's rows b in [y * rows_per_block, ...): a block
+// covers 32 columns; its eight row groups each keep four independent running sums (rows g, g + 32, ...;
+// g + 8, ...; g + 16, ...; g + 24, ...), combined in a fixed order, then the eight group sums are added in
+// ascending order. Run it once over many row blocks and once more over their results.
+__global__ void colsum_kernel(const float* __restrict__ partial, long long rows, int cols, long long ld,
+                              long long rows_per_block, float* __restrict__ out, int out_ld) {
+    __shared__ float sm[8][33];
     const int c = blockIdx.x * 32 + threadIdx.x;
-    const long long groups = (long long)gridDim.y * 8;
-    const long long g = (long long)blockIdx.y * 8 + threadIdx.y;
-    if (c >= cols) return;
-    float s = 0.f;
-    for (long long b = g; b < blocks; b += groups) s += partial[b * ld + c];
-    out[g * out_ld + c] = s;
-}
-
-// db[c] = sum of the 8 * stage_blocks group sums in ascending order.
-__global__ void colsum_last_kernel(const float* __restrict__ sums, int groups, int cols, int ld,
-                                   float* __restrict__ out) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
-    float t = 0.f;
-    for (int g = 0; g < groups; ++g) t += sums[(long long)g * ld + c];
-    out[c] = t;
+    const long long r0 = (long long)blockIdx.y * rows_per_block;
+    const long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (c < cols) {
+        for (long long b = r0 + threadIdx.y; b < r1; b += 32) {
+            a0 += partial[b * ld + c];
+            if (b + 8 < r1) a1 += partial[(b + 8) * ld + c];
+            if (b + 16 < r1) a2 += partial[(b + 16) * ld + c];
+            if (b + 24 < r1) a3 += partial[(b + 24) * ld + c];
+        }
+    }
+    sm[threadIdx.y][threadIdx.x] = (a0 + a1) + (a2 + a3);
+    __syncthreads();
+    if (threadIdx.y == 0 && c < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) t += sm[g][threadIdx.x];
+        out[(long long)blockIdx.y * out_ld + c] = t;
+    }
 }
 
 template <int BN, int STAGES, bool PAIR, int CONV>
@@ -195,7 +200,7 @@ int plane_maps(CUtensorMap out[2], const float* hi, const float* lo, int64_t cp,
     return make_map_nd(&out[1], lo, 4, dims, strides, box, atom32);
 }
 
-constexpr int kBiasStageBlocks = 16;   // x 8 row groups = 128 partial sums per column after the first stage
+constexpr int kBiasStageBlocks = 32;   // row blocks of the first bias-gradient reduction stage
 
 struct SpatialCall {
     const float* src_hi; const float* src_lo;   // NHWC planes of the tensor the taps are gathered from
@@ -341,7 +346,7 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
     auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
     const size_t o_dy = take((size_t)(2 * s.N * Po * cop) * 4);
     const size_t o_bsum = want_db ? take((size_t)(s.N * pblocks * cop) * 4) : 0;
-    const size_t o_bstage = want_db ? take((size_t)(kBiasStageBlocks * 8 * cop) * 4) : 0;
+    const size_t o_bstage = want_db ? take((size_t)(kBiasStageBlocks * cop) * 4) : 0;
     const size_t o_fd = want_dx ? take((size_t)(2 * s.Cin * khw * cop) * 4) : 0;
     const size_t o_x = want_dw ? take((size_t)(2 * s.N * P * cp) * 4) : 0;
     const size_t o_part = want_dw ? take((size_t)(splits * rows_per_split * ld_part) * 4) : 0;
@@ -357,11 +362,14 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
     if (rc != TFB_OK) return rc;
     if (want_db) {
         float* stage = reinterpret_cast<float*>(ws + o_bstage);
-        colsum_stage_kernel<<<dim3((unsigned)((s.Cout + 31) / 32), kBiasStageBlocks), dim3(32, 8), 0, stream>>>(
-            bsum, s.N * pblocks, (int)s.Cout, (int)cop, stage, (int)cop);
+        const long long rows = s.N * pblocks;
+        const long long per_block = (rows + kBiasStageBlocks - 1) / kBiasStageBlocks;
+        const unsigned col_blocks = (unsigned)((s.Cout + 31) / 32);
+        colsum_kernel<<<dim3(col_blocks, kBiasStageBlocks), dim3(32, 8), 0, stream>>>(bsum, rows, (int)s.Cout, cop,
+                                                                                      per_block, stage, (int)cop);
         TFB_CUDA_OK(cudaGetLastError());
-        colsum_last_kernel<<<(unsigned)((s.Cout + 127) / 128), 128, 0, stream>>>(stage, kBiasStageBlocks * 8, (int)s.Cout,
-                                                                                 (int)cop, db);
+        colsum_kernel<<<dim3(col_blocks, 1), dim3(32, 8), 0, stream>>>(stage, kBiasStageBlocks, (int)s.Cout, cop,
+                                                                       kBiasStageBlocks, db, 0);
         TFB_CUDA_OK(cudaGetLastError());
     }
     if (want_dx) {
