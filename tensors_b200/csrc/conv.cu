@@ -199,6 +199,7 @@ int conv2d_forward(const float* x, const float* w, const float* bias, float* out
     if (rc != TFB_OK) return rc;
     if (s.N == 0) return TFB_OK;
     if (conv_tma_eligible(s, s.Cin)) return conv_tma_forward(x, w, bias, out, s, relu, stream);
+    if (conv_direct_forward_eligible(s)) return conv_direct_forward(x, w, bias, out, s, relu, stream);
     DeviceState* st = nullptr;
     rc = device_state(&st);
     if (rc != TFB_OK) return rc;
@@ -254,7 +255,15 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
         return TFB_OK;
     }
     {
-        // Each product goes to the TMA-fed path or stays on the gather kernel by its own contraction.
+        // Each product goes its own way: an input gradient with at most 4 channels to the CUDA-core
+        // kernel, products with enough contraction channels and stride 1 to the TMA-fed path, the rest
+        // to the gather kernel.
+        if (dX != nullptr && !conv_tma_forced() && conv_direct_dgrad_eligible(s)) {
+            rc = conv_direct_dgrad(dY, w, dX, s, stream);
+            if (rc != TFB_OK) return rc;
+            dX = nullptr;
+            if (dW == nullptr && db == nullptr) return TFB_OK;
+        }
         const bool t_dx = dX != nullptr && conv_tma_eligible(s, s.Cout);
         const bool t_w = (dW != nullptr || db != nullptr) && conv_tma_eligible(s, s.Cin);
         if (t_dx || t_w) {

@@ -1,0 +1,185 @@
+// Direct (CUDA-core) convolution kernels for the shapes whose contraction is too short to feed a tensor
+// core: a first layer with 3 input channels has 27 products per output and 13 FLOP per byte, so it is
+// bound by HBM traffic and latency, not by arithmetic. One thread owns one position and a strip of
+// channels, keeps the partial sums in registers, reads the activations straight from the NCHW tensor
+// (lanes = consecutive positions: coalesced) and the filter from shared memory (all lanes read the same
+// address: a broadcast). Plain FP32 FMAs in the reference's accumulation order (channel, then filter
+// row, then filter column); any stride, padding and dilation.
+#include <cstdlib>
+
+#include "internal.hpp"
+
+namespace tfb {
+
+namespace {
+
+constexpr int kDirectThreads = 128;
+constexpr int kDirectCout = 32;      // output channels per thread in the forward kernel
+constexpr int kDirectMaxTaps = 128;  // Cin * kH * kW the forward kernel accepts
+constexpr int kDirectCin = 4;        // input channels per thread in the input-gradient kernel
+static_assert(kDirectCin == 4, "the input-gradient kernel keeps exactly two accumulator pairs");
+
+struct DirectArgs {
+    int N, Cin, H, W, Cout, kH, kW, sh, sw, ph, pw, dh, dw, outH, outW;
+};
+
+// out[n][co][p] = bias[co] + sum_k x[n][c][iy][ix] * w[co][k], k = (c, ki, kj) ascending.
+// grid = (position blocks, Cout / kDirectCout, N).
+__global__ void __launch_bounds__(kDirectThreads)
+conv_direct_forward_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                           float* __restrict__ out, const DirectArgs a, int relu) {
+    __shared__ __align__(16) float w_s[kDirectMaxTaps][kDirectCout];
+    const int taps = a.Cin * a.kH * a.kW;
+    const int co0 = blockIdx.y * kDirectCout;
+    // consecutive threads read consecutive filter elements (the strip's rows are contiguous in w)
+    for (int i = threadIdx.x; i < taps * kDirectCout; i += kDirectThreads) {
+        const int j = i / taps, k = i - j * taps;
+        w_s[k][j] = (co0 + j < a.Cout) ? w[(long long)co0 * taps + i] : 0.f;
+    }
+    __syncthreads();
+    const int P = a.outH * a.outW;
+    const int p = blockIdx.x * kDirectThreads + threadIdx.x;
+    if (p >= P) return;
+    const int n = blockIdx.z;
+    const int oy = p / a.outW, ox = p - oy * a.outW;
+    const int iy0 = oy * a.sh - a.ph, ix0 = ox * a.sw - a.pw;
+    // Accumulators in pairs: sm_100 issues two FP32 FMAs per instruction on packed operands.
+    float2 acc2[kDirectCout / 2];
+#pragma unroll
+    for (int j = 0; j < kDirectCout / 2; ++j) acc2[j] = make_float2(0.f, 0.f);
+    const float* xs = x + (long long)n * a.Cin * a.H * a.W;
+    int k = 0;
+    for (int c = 0; c < a.Cin; ++c) {
+        const float* xc = xs + (long long)c * a.H * a.W;
+        for (int ki = 0; ki < a.kH; ++ki) {
+            const int iy = iy0 + ki * a.dh;
+            const bool row_ok = iy >= 0 && iy < a.H;
+            for (int kj = 0; kj < a.kW; ++kj, ++k) {
+                const int ix = ix0 + kj * a.dw;
+                const float v = (row_ok && ix >= 0 && ix < a.W) ? __ldg(xc + (long long)iy * a.W + ix) : 0.f;
+                const float2 vv = make_float2(v, v);
+                const float4* wr = reinterpret_cast<const float4*>(w_s[k]);
+#pragma unroll
+                for (int j = 0; j < kDirectCout / 4; ++j) {
+                    const float4 ww = wr[j];
+                    acc2[2 * j] = __ffma2_rn(vv, make_float2(ww.x, ww.y), acc2[2 * j]);
+                    acc2[2 * j + 1] = __ffma2_rn(vv, make_float2(ww.z, ww.w), acc2[2 * j + 1]);
+                }
+            }
+        }
+    }
+    float* o = out + ((long long)n * a.Cout + co0) * P + p;
+#pragma unroll
+    for (int j = 0; j < kDirectCout; ++j) {
+        if (co0 + j < a.Cout) {
+            float r = ((j & 1) ? acc2[j >> 1].y : acc2[j >> 1].x) + (bias != nullptr ? __ldg(bias + co0 + j) : 0.f);
+            if (relu) r = r > 0.f ? r : 0.f;
+            o[(long long)j * P] = r;
+        }
+    }
+}
+
+// dX[n][c][y][x] = sum over (ki, kj, co) of dY[n][co][oy][ox] * w[co][c][ki][kj] with
+// oy = (y + ph - ki * dh) / sh where that division is exact and in range (x alike) — the gather form
+// of the transposed convolution: no atomics, a fixed order. One thread owns one input position and up
+// to kDirectCin input channels; grid = (position blocks, ceil(Cin / kDirectCin), N).
+// Shared memory: the filter slice w_s[co * khw + tap][c], (Cout * khw * kDirectCin) floats.
+__global__ void __launch_bounds__(kDirectThreads)
+conv_direct_dgrad_kernel(const float* __restrict__ dY, const float* __restrict__ w, float* __restrict__ dX,
+                         const DirectArgs a) {
+    extern __shared__ __align__(16) float wd_s[];
+    const int khw = a.kH * a.kW;
+    const int c0 = blockIdx.y * kDirectCin;
+    for (int i = threadIdx.x; i < a.Cout * khw * kDirectCin; i += kDirectThreads) {
+        const int c = i % kDirectCin, r = i / kDirectCin;   // r = co * khw + tap
+        const int co = r / khw, tap = r - co * khw;
+        wd_s[i] = (c0 + c < a.Cin) ? __ldg(w + ((long long)co * a.Cin + c0 + c) * khw + tap) : 0.f;
+    }
+    __syncthreads();
+    const int P = a.H * a.W, Po = a.outH * a.outW;
+    const int p = blockIdx.x * kDirectThreads + threadIdx.x;
+    if (p >= P) return;
+    const int n = blockIdx.z;
+    const int y = p / a.W, xx = p - y * a.W;
+    float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
+    const float* g = dY + (long long)n * a.Cout * Po;
+    for (int ki = 0; ki < a.kH; ++ki) {
+        const int ny = y + a.ph - ki * a.dh;
+        if (ny < 0 || ny % a.sh != 0) continue;
+        const int oy = ny / a.sh;
+        if (oy >= a.outH) continue;
+        for (int kj = 0; kj < a.kW; ++kj) {
+            const int nx = xx + a.pw - kj * a.dw;
+            if (nx < 0 || nx % a.sw != 0) continue;
+            const int ox = nx / a.sw;
+            if (ox >= a.outW) continue;
+            const float* gp = g + (long long)oy * a.outW + ox;
+            const float4* wr = reinterpret_cast<const float4*>(wd_s) + (ki * a.kW + kj);
+#pragma unroll 4
+            for (int co = 0; co < a.Cout; ++co) {
+                const float v = __ldg(gp + (long long)co * Po);
+                const float4 ww = wr[co * khw];
+                a01 = __ffma2_rn(make_float2(v, v), make_float2(ww.x, ww.y), a01);
+                a23 = __ffma2_rn(make_float2(v, v), make_float2(ww.z, ww.w), a23);
+            }
+        }
+    }
+    const float acc[kDirectCin] = {a01.x, a01.y, a23.x, a23.y};
+#pragma unroll
+    for (int c = 0; c < kDirectCin; ++c)
+        if (c0 + c < a.Cin) dX[((long long)n * a.Cin + c0 + c) * P + p] = acc[c];
+}
+
+DirectArgs direct_args(const ConvShape& s) {
+    return DirectArgs{(int)s.N, (int)s.Cin, (int)s.H, (int)s.W, (int)s.Cout, (int)s.kH, (int)s.kW, (int)s.sh,
+                      (int)s.sw, (int)s.ph, (int)s.pw, (int)s.dh, (int)s.dw, (int)s.outH, (int)s.outW};
+}
+
+bool direct_enabled() {
+    if (const char* e = getenv("TFB_CONV_DIRECT")) return atoi(e) != 0;   // debugging override
+    return true;
+}
+
+constexpr size_t kDgradSmemLimit = 200 * 1024;
+
+}  // namespace
+
+bool conv_direct_forward_eligible(const ConvShape& s) {
+    return direct_enabled() && s.Cin * s.kH * s.kW <= kDirectMaxTaps && s.N < 65536 &&
+           (s.Cout + kDirectCout - 1) / kDirectCout < 65536 && s.outH * s.outW < (1ll << 31) - kDirectThreads;
+}
+
+bool conv_direct_dgrad_eligible(const ConvShape& s) {
+    return direct_enabled() && s.Cin <= kDirectCin && s.N < 65536 &&
+           (size_t)(s.Cout * s.kH * s.kW * kDirectCin) * 4 <= kDgradSmemLimit && s.H * s.W < (1ll << 31) - kDirectThreads;
+}
+
+int conv_direct_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
+                        cudaStream_t stream) {
+    const long long P = s.outH * s.outW;
+    dim3 grid((unsigned)((P + kDirectThreads - 1) / kDirectThreads), (unsigned)((s.Cout + kDirectCout - 1) / kDirectCout),
+              (unsigned)s.N);
+    conv_direct_forward_kernel<<<grid, kDirectThreads, 0, stream>>>(x, w, bias, out, direct_args(s), relu ? 1 : 0);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+int conv_direct_dgrad(const float* dY, const float* w, float* dX, const ConvShape& s, cudaStream_t stream) {
+    const long long P = s.H * s.W;
+    const size_t smem = (size_t)(s.Cout * s.kH * s.kW * kDirectCin) * 4;
+    static size_t attr_set[64] = {0};
+    int dev = 0;
+    TFB_CUDA_OK(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && attr_set[dev] < smem) {
+        TFB_CUDA_OK(cudaFuncSetAttribute(conv_direct_dgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kDgradSmemLimit));
+        attr_set[dev] = kDgradSmemLimit;
+    }
+    dim3 grid((unsigned)((P + kDirectThreads - 1) / kDirectThreads), (unsigned)((s.Cin + kDirectCin - 1) / kDirectCin),
+              (unsigned)s.N);
+    conv_direct_dgrad_kernel<<<grid, kDirectThreads, smem, stream>>>(dY, w, dX, direct_args(s));
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+}  // namespace tfb

@@ -272,6 +272,11 @@ int run_spatial(const SpatialCall& c, const ConvShape& s, const DeviceState* st,
 
 }  // namespace
 
+bool conv_tma_forced() {
+    const char* e = getenv("TFB_CONV_TMA");
+    return e != nullptr && atoi(e) == 2;
+}
+
 bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels) {
     int mode = 1;
     if (const char* e = getenv("TFB_CONV_TMA")) mode = atoi(e);   // debugging override: 0 never, 2 whenever possible

@@ -106,10 +106,20 @@ struct ConvShape {
 // tensor-map limits, and enough channels in the contraction (forward and weight gradient: Cin; input
 // gradient: Cout) to fill the 32-channel K blocks.
 bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels);
+// True when the debugging override asks for the TMA-fed path wherever it is possible.
+bool conv_tma_forced();
 int conv_tma_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
                      cudaStream_t stream);
 // dX, dW, db may each be null.
 int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX, float* dW, float* db,
                       const ConvShape& s, cudaStream_t stream);
+
+// conv_direct.cu: CUDA-core kernels for short contractions (any stride). Forward: Cin*kH*kW <= 128;
+// input gradient: Cin <= 4.
+bool conv_direct_forward_eligible(const ConvShape& s);
+bool conv_direct_dgrad_eligible(const ConvShape& s);
+int conv_direct_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
+                        cudaStream_t stream);
+int conv_direct_dgrad(const float* dY, const float* w, float* dX, const ConvShape& s, cudaStream_t stream);
 
 }  // namespace tfb

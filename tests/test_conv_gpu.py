@@ -48,20 +48,24 @@ def conv_backward(x, w, g, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
 @pytest.fixture(params=["default", "tma_feed", "gather_kernel"])
 def feed(request):
     """By default a stride-1 product with at least 16 contraction channels runs on the TMA-fed GEMM
-    kernel and everything else on the kernel with software gather producers. TFB_CONV_TMA=2 sends every
-    stride-1 product to the former, TFB_CONV_TMA=0 everything to the latter, so both get every case."""
-    old = os.environ.get("TFB_CONV_TMA")
+    kernel, short contractions (forward with Cin*kH*kW <= 128, input gradient with Cin <= 4) on the
+    CUDA-core kernels and everything else on the kernel with software gather producers.
+    TFB_CONV_TMA=2 sends every stride-1 product to the first, TFB_CONV_TMA=0 with TFB_CONV_DIRECT=0
+    everything to the last, so each kernel gets every case it can take."""
+    old = {k: os.environ.get(k) for k in ("TFB_CONV_TMA", "TFB_CONV_DIRECT")}
+    for k in old:
+        os.environ.pop(k, None)
     if request.param == "gather_kernel":
         os.environ["TFB_CONV_TMA"] = "0"
+        os.environ["TFB_CONV_DIRECT"] = "0"
     elif request.param == "tma_feed":
         os.environ["TFB_CONV_TMA"] = "2"
-    else:
-        os.environ.pop("TFB_CONV_TMA", None)
     yield request.param
-    if old is None:
-        os.environ.pop("TFB_CONV_TMA", None)
-    else:
-        os.environ["TFB_CONV_TMA"] = old
+    for k, v in old.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
 
 
 def test_reference_known_answers(feed):
