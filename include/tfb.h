@@ -234,6 +234,24 @@ int tfb_log_softmax_nll(const float* logits, const int64_t* labels, float* dlogi
 int tfb_sgd_momentum(float* params, float* velocity, const float* grads, int64_t n, float lr,
                      float momentum, float grad_scale, void* stream);
 
+/* ---- device-side pieces of the autograd walk (FP32, n elements, any alignment) ---------- */
+
+/* dst[i] = value. The ones-fill of the root gradient that Tensor::backward does in a host loop.
+ * ref: autograd/TensorAutograd.cpp:57-70. */
+int tfb_fill(float* dst, int64_t n, float value, void* stream);
+/* y = max(x, 0). ref: Tensor::relu, tensor/Tensor.cpp:227-249; ReluOp, cuda/kernels/elementwise.cu:112-114. */
+int tfb_relu_forward(const float* x, float* y, int64_t n, void* stream);
+/* dx = x > 0 ? dy : 0 (zero at x == 0), x the ReLU's input — or its output, which has the same sign.
+ * ref: ReluBackward, autograd/ops/ReluBackward.hpp:22-32 (host loop building a mask, then a product). */
+int tfb_relu_backward(const float* x, const float* dy, float* dx, int64_t n, void* stream);
+/* dst += src: gradient accumulation where a tensor feeds several consumers.
+ * ref: InputBuffer::add, autograd/InputBuffer.cpp:11-26, 32-41 (host loop). */
+int tfb_accumulate(float* dst, const float* src, int64_t n, void* stream);
+/* dst = src · scalar[0] with the scalar in device memory (a loss node scaling its saved gradient by
+ * the upstream one-element gradient without reading it on the host).
+ * ref: the scalar products closing the loss graph, examples/train_mlp.cpp:68-75. */
+int tfb_scale_by_device_scalar(const float* src, const float* scalar, float* dst, int64_t n, void* stream);
+
 /* ---- device memory: one explicit stream-ordered pool per device ------------------------ */
 
 /* ref for the whole group: CudaStorageAllocator, cuda/memory/CudaStorageAllocator.cpp:34-57

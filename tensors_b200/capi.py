@@ -54,6 +54,11 @@ PROTOTYPES = {
     "tfb_im2col_index_map": (_i32, [_vp] + [_i64] * 13 + [_vp]),
     "tfb_log_softmax_nll": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tfb_sgd_momentum": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
+    "tfb_fill": (_i32, [_vp, _i64, ctypes.c_float, _vp]),
+    "tfb_relu_forward": (_i32, [_vp, _vp, _i64, _vp]),
+    "tfb_relu_backward": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "tfb_accumulate": (_i32, [_vp, _vp, _i64, _vp]),
+    "tfb_scale_by_device_scalar": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "tfb_device_count": (_i32, [_ip]),
     "tfb_alloc": (_i32, [_i32, _sz, _vp, ctypes.POINTER(ctypes.c_void_p)]),
     "tfb_free": (_i32, [_vp, _i32, _vp]),

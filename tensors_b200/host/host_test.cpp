@@ -52,6 +52,112 @@ static void cpu_checks() {
     tfb_register_kernels();
     CHECK(registered_cuda_matmul() != nullptr);
     CHECK(dtype_size(Dtype::BFloat16) == 2 && dtype_size(Dtype::Int64) == 8);
+    CHECK(throws([&] { a.backward(); }));         // no grad_fn (autograd/TensorAutograd.cpp:54-56)
+    CHECK(!a.requires_grad() && !a.grad().defined());
+    a.requires_grad(true);
+    CHECK(a.requires_grad() && a.gradient_edge().function != nullptr);
+}
+
+// Backward passes over CUDA tensors: every step of the walk runs on the device.
+static void autograd_checks() {
+    // matmul_grad of autograd/ops/autograd_all_ops_test.cpp:281-328: c = a.matmul(b); c.backward()
+    {
+        Tensor a = upload({0, 1, 2, 3, 4, 5}, Shape{2, 3}), b = upload({0, 1, 2, 3, 4, 5}, Shape{3, 2});
+        a.requires_grad(true);
+        b.requires_grad(true);
+        Tensor c = a.matmul(b);
+        CHECK(c.requires_grad() && c.grad_fn() != nullptr);
+        c.backward();
+        auto ga = download(a.grad()), gb = download(b.grad());
+        const float ea[6] = {1, 5, 9, 1, 5, 9}, eb[6] = {3, 3, 5, 5, 7, 7};
+        for (int i = 0; i < 6; ++i) CHECK(approx(ga[i], ea[i], 1e-5f) && approx(gb[i], eb[i], 1e-5f));
+        // no grad requested: no node
+        Tensor p = upload({1, 2, 3, 4}, Shape{2, 2});
+        CHECK(p.matmul(p).grad_fn() == nullptr);
+    }
+    // relu: mask is 0 at x == 0 (autograd/ops/ReluBackward.hpp:26-30)
+    {
+        Tensor x = upload({-1.f, 0.f, 2.f, 3.f, -0.5f}, Shape{1, 5});
+        x.requires_grad(true);
+        Tensor y = x.relu();
+        auto yh = download(y);
+        const float ey[5] = {0, 0, 2, 3, 0};
+        for (int i = 0; i < 5; ++i) CHECK(yh[i] == ey[i]);
+        y.backward();
+        auto gx = download(x.grad());
+        const float eg[5] = {0, 0, 1, 1, 0};
+        for (int i = 0; i < 5; ++i) CHECK(gx[i] == eg[i]);
+    }
+    // one tensor feeding two products: y = (x W) W, root gradient of ones;
+    // dW = x^T (1 W^T) + (x W)^T 1 accumulated on the device
+    {
+        const std::vector<float> xh = {1, -2, 0.5f, 3, 0.25f, -1}, wh = {0.5f, -1, 2, 1.5f, 0.25f, -0.75f, -2, 1, 0.5f};
+        Tensor x = upload(xh, Shape{2, 3}), W = upload(wh, Shape{3, 3});
+        W.requires_grad(true);
+        Tensor y = x.matmul(W).matmul(W);
+        y.backward();
+        auto gw = download(W.grad());
+        double h[2][3] = {}, want[3][3] = {};
+        for (int i = 0; i < 2; ++i)
+            for (int j = 0; j < 3; ++j)
+                for (int k = 0; k < 3; ++k) h[i][j] += double(xh[i * 3 + k]) * wh[k * 3 + j];
+        for (int r = 0; r < 3; ++r)
+            for (int c = 0; c < 3; ++c) {
+                for (int i = 0; i < 2; ++i) {
+                    double g1 = 0;   // (1 W^T)[i][c] = sum_j W[c][j]
+                    for (int j = 0; j < 3; ++j) g1 += wh[c * 3 + j];
+                    want[r][c] += double(xh[i * 3 + r]) * g1 + h[i][r];
+                }
+            }
+        for (int r = 0; r < 3; ++r)
+            for (int c = 0; c < 3; ++c) CHECK(approx(gw[r * 3 + c], float(want[r][c]), 1e-5f));
+        CHECK(!x.grad().defined());   // x did not ask for a gradient
+    }
+    // the training graph of examples/train_mlp.cpp:161-183: Linear -> relu -> Linear -> cross_entropy ->
+    // backward, against the same step done by hand with the (oracle-checked) explicit backward calls
+    {
+        const int64_t N = 7, D = 6, Hd = 5, C = 3;
+        std::vector<float> xh(N * D);
+        for (int64_t i = 0; i < N * D; ++i) xh[i] = 0.1f * float((i * 7) % 11) - 0.4f;
+        std::vector<int64_t> lab = {0, 2, 1, 1, 0, 2, 2};
+        Tensor x = upload(xh, Shape{N, D});
+        Tensor labels = Tensor::from_host(lab.data(), Shape{N}, Dtype::Int64, Device::cuda(0));
+        nn::Linear fc1(D, Hd), fc2(Hd, C);
+        fc1.weight().requires_grad(true); fc1.bias().requires_grad(true);
+        fc2.weight().requires_grad(true); fc2.bias().requires_grad(true);
+        Tensor h = fc1.forward(x).relu();
+        Tensor logits = fc2.forward(h);
+        Tensor loss = cross_entropy(logits, labels);
+        loss.backward();
+        // by hand
+        Tensor dz = Tensor::empty(Shape{N, C}, Dtype::Float32, Device::cuda(0));
+        Tensor loss2 = Tensor::empty(Shape{1}, Dtype::Float32, Device::cuda(0));
+        void* st = DeviceContext::current().current_stream;
+        CHECK(tfb_log_softmax_nll(static_cast<const float*>(logits.data()), static_cast<const int64_t*>(labels.data()),
+                                  static_cast<float*>(dz.data()), static_cast<float*>(loss2.data()), N, C, N, st) == TFB_OK);
+        Tensor pre = fc1.forward(x);
+        auto g2 = fc2.backward(h, logits, dz);
+        Tensor dpre = Tensor::empty(Shape{N, Hd}, Dtype::Float32, Device::cuda(0));
+        CHECK(tfb_relu_backward(static_cast<const float*>(pre.data()), static_cast<const float*>(g2.grad_input.data()),
+                                static_cast<float*>(dpre.data()), N * Hd, st) == TFB_OK);
+        auto g1 = fc1.backward(x, pre, dpre);
+        auto same = [&](const Tensor& a, const Tensor& b) {
+            auto ah = download(a), bh = download(b);
+            CHECK(ah.size() == bh.size());
+            for (size_t i = 0; i < ah.size() && i < bh.size(); ++i) CHECK(approx(ah[i], bh[i], 1e-6f));
+        };
+        same(loss, loss2);
+        same(fc2.weight().grad(), g2.grad_weight);
+        same(fc2.bias().grad(), g2.grad_bias);
+        same(fc1.weight().grad(), g1.grad_weight);
+        same(fc1.bias().grad(), g1.grad_bias);
+        auto lh = download(loss);
+        CHECK(lh[0] > 0.5f && lh[0] < 2.0f);   // about ln(3) for near-uniform predictions
+        // a second backward pass replaces the stored gradients (autograd/AccumulateGrad.cpp:20-23)
+        Tensor loss3 = cross_entropy(fc2.forward(fc1.forward(x).relu()), labels);
+        loss3.backward();
+        same(fc2.weight().grad(), g2.grad_weight);
+    }
 }
 
 static void gpu_checks() {
@@ -142,6 +248,7 @@ static void gpu_checks() {
             CHECK(throws([&] { (void)Tensor::empty(Shape{2}, Dtype::Float32, Device::cuda(1)); }));   // as tensor_cuda_dispatch_test.cpp:55-58
         }
     }
+    autograd_checks();
     int code = -1;
     CHECK(tfb_device_status(&code) == TFB_OK && code == 0);
 }

@@ -9,6 +9,11 @@
 
 namespace tensorforge {
 
+// autograd_b200.cpp
+void record_matmul(Tensor& out, const Tensor& a, const Tensor& b);
+void record_linear(Tensor& y, const Tensor& x, const Tensor& w, const Tensor& bias, int64_t in_f, int64_t out_f,
+                   bool relu, bool bias_enabled);
+
 namespace {
 
 [[noreturn]] void raise(const char* what) {
@@ -171,6 +176,7 @@ Tensor Tensor::matmul(const Tensor& other) const {
     Tensor out = Tensor::empty(Shape{M, N}, Dtype::Float32, device());
     g_cuda_matmul(data(), other.data(), out.data(), M, N, K, dtype(), Dtype::Float32,
                   DeviceContext::for_device(device().index).current_stream);
+    record_matmul(out, *this, other);
     return out;
 }
 
@@ -214,6 +220,7 @@ Tensor Linear::forward(Tensor x, bool fuse_relu) {
                           y.data(), batch, in_features_, out_features_, fuse_relu ? 1 : 0, TFB_DTYPE_F32,
                           DeviceContext::for_device(x.device().index).current_stream),
        "tfb_linear_forward");
+    record_linear(y, x, weight_, bias_, in_features_, out_features_, fuse_relu, bias_enabled_);
     return y;
 }
 

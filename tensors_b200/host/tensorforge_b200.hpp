@@ -9,6 +9,9 @@
 //   DeviceContext, DeviceGuard        cuda/CudaContext.hpp:134-140, cuda/CudaContext.cpp:18-60
 //   CudaStorageAllocator              cuda/memory/CudaStorageAllocator.hpp
 //   MatmulBackward                    autograd/ops/MatmulBackward.hpp:26-34
+//   Node, Edge, Engine, AccumulateGrad autograd/Node.hpp:14-45, autograd/Engine.hpp:12-30, autograd/AccumulateGrad.cpp:10-27
+//   ReluBackward, Tensor::backward    autograd/ops/ReluBackward.hpp:22-32, autograd/TensorAutograd.cpp:52-73
+//   cross_entropy                     the loss graph of examples/train_mlp.cpp:54-76, as one node
 //   nn::Linear, nn::Conv2d            nn/Linear.hpp, nn/Conv2d.hpp:32-61
 //
 // Only CUDA tensors are served: CPU tensors stay on the reference's own loops, and there is no
@@ -112,6 +115,13 @@ void launch_gemm_tiled_16x16(const void* A, const void* B, void* C, int64_t M, i
 void launch_gemm_optimized(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, Dtype dtype, void* stream);
 
 // ---- Tensor ---------------------------------------------------------------------------------------
+class Node;
+struct AutogradMeta;
+struct Edge {
+    std::shared_ptr<Node> function;
+    uint32_t input_nr = 0;
+};
+
 class Tensor {
 public:
     Tensor() = default;
@@ -129,20 +139,90 @@ public:
 
     // C[M,N] = this[M,K] · other[K,N]. CUDA tensors of one device; Float32 -> Float32,
     // Float16 / BFloat16 -> Float32 (accumulate and output). Same argument checks and messages as
-    // the reference (tensor/Tensor.cpp:335-346) where they still apply.
+    // the reference (tensor/Tensor.cpp:335-346) where they still apply. Records a MatmulBackward
+    // node when an operand requires a gradient.
     Tensor matmul(const Tensor& other) const;
+    // max(x, 0) on the device; records a ReluBackward node when this tensor requires a gradient.
+    Tensor relu() const;
+
+    // Autograd, with the reference's names (tensor/Tensor.hpp:65-68). Everything a backward pass does
+    // to tensor data — the ones-fill of the root gradient, masks, accumulation — runs on the device.
+    void requires_grad(bool req);
+    bool requires_grad() const noexcept;
+    Tensor grad() const;            // an empty Tensor (no storage) until a backward pass reached it
+    void backward();                // root gradient of ones; throws without a grad_fn
+    bool defined() const noexcept { return static_cast<bool>(storage_); }
+
+    // Plumbing for code that records nodes (nn::Linear, cross_entropy).
+    std::shared_ptr<Node> grad_fn() const;
+    void set_grad_fn(std::shared_ptr<Node> fn, uint32_t output_nr = 0);
+    Edge gradient_edge() const;     // where this tensor's gradient flows: its grad_fn, or a leaf's accumulator
 
 private:
     Storage storage_;
     Shape shape_;
+    std::shared_ptr<AutogradMeta> autograd_meta_;
 };
 
+// ---- autograd graph -------------------------------------------------------------------------------
+class Node : public std::enable_shared_from_this<Node> {
+public:
+    std::vector<Edge> next_edges_;   // towards the nodes that produced this node's inputs
+    uint64_t sequence_nr_ = 0;       // creation order; the engine prefers later nodes among ready ones
+    Node();
+    virtual std::vector<Tensor> apply(std::vector<Tensor>&& grads) = 0;
+    virtual void release_saved() {}
+    virtual ~Node() = default;
+};
+
+struct AutogradMeta {
+    bool requires_grad_ = false;
+    Tensor grad_;
+    std::shared_ptr<Node> grad_fn_;
+    uint32_t output_nr_ = 0;
+    std::shared_ptr<Node> grad_accumulator_;   // created on first use for leaves
+};
+
+// Leaf sink: stores the incoming gradient as the tensor's grad, replacing an earlier one as the
+// reference does (autograd/AccumulateGrad.cpp:20-23).
+class AccumulateGrad : public Node {
+public:
+    explicit AccumulateGrad(std::weak_ptr<AutogradMeta> meta);
+    std::vector<Tensor> apply(std::vector<Tensor>&& grads) override;
+
+private:
+    std::weak_ptr<AutogradMeta> meta_;
+};
+
+class Engine {
+public:
+    // Runs the graph below `root` once: a node runs when every consumer of its output has delivered
+    // its gradient; gradients meeting at one input are added on the device.
+    void execute(std::shared_ptr<Node> root, const Tensor& initial_grad, bool keep_graph = false);
+};
+
+class ReluBackward : public Node {
+public:
+    explicit ReluBackward(const Tensor& input) : input_(input) {}
+    std::vector<Tensor> apply(std::vector<Tensor>&& grads) override;
+    void release_saved() override { input_ = Tensor(); }
+
+private:
+    Tensor input_;
+};
+
+// loss[1] = -(1/N) * sum_i log_softmax(logits)[i, labels[i]] for logits [N, C] (Float32) and labels [N]
+// (Int64), both on one CUDA device: the loss of examples/train_mlp.cpp:54-76 computed by one kernel,
+// which also leaves d loss / d logits for the backward node.
+Tensor cross_entropy(const Tensor& logits, const Tensor& labels);
+
 // ---- autograd node ----------------------------------------------------------------------------------
-class MatmulBackward {
+class MatmulBackward : public Node {
 public:
     MatmulBackward(const Tensor& a, const Tensor& b) : a_(a), b_(b) {}
     // {dA, dB} = {grad · Bᵀ, Aᵀ · grad}, no transpose copies.
-    std::vector<Tensor> apply(std::vector<Tensor>&& grads);
+    std::vector<Tensor> apply(std::vector<Tensor>&& grads) override;
+    void release_saved() override { a_ = Tensor(); b_ = Tensor(); }
 
 private:
     Tensor a_, b_;
@@ -157,6 +237,8 @@ public:
     Linear(int in_features, int out_features, bool bias = true, Device device = Device::cuda(0));
     // y = x · Wᵀ + b. The bias IS applied (it is zero-initialised, so results equal the reference's,
     // which registers the bias and leaves it out). fuse_relu applies ReLU in the same kernel.
+    // When x, the weight or the bias requires a gradient, one node computing all three gradients
+    // (tfb_linear_backward) is recorded.
     Tensor forward(Tensor x, bool fuse_relu = false);
     struct Grads {
         Tensor grad_input, grad_weight, grad_bias;
