@@ -264,6 +264,12 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
             dX = nullptr;
             if (dW == nullptr && db == nullptr) return TFB_OK;
         }
+        if ((dW != nullptr || db != nullptr) && !conv_tma_forced() && conv_direct_wgrad_eligible(s)) {
+            rc = conv_direct_wgrad(x, dY, dW, db, s, stream);
+            if (rc != TFB_OK) return rc;
+            dW = nullptr, db = nullptr;
+            if (dX == nullptr) return TFB_OK;
+        }
         const bool t_dx = dX != nullptr && conv_tma_eligible(s, s.Cout);
         const bool t_w = (dW != nullptr || db != nullptr) && conv_tma_eligible(s, s.Cin);
         if (t_dx || t_w) {

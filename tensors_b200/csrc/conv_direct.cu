@@ -130,6 +130,86 @@ conv_direct_dgrad_kernel(const float* __restrict__ dY, const float* __restrict__
         if (c0 + c < a.Cin) dX[((long long)n * a.Cin + c0 + c) * P + p] = acc[c];
 }
 
+// Weight and bias gradient for short filters (Cin * kH * kW + 1 <= 32):
+//   dW[co][k] = sum over samples and positions of dY[n][co][p] * x[n][c][iy][ix],  db[co] = sum of dY[n][co][p].
+// A block takes one sample and `chunks` runs of 128 output positions: it stages the dY tile
+// (64 channels x 128 positions) and the gathered activation patch (one row per filter tap, plus a row of
+// ones whose product is the bias gradient) in shared memory and multiplies them there; thread
+// (channel, tap group) keeps 8 sums in registers, walking the positions in ascending order. Each block
+// writes its 64 x 32 partial result; column_sums adds the blocks in a fixed order.
+constexpr int kWgPositions = 128, kWgCout = 64, kWgTaps = 32, kWgLd = kWgPositions + 4, kWgThreads = 256;
+constexpr size_t kWgSmem = (size_t)(kWgCout + kWgTaps) * kWgLd * sizeof(float);
+
+__global__ void __launch_bounds__(kWgThreads)
+conv_direct_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dY, float* __restrict__ partial,
+                         const DirectArgs a, int chunks, int chunk_groups, int cout_pad) {
+    extern __shared__ __align__(16) float wg_s[];
+    float (*dy_s)[kWgLd] = reinterpret_cast<float (*)[kWgLd]>(wg_s);
+    float (*xc_s)[kWgLd] = reinterpret_cast<float (*)[kWgLd]>(wg_s + kWgCout * kWgLd);
+    const int taps = a.Cin * a.kH * a.kW, khw = a.kH * a.kW;
+    const int Po = a.outH * a.outW;
+    const int n = blockIdx.z, co0 = blockIdx.y * kWgCout;
+    // thread (channel co_i, kq) owns taps k = 4 * j + kq, j < 8: the four kq of a channel read four
+    // different shared-memory rows whose bank offsets differ, so the reads do not conflict
+    const int co_i = threadIdx.x >> 2, kq = threadIdx.x & 3;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const float* xs = x + (long long)n * a.Cin * a.H * a.W;
+    const float* gs = dY + ((long long)n * a.Cout + co0) * Po;
+    for (int ch = 0; ch < chunks; ++ch) {
+        const int p0 = (blockIdx.x * chunks + ch) * kWgPositions;
+        if (p0 >= Po) break;
+        for (int i = threadIdx.x; i < kWgCout * kWgPositions; i += kWgThreads) {
+            const int co = i / kWgPositions, p = i - co * kWgPositions;
+            dy_s[co][p] = (co0 + co < a.Cout && p0 + p < Po) ? __ldg(gs + (long long)co * Po + p0 + p) : 0.f;
+        }
+        for (int i = threadIdx.x; i < kWgTaps * kWgPositions; i += kWgThreads) {
+            const int k = i / kWgPositions, p = i - k * kWgPositions;
+            float v = 0.f;
+            if (p0 + p < Po) {
+                if (k < taps) {
+                    const int c = k / khw, r = k - c * khw, ki = r / a.kW, kj = r - ki * a.kW;
+                    const int oy = (p0 + p) / a.outW, ox = (p0 + p) - oy * a.outW;
+                    const int iy = oy * a.sh - a.ph + ki * a.dh, ix = ox * a.sw - a.pw + kj * a.dw;
+                    if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) v = __ldg(xs + ((long long)c * a.H + iy) * a.W + ix);
+                } else if (k == taps) {
+                    v = 1.f;
+                }
+            }
+            xc_s[k][p] = v;
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int p = 0; p < kWgPositions; p += 4) {
+            const float4 g = *reinterpret_cast<const float4*>(&dy_s[co_i][p]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 b = *reinterpret_cast<const float4*>(&xc_s[4 * j + kq][p]);
+                acc[j] = fmaf(g.x, b.x, acc[j]);
+                acc[j] = fmaf(g.y, b.y, acc[j]);
+                acc[j] = fmaf(g.z, b.z, acc[j]);
+                acc[j] = fmaf(g.w, b.w, acc[j]);
+            }
+        }
+        __syncthreads();
+    }
+    float* out = partial + (((long long)n * chunk_groups + blockIdx.x) * cout_pad + co0 + co_i) * kWgTaps + kq;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) out[4 * j] = acc[j];
+}
+
+// dW[co][k] = sums[co * 32 + k] for k < taps; db[co] = sums[co * 32 + taps].
+__global__ void wgrad_direct_finish_kernel(const float* __restrict__ sums, int Cout, int taps, float* __restrict__ dW,
+                                           float* __restrict__ db) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= Cout * kWgTaps) return;
+    const int co = i / kWgTaps, k = i - co * kWgTaps;
+    if (k < taps) {
+        if (dW != nullptr) dW[(long long)co * taps + k] = sums[i];
+    } else if (k == taps && db != nullptr) {
+        db[co] = sums[i];
+    }
+}
+
 DirectArgs direct_args(const ConvShape& s) {
     return DirectArgs{(int)s.N, (int)s.Cin, (int)s.H, (int)s.W, (int)s.Cout, (int)s.kH, (int)s.kW, (int)s.sh,
                       (int)s.sw, (int)s.ph, (int)s.pw, (int)s.dh, (int)s.dw, (int)s.outH, (int)s.outW};
@@ -178,6 +258,54 @@ int conv_direct_dgrad(const float* dY, const float* w, float* dX, const ConvShap
     dim3 grid((unsigned)((P + kDirectThreads - 1) / kDirectThreads), (unsigned)((s.Cin + kDirectCin - 1) / kDirectCin),
               (unsigned)s.N);
     conv_direct_dgrad_kernel<<<grid, kDirectThreads, smem, stream>>>(dY, w, dX, direct_args(s));
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+}  // namespace tfb
+
+namespace tfb {
+
+bool conv_direct_wgrad_eligible(const ConvShape& s) {
+    return direct_enabled() && s.Cin * s.kH * s.kW + 1 <= kWgTaps && s.N < 65536 &&
+           (s.Cout + kWgCout - 1) / kWgCout < 65536 && s.outH * s.outW < (1ll << 30);
+}
+
+int conv_direct_wgrad(const float* x, const float* dY, float* dW, float* db, const ConvShape& s, cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    const int64_t Po = s.outH * s.outW;
+    const int64_t pos_chunks = (Po + kWgPositions - 1) / kWgPositions;
+    const int64_t co_tiles = (s.Cout + kWgCout - 1) / kWgCout, cout_pad = co_tiles * kWgCout;
+    // enough blocks to fill the GPU a few times over, few enough partial results to add up quickly
+    int64_t chunks = 1;
+    while (chunks < pos_chunks && s.N * co_tiles * ((pos_chunks + chunks - 1) / chunks) > 8ll * st->sm_count) chunks *= 2;
+    const int64_t chunk_groups = (pos_chunks + chunks - 1) / chunks;
+    const int64_t rows = s.N * chunk_groups, cols = cout_pad * kWgTaps;
+    const size_t part_bytes = ((size_t)(rows * cols) * 4 + 255) & ~(size_t)255;
+    const size_t sums_bytes = ((size_t)cols * 4 + 255) & ~(size_t)255;
+    void* ws_v = nullptr;
+    rc = workspace_get(stream, part_bytes + sums_bytes + column_sums_stage_bytes(cols) + 256, &ws_v);
+    if (rc != TFB_OK) return rc;
+    float* partial = static_cast<float*>(ws_v);
+    float* sums = reinterpret_cast<float*>(static_cast<uint8_t*>(ws_v) + part_bytes);
+    float* stage = reinterpret_cast<float*>(static_cast<uint8_t*>(ws_v) + part_bytes + sums_bytes);
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    TFB_CUDA_OK(cudaGetDevice(&dev));
+    if (!attr_set[dev]) {
+        TFB_CUDA_OK(cudaFuncSetAttribute(conv_direct_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWgSmem));
+        attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)chunk_groups, (unsigned)co_tiles, (unsigned)s.N);
+    conv_direct_wgrad_kernel<<<grid, kWgThreads, kWgSmem, stream>>>(x, dY, partial, direct_args(s), (int)chunks,
+                                                                    (int)chunk_groups, (int)cout_pad);
+    TFB_CUDA_OK(cudaGetLastError());
+    rc = column_sums(partial, rows, cols, cols, stage, sums, stream);
+    if (rc != TFB_OK) return rc;
+    const int total = (int)(s.Cout * kWgTaps);
+    wgrad_direct_finish_kernel<<<(total + 255) / 256, 256, 0, stream>>>(sums, (int)s.Cout, (int)(s.Cin * s.kH * s.kW), dW, db);
     TFB_CUDA_OK(cudaGetLastError());
     return TFB_OK;
 }

@@ -200,8 +200,6 @@ int plane_maps(CUtensorMap out[2], const float* hi, const float* lo, int64_t cp,
     return make_map_nd(&out[1], lo, 4, dims, strides, box, atom32);
 }
 
-constexpr int kBiasStageBlocks = 32;   // row blocks of the first bias-gradient reduction stage
-
 struct SpatialCall {
     const float* src_hi; const float* src_lo;   // NHWC planes of the tensor the taps are gathered from
     int64_t src_c, src_cp, src_H, src_W;        // its channels (contraction), padded channels, extent
@@ -271,6 +269,26 @@ int run_spatial(const SpatialCall& c, const ConvShape& s, const DeviceState* st,
 }
 
 }  // namespace
+
+constexpr int kColsumStageBlocks = 32;   // row blocks of the first reduction stage
+
+size_t column_sums_stage_bytes(int64_t cols) { return (size_t)(kColsumStageBlocks * ((cols + 3) / 4 * 4)) * 4; }
+
+int column_sums(const float* partial, int64_t rows, int64_t cols, int64_t ld, float* stage, float* out,
+                cudaStream_t stream) {
+    if (cols <= 0) return TFB_OK;
+    const int64_t stage_ld = (cols + 3) / 4 * 4;
+    const long long per_block = (rows + kColsumStageBlocks - 1) / kColsumStageBlocks;
+    const unsigned col_blocks = (unsigned)((cols + 31) / 32);
+    colsum_kernel<<<dim3(col_blocks, kColsumStageBlocks), dim3(32, 8), 0, stream>>>(partial, rows, (int)cols, ld,
+                                                                                    per_block > 0 ? per_block : 1, stage,
+                                                                                    (int)stage_ld);
+    TFB_CUDA_OK(cudaGetLastError());
+    colsum_kernel<<<dim3(col_blocks, 1), dim3(32, 8), 0, stream>>>(stage, kColsumStageBlocks, (int)cols, stage_ld,
+                                                                   kColsumStageBlocks, out, 0);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
 
 bool conv_tma_forced() {
     const char* e = getenv("TFB_CONV_TMA");
@@ -351,7 +369,7 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
     auto take = [&](size_t bytes) { size_t o = off; off += align256(bytes); return o; };
     const size_t o_dy = take((size_t)(2 * s.N * Po * cop) * 4);
     const size_t o_bsum = want_db ? take((size_t)(s.N * pblocks * cop) * 4) : 0;
-    const size_t o_bstage = want_db ? take((size_t)(kBiasStageBlocks * cop) * 4) : 0;
+    const size_t o_bstage = want_db ? take(column_sums_stage_bytes(s.Cout)) : 0;
     const size_t o_fd = want_dx ? take((size_t)(2 * s.Cin * khw * cop) * 4) : 0;
     const size_t o_x = want_dw ? take((size_t)(2 * s.N * P * cp) * 4) : 0;
     const size_t o_part = want_dw ? take((size_t)(splits * rows_per_split * ld_part) * 4) : 0;
@@ -366,16 +384,8 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
     rc = to_nhwc_planes(dY, s.N, s.Cout, Po, cop, dy_hi, dy_lo, bsum, stream);
     if (rc != TFB_OK) return rc;
     if (want_db) {
-        float* stage = reinterpret_cast<float*>(ws + o_bstage);
-        const long long rows = s.N * pblocks;
-        const long long per_block = (rows + kBiasStageBlocks - 1) / kBiasStageBlocks;
-        const unsigned col_blocks = (unsigned)((s.Cout + 31) / 32);
-        colsum_kernel<<<dim3(col_blocks, kBiasStageBlocks), dim3(32, 8), 0, stream>>>(bsum, rows, (int)s.Cout, cop,
-                                                                                      per_block, stage, (int)cop);
-        TFB_CUDA_OK(cudaGetLastError());
-        colsum_kernel<<<dim3(col_blocks, 1), dim3(32, 8), 0, stream>>>(stage, kBiasStageBlocks, (int)s.Cout, cop,
-                                                                       kBiasStageBlocks, db, 0);
-        TFB_CUDA_OK(cudaGetLastError());
+        rc = column_sums(bsum, s.N * pblocks, s.Cout, cop, reinterpret_cast<float*>(ws + o_bstage), db, stream);
+        if (rc != TFB_OK) return rc;
     }
     if (want_dx) {
         float* f_hi = reinterpret_cast<float*>(ws + o_fd);

@@ -114,12 +114,21 @@ int conv_tma_forward(const float* x, const float* w, const float* bias, float* o
 int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX, float* dW, float* db,
                       const ConvShape& s, cudaStream_t stream);
 
+// out[c] = sum over rows of partial[row * ld + c], c < cols, in an order fixed by (rows, cols) alone: two
+// launches; `stage` is scratch of column_sums_stage_bytes(cols) bytes.
+size_t column_sums_stage_bytes(int64_t cols);
+int column_sums(const float* partial, int64_t rows, int64_t cols, int64_t ld, float* stage, float* out,
+                cudaStream_t stream);
+
 // conv_direct.cu: CUDA-core kernels for short contractions (any stride). Forward: Cin*kH*kW <= 128;
-// input gradient: Cin <= 4.
+// input gradient: Cin <= 4; weight and bias gradient: Cin*kH*kW < 32.
 bool conv_direct_forward_eligible(const ConvShape& s);
 bool conv_direct_dgrad_eligible(const ConvShape& s);
 int conv_direct_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
                         cudaStream_t stream);
 int conv_direct_dgrad(const float* dY, const float* w, float* dX, const ConvShape& s, cudaStream_t stream);
+// Weight and bias gradient (either may be null) for Cin*kH*kW + 1 <= 32.
+bool conv_direct_wgrad_eligible(const ConvShape& s);
+int conv_direct_wgrad(const float* x, const float* dY, float* dW, float* db, const ConvShape& s, cudaStream_t stream);
 
 }  // namespace tfb

@@ -219,3 +219,15 @@ def test_conv_argument_errors():
     bad[11] = 0  # stride_h
     assert lib.tfb_conv2d_forward(*bad, capi.DTYPE_F32, stream_ptr()) == -1
     assert lib.tfb_conv2d_forward(None, ptr(t), None, ptr(t), *args[4:], capi.DTYPE_F32, stream_ptr()) == -1
+
+
+def test_empty_batch(feed):
+    # N = 0: nothing to compute; the weight and bias gradients of an empty batch are zeros
+    t = torch.full((64,), float("nan"), device="cuda")
+    gw, gb = torch.full((2 * 3 * 9,), float("nan"), device="cuda"), torch.full((2,), float("nan"), device="cuda")
+    args = [0, 3, 8, 8, 2, 3, 3, 1, 1, 1, 1, 1, 1]
+    capi.check(lib.tfb_conv2d_forward(ptr(t), ptr(t), None, ptr(t), *args, 0, capi.DTYPE_F32, stream_ptr()))
+    capi.check(lib.tfb_conv2d_backward(ptr(t), ptr(t), ptr(t), ptr(t), ptr(gw), ptr(gb), *args, capi.DTYPE_F32,
+                                       stream_ptr()))
+    assert_device_ok()
+    assert float(gw.abs().sum()) == 0.0 and float(gb.abs().sum()) == 0.0
