@@ -38,6 +38,34 @@ static std::vector<float> download(const Tensor& t) {
     return h;
 }
 
+// A node that records when it ran and hands nothing on: the engine's ordering can be checked without a GPU.
+struct ProbeNode : Node {
+    std::vector<int>* order;
+    int id;
+    ProbeNode(std::vector<int>* o, int i) : order(o), id(i) {}
+    std::vector<Tensor> apply(std::vector<Tensor>&&) override {
+        order->push_back(id);
+        return std::vector<Tensor>(next_edges_.size());
+    }
+};
+
+static void engine_order_checks() {
+    // diamond: root -> {left, right} -> sink, plus root -> sink directly. The sink must run once, last.
+    std::vector<int> order;
+    auto sink = std::make_shared<ProbeNode>(&order, 3);
+    auto left = std::make_shared<ProbeNode>(&order, 1);
+    auto right = std::make_shared<ProbeNode>(&order, 2);
+    auto root = std::make_shared<ProbeNode>(&order, 0);
+    left->next_edges_ = {Edge{sink, 0}};
+    right->next_edges_ = {Edge{sink, 0}, Edge{}};   // a null edge (input that needs no gradient) is skipped
+    root->next_edges_ = {Edge{left, 0}, Edge{right, 0}, Edge{sink, 1}};
+    Engine().execute(root, Tensor(), false);
+    CHECK(order.size() == 4 && order.front() == 0 && order.back() == 3);
+    // among ready nodes the later-created one runs first
+    CHECK(order.size() == 4 && order[1] == 2 && order[2] == 1);
+    Engine().execute(nullptr, Tensor(), false);     // nothing to do
+}
+
 static void cpu_checks() {
     CHECK(registered_cuda_matmul() != nullptr);   // the static registrar ran
     Tensor a = Tensor::empty(Shape{2, 3}, Dtype::Float32, Device::cpu());
@@ -52,6 +80,7 @@ static void cpu_checks() {
     tfb_register_kernels();
     CHECK(registered_cuda_matmul() != nullptr);
     CHECK(dtype_size(Dtype::BFloat16) == 2 && dtype_size(Dtype::Int64) == 8);
+    engine_order_checks();
     CHECK(throws([&] { a.backward(); }));         // no grad_fn (autograd/TensorAutograd.cpp:54-56)
     CHECK(!a.requires_grad() && !a.grad().defined());
     a.requires_grad(true);
