@@ -16,9 +16,11 @@ int fail(int code, const char* fmt, ...);
 #define TFB_CUDA_OK(expr)                                                                  \
     do {                                                                                   \
         cudaError_t e_ = (expr);                                                           \
-        if (e_ != cudaSuccess)                                                             \
+        if (e_ != cudaSuccess) {                                                           \
+            (void)cudaGetLastError(); /* reported here: a later call must not see it again */ \
             return ::tfb::fail(TFB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,               \
                                cudaGetErrorString(e_), __FILE__, __LINE__);                \
+        }                                                                                  \
     } while (0)
 
 // Per-device state created on first use with that device current.

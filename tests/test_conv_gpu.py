@@ -48,8 +48,8 @@ def conv_backward(x, w, g, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
 @pytest.fixture(params=["default", "tma_feed", "gather_kernel"])
 def feed(request):
     """By default a stride-1 product with at least 16 contraction channels runs on the TMA-fed GEMM
-    kernel, short contractions (forward with Cin*kH*kW <= 128, input gradient with Cin <= 4) on the
-    CUDA-core kernels and everything else on the kernel with software gather producers.
+    kernel, short contractions (forward with Cin*kH*kW <= 128, input gradient with Cin <= 4, weight
+    gradient with Cin*kH*kW < 32) on the CUDA-core kernels and everything else on the kernel with software gather producers.
     TFB_CONV_TMA=2 sends every stride-1 product to the first, TFB_CONV_TMA=0 with TFB_CONV_DIRECT=0
     everything to the last, so each kernel gets every case it can take."""
     old = {k: os.environ.get(k) for k in ("TFB_CONV_TMA", "TFB_CONV_DIRECT")}
