@@ -91,9 +91,17 @@ class MLP:
         batch = X.shape[0]
         acts = [X]
         self._xs, self._ws = [], []
+        # All weights live in one flat buffer with 16-byte aligned segments, so one launch splits them
+        # all; a weight whose row length is a multiple of 4 is then a view of the flat planes.
+        flat, _ = self._split(("params",), self.params.view(1, -1))
         for i in range(self.L):
             xs, ldx = self._split(("x", i), acts[-1])
-            ws, ldw = self._split(("w", i), self.weight(i))
+            if self.dims[i] % 4 == 0:
+                n = self.dims[i + 1] * self.dims[i]
+                ws = flat[:, 0, self.offsets[2 * i]:self.offsets[2 * i] + n].view(2, self.dims[i + 1], self.dims[i])
+                ldw = self.dims[i]
+            else:
+                ws, ldw = self._split(("w", i), self.weight(i))
             Y = torch.empty((batch, self.dims[i + 1]), device=X.device, dtype=torch.float32)
             flags = capi.EPI_BIAS_COL | (capi.EPI_RELU if i < self.L - 1 else 0)
             capi.check(lib.tfb_gemm_presplit(_p(xs[0]), _p(xs[1]), _p(ws[0]), _p(ws[1]), _p(Y), batch,

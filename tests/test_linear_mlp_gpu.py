@@ -189,3 +189,40 @@ def test_mlp_graph_replay_matches_eager_steps(oracle):
     assert_device_ok()
     assert torch.equal(eager.params, graphed.params)
     assert float(eager.loss.item()) == float(graphed.loss.item())
+
+
+def test_mlp_full_batch_data_parallel_invariance(oracle):
+    # The named configuration at its full global batch of 8192 rows. The batch is cut into G row shards
+    # as G data-parallel ranks would hold them; each shard's gradient is scaled by the GLOBAL batch, so
+    # the shard gradients must add up to the one-rank gradient for every G (up to FP32 summation order),
+    # and the shard losses to the full-batch loss. The oracle covers the loss (its forward pass alone is
+    # ~30 GFLOP of scalar loops) through a sample of rows: the per-row loss terms of those rows.
+    from tensors_b200.mlp import MLP, shard_rows
+    dims, batch = (784, 1024, 1024, 10), 8192
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    xb, lab = refdata.mnist_like(7, (batch, 784)), refdata.labels(8, batch)
+    X, L = dev(xb), torch.from_numpy(lab).cuda()
+    full = MLP(dims, ws)
+    full.forward_backward(X, L)
+    assert_device_ok()
+    g1, loss1 = full.grads.clone(), float(full.loss.item())
+    assert np.isfinite(loss1) and 2.0 < loss1 < 2.7   # ten classes, small random weights: about ln 10
+    for G in (2, 4, 8):
+        total, loss = torch.zeros_like(g1), 0.0
+        for r in range(G):
+            b, e = shard_rows(batch, r, G)
+            m = MLP(dims, ws)
+            m.forward_backward(X[b:e], L[b:e], global_rows=batch)
+            total += m.grads
+            loss += float(m.loss.item())
+        assert_device_ok()
+        assert float((total - g1).norm() / g1.norm()) < 1e-5, G
+        assert abs(loss - loss1) < 1e-5, G
+    # sampled oracle: the first 64 rows as one rank's shard of the global batch
+    sub = MLP(dims, ws)
+    sub.forward_backward(X[:64], L[:64], global_rows=batch)
+    ol, odw, _ = oracle.mlp_grads(xb[:64], lab[:64], ws, bs=[np.zeros(d, np.float32) for d in dims[1:]],
+                                  global_rows=batch)
+    assert abs(float(sub.loss.item()) - ol) < 1e-6
+    for i in range(3):
+        assert rel_err(sub.weight(i, sub.grads).cpu().numpy(), odw[i]) < 2e-5, i
