@@ -2,7 +2,9 @@
 // nodes. Every loop over tensor data that the reference runs on the host during a backward pass is a
 // libtfb kernel here, so gradients of CUDA tensors never visit the host.
 #include <atomic>
+#include <cmath>
 #include <queue>
+#include <random>
 #include <unordered_map>
 #include <unordered_set>
 
@@ -81,6 +83,34 @@ public:
 
 private:
     Tensor dlogits_;
+};
+
+class Conv2dBackward : public Node {
+public:
+    Conv2dBackward(Tensor x, Tensor w, int k, int stride, int padding, int dilation, bool bias)
+        : x_(std::move(x)), w_(std::move(w)), k_(k), stride_(stride), padding_(padding), dilation_(dilation), bias_(bias),
+          need_dx_(x_.requires_grad()) {}
+    std::vector<Tensor> apply(std::vector<Tensor>&& grads) override {
+        const Tensor& dy = grads.at(0);
+        const Shape& in = x_.shape();
+        const int64_t cout = w_.shape()[0];
+        DeviceGuard g(x_.device().index);
+        // the input gradient of a first layer is nobody's input: skip that product
+        Tensor dx = need_dx_ ? Tensor::empty(Shape{in[0], in[1], in[2], in[3]}, Dtype::Float32, x_.device()) : Tensor();
+        Tensor dw = Tensor::empty(Shape{cout, in[1], k_, k_}, Dtype::Float32, x_.device());
+        Tensor db = bias_ ? Tensor::empty(Shape{cout}, Dtype::Float32, x_.device()) : Tensor();
+        ok(tfb_conv2d_backward(x_.data(), w_.data(), dy.data(), need_dx_ ? dx.data() : nullptr, dw.data(),
+                               bias_ ? static_cast<float*>(db.data()) : nullptr, in[0], in[1], in[2], in[3], cout, k_, k_,
+                               stride_, stride_, padding_, padding_, dilation_, dilation_, TFB_DTYPE_F32, stream_of(x_)),
+           "tfb_conv2d_backward");
+        return {std::move(dx), std::move(dw), std::move(db)};
+    }
+    void release_saved() override { x_ = Tensor(); w_ = Tensor(); }
+
+private:
+    Tensor x_, w_;
+    int k_, stride_, padding_, dilation_;
+    bool bias_, need_dx_;
 };
 
 }  // namespace
@@ -238,4 +268,47 @@ Tensor cross_entropy(const Tensor& logits, const Tensor& labels) {
     return loss;
 }
 
+namespace nn {
+
+Conv2dModule::Conv2dModule(int in_channels, int out_channels, int kernel_size, int stride, int padding, int dilation,
+                           bool bias, Device device)
+    : in_channels_(in_channels), out_channels_(out_channels), kernel_size_(kernel_size), stride_(stride),
+      padding_(padding), dilation_(dilation), bias_enabled_(bias) {
+    std::vector<float> w(static_cast<size_t>(out_channels) * in_channels * kernel_size * kernel_size);
+    const float bound = std::sqrt(1.0f / static_cast<float>(in_channels * kernel_size * kernel_size));
+    std::mt19937 rng(0xC0FFEEu);
+    std::uniform_real_distribution<float> dist(-bound, bound);
+    for (float& v : w) v = dist(rng);
+    weight_ = Tensor::from_host(w.data(), Shape{out_channels, in_channels, kernel_size, kernel_size}, Dtype::Float32, device);
+    weight_.requires_grad(true);
+    if (bias_enabled_) {
+        std::vector<float> b(static_cast<size_t>(out_channels), 0.0f);
+        bias_ = Tensor::from_host(b.data(), Shape{out_channels}, Dtype::Float32, device);
+        bias_.requires_grad(true);
+    }
+}
+
+Tensor Conv2dModule::forward(Tensor x) {
+    const Shape& s = x.shape();
+    if (s.ndim() != 4) throw std::invalid_argument("Conv2dModule.forward expects [N, Cin, H, W]");
+    if (s[1] != in_channels_) throw std::invalid_argument("Conv2dModule.forward: Cin mismatch");
+    require_cuda_f32(x, "Conv2dModule.forward");
+    DeviceGuard g(x.device().index);
+    const int64_t oh = tfb_conv_out_dim(s[2], kernel_size_, stride_, padding_, dilation_);
+    const int64_t ow = tfb_conv_out_dim(s[3], kernel_size_, stride_, padding_, dilation_);
+    if (oh <= 0 || ow <= 0) throw std::invalid_argument("Conv2dModule.forward: empty output");
+    Tensor out = Tensor::empty(Shape{s[0], out_channels_, oh, ow}, Dtype::Float32, x.device());
+    ok(tfb_conv2d_forward(x.data(), weight_.data(), bias_enabled_ ? static_cast<const float*>(bias_.data()) : nullptr,
+                          out.data(), s[0], s[1], s[2], s[3], out_channels_, kernel_size_, kernel_size_, stride_, stride_,
+                          padding_, padding_, dilation_, dilation_, 0, TFB_DTYPE_F32, stream_of(x)),
+       "tfb_conv2d_forward");
+    if (x.requires_grad() || weight_.requires_grad() || (bias_enabled_ && bias_.requires_grad())) {
+        auto node = std::make_shared<Conv2dBackward>(x, weight_, kernel_size_, stride_, padding_, dilation_, bias_enabled_);
+        node->next_edges_ = {x.gradient_edge(), weight_.gradient_edge(), bias_enabled_ ? bias_.gradient_edge() : Edge{}};
+        out.set_grad_fn(std::move(node));
+    }
+    return out;
+}
+
+}  // namespace nn
 }  // namespace tensorforge

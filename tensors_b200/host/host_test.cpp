@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <random>
 #include <string>
 #include <vector>
 
@@ -186,6 +187,47 @@ static void autograd_checks() {
         Tensor loss3 = cross_entropy(fc2.forward(fc1.forward(x).relu()), labels);
         loss3.backward();
         same(fc2.weight().grad(), g2.grad_weight);
+    }
+    // Conv2dModule: reference initialisation, and backward through the recorded node against the explicit
+    // Conv2d::backward call (which the oracle checks) — y.backward() seeds a gradient of ones
+    {
+        nn::Conv2dModule conv(3, 8, 3, 1, 1);
+        std::vector<float> wexp(8 * 3 * 9);
+        {
+            const float bound = std::sqrt(1.0f / 27.0f);
+            std::mt19937 rng(0xC0FFEEu);
+            std::uniform_real_distribution<float> dist(-bound, bound);
+            for (float& v : wexp) v = dist(rng);
+        }
+        auto wh = download(conv.weight());
+        for (size_t i = 0; i < wexp.size(); ++i) CHECK(wh[i] == wexp[i]);
+        for (float b : download(conv.bias())) CHECK(b == 0.f);
+        std::vector<float> xh(2 * 3 * 6 * 5);
+        for (size_t i = 0; i < xh.size(); ++i) xh[i] = 0.05f * float((i * 13) % 17) - 0.4f;
+        Tensor x = upload(xh, Shape{2, 3, 6, 5});
+        x.requires_grad(true);
+        Tensor y = conv.forward(x);
+        CHECK(y.shape()[1] == 8 && y.shape()[2] == 6 && y.shape()[3] == 5 && y.grad_fn() != nullptr);
+        y.backward();
+        nn::Conv2d plain(3, 8, 3, 3, 1, 1, 1, 1);
+        plain.weight() = conv.weight();
+        auto gr = plain.backward(upload(std::vector<float>(2 * 8 * 6 * 5, 1.f), Shape{2, 8, 6, 5}), x);
+        auto eq = [&](const Tensor& a, const Tensor& b) {
+            auto ah = download(a), bh = download(b);
+            CHECK(ah.size() == bh.size());
+            for (size_t i = 0; i < ah.size() && i < bh.size(); ++i) CHECK(approx(ah[i], bh[i], 1e-6f));
+        };
+        eq(x.grad(), gr.grad_input);
+        eq(conv.weight().grad(), gr.grad_weight);
+        eq(conv.bias().grad(), gr.grad_bias);
+        auto gb = download(conv.bias().grad());
+        CHECK(approx(gb[0], 60.f, 1e-6f));   // 2 samples x 30 positions of ones
+        // an input that asks for no gradient gets none, the parameters still do
+        Tensor x2 = upload(xh, Shape{2, 3, 6, 5});
+        conv.forward(x2).backward();
+        CHECK(!x2.grad().defined());
+        eq(conv.weight().grad(), gr.grad_weight);
+        CHECK(throws([&] { (void)conv.forward(upload({1, 2, 3, 4}, Shape{1, 1, 2, 2})); }));   // Cin mismatch
     }
 }
 

@@ -13,6 +13,7 @@
 //   ReluBackward, Tensor::backward    autograd/ops/ReluBackward.hpp:22-32, autograd/TensorAutograd.cpp:52-73
 //   cross_entropy                     the loss graph of examples/train_mlp.cpp:54-76, as one node
 //   nn::Linear, nn::Conv2d            nn/Linear.hpp, nn/Conv2d.hpp:32-61
+//   nn::Conv2dModule                  nn/Conv2dModule.hpp:16-32, nn/Conv2dModule.cpp:74-106
 //
 // Only CUDA tensors are served: CPU tensors stay on the reference's own loops, and there is no
 // fallback of any kind — a missing registration or a failing library call throws.
@@ -278,6 +279,24 @@ public:
 private:
     int64_t in_channels_, out_channels_, kernel_h_, kernel_w_, stride_h_, stride_w_, pad_h_, pad_w_, dilation_h_,
         dilation_w_;
+    bool bias_enabled_;
+    Tensor weight_, bias_;
+};
+
+// The trainable convolution of the reference (nn/Conv2dModule.hpp:16-32, nn/Conv2dModule.cpp:74-106), on
+// the GPU: square kernel / stride / padding / dilation, weight ~ U(±sqrt(1/(Cin·k·k))) from
+// mt19937(0xC0FFEE), zero bias, both requiring gradients. forward() records one node that computes the
+// input, weight and bias gradients with tfb_conv2d_backward.
+class Conv2dModule {
+public:
+    Conv2dModule(int in_channels, int out_channels, int kernel_size, int stride = 1, int padding = 0,
+                 int dilation = 1, bool bias = true, Device device = Device::cuda(0));
+    Tensor forward(Tensor x);
+    Tensor& weight() { return weight_; }
+    Tensor& bias() { return bias_; }
+
+private:
+    int in_channels_, out_channels_, kernel_size_, stride_, padding_, dilation_;
     bool bias_enabled_;
     Tensor weight_, bias_;
 };
