@@ -26,3 +26,13 @@ def test_host_mirror_known_answers_on_gpu():
     r = subprocess.run([os.path.join(HOST, "host_test"), "gpu"], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "all passed" in r.stdout
+
+
+@pytest.mark.gpu
+def test_training_loop_on_the_host_mirror_learns():
+    # Linear -> relu -> Linear -> cross_entropy -> backward -> SGD, all on the device; exits 0 when the
+    # loss at least halves
+    build()
+    r = subprocess.run([os.path.join(HOST, "train_mlp_b200"), "100", "256", "128"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "final_loss" in r.stdout
