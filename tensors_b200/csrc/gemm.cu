@@ -106,15 +106,27 @@ __device__ __forceinline__ float tf32_round(float x) {
 // hi = x rounded to TF32 (10-bit mantissa), lo = x - hi (exact in FP32).
 // One thread per group of 4 output columns; ld_out is a multiple of 4 so the stores are
 // 16-byte vectors. Columns in [cols, ld_out) are written as zeros.
-__global__ void split_tf32_kernel(const float* __restrict__ src, long long rows, long long cols,
-                                  long long ld, const float* __restrict__ mask,
-                                  float* __restrict__ hi, float* __restrict__ lo, long long ld_out) {
+struct SplitJob {
+    const float* src;
+    long long rows, cols, ld;
+    const float* mask;
+    float* hi;
+    float* lo;
+    long long ld_out;
+};
+
+// The work of blocks [0, nblocks) on one matrix; `block` is this block's index among them.
+__device__ __forceinline__ void split_tf32_body(const SplitJob& job, long long block, long long nblocks) {
+    const float* __restrict__ src = job.src;
+    const float* __restrict__ mask = job.mask;
+    float* __restrict__ hi = job.hi;
+    float* __restrict__ lo = job.lo;
+    const long long rows = job.rows, cols = job.cols, ld = job.ld, ld_out = job.ld_out;
     const long long groups = ld_out >> 2;
     const long long total = rows * groups;
     const bool vec_in = ((ld & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) &&
                         (mask == nullptr || (reinterpret_cast<uintptr_t>(mask) & 15u) == 0);
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x) {
+    for (long long i = block * blockDim.x + threadIdx.x; i < total; i += nblocks * blockDim.x) {
         const long long r = i / groups;
         const long long c = (i - r * groups) << 2;
         float x[4] = {0.f, 0.f, 0.f, 0.f};
@@ -148,6 +160,19 @@ __global__ void split_tf32_kernel(const float* __restrict__ src, long long rows,
         *reinterpret_cast<float4*>(hi + r * ld_out + c) = make_float4(h[0], h[1], h[2], h[3]);
         *reinterpret_cast<float4*>(lo + r * ld_out + c) = make_float4(l[0], l[1], l[2], l[3]);
     }
+}
+
+__global__ void split_tf32_kernel(const float* __restrict__ src, long long rows, long long cols,
+                                  long long ld, const float* __restrict__ mask,
+                                  float* __restrict__ hi, float* __restrict__ lo, long long ld_out) {
+    const SplitJob job{src, rows, cols, ld, mask, hi, lo, ld_out};
+    split_tf32_body(job, blockIdx.x, gridDim.x);
+}
+
+// Both operands of a product in one launch: blocks [0, blocks_a) split A, the rest split B.
+__global__ void split_tf32_pair_kernel(const SplitJob a, const SplitJob b, int blocks_a) {
+    if ((int)blockIdx.x < blocks_a) split_tf32_body(a, blockIdx.x, blocks_a);
+    else split_tf32_body(b, (long long)blockIdx.x - blocks_a, (long long)gridDim.x - blocks_a);
 }
 
 // Copies a 16-bit matrix into a buffer whose leading dimension is a multiple of 8.
@@ -421,15 +446,15 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     };
     if (c.K > 0) {
         if (f32) {
+            SplitJob jobs[2];
+            int njobs = 0;
             if (c.a_presplit) {
                 a_ptr[1] = static_cast<const float*>(c.A) + c.a_lo_off;
             } else {
                 const int64_t ldp = round_up(a_cols, 4);
                 float* hi = reinterpret_cast<float*>(carve((size_t)(2 * a_rows * ldp * 4)));
                 float* lo = hi + a_rows * ldp;
-                rc = split_operand_on(st->sm_count, static_cast<const float*>(c.A), a_rows, a_cols, c.lda,
-                                      c.a_mask, hi, lo, ldp, stream);
-                if (rc != TFB_OK) return rc;
+                jobs[njobs++] = SplitJob{static_cast<const float*>(c.A), a_rows, a_cols, c.lda, c.a_mask, hi, lo, ldp};
                 a_ptr[0] = hi; a_ptr[1] = lo; lda = ldp;
             }
             if (c.b_presplit) {
@@ -438,10 +463,19 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
                 const int64_t ldp = round_up(b_cols, 4);
                 float* hi = reinterpret_cast<float*>(carve((size_t)(2 * b_rows * ldp * 4)));
                 float* lo = hi + b_rows * ldp;
-                rc = split_operand_on(st->sm_count, static_cast<const float*>(c.B), b_rows, b_cols, c.ldb,
-                                      nullptr, hi, lo, ldp, stream);
-                if (rc != TFB_OK) return rc;
+                jobs[njobs++] = SplitJob{static_cast<const float*>(c.B), b_rows, b_cols, c.ldb, nullptr, hi, lo, ldp};
                 b_ptr[0] = hi; b_ptr[1] = lo; ldb = ldp;
+            }
+            if (njobs == 1) {
+                rc = split_operand_on(st->sm_count, jobs[0].src, jobs[0].rows, jobs[0].cols, jobs[0].ld, jobs[0].mask,
+                                      jobs[0].hi, jobs[0].lo, jobs[0].ld_out, stream);
+                if (rc != TFB_OK) return rc;
+            } else if (njobs == 2) {
+                // one launch for both operands, blocks shared out in proportion to their sizes
+                const long long ia = jobs[0].rows * (jobs[0].ld_out >> 2), ib = jobs[1].rows * (jobs[1].ld_out >> 2);
+                const int ga = grid_for(ia, 256, st->sm_count), gb = grid_for(ib, 256, st->sm_count);
+                split_tf32_pair_kernel<<<ga + gb, 256, 0, stream>>>(jobs[0], jobs[1], ga);
+                TFB_CUDA_OK(cudaGetLastError());
             }
         } else {
             if (c.a_mask != nullptr)
