@@ -278,3 +278,41 @@ def test_row_panels_over_the_devices_of_one_process(oracle, in_dtype):
     bad = (ctypes.c_int * n)(*([devices[0]] * (n - 1) + [ndev + 3]))
     assert lib.tfb_matmul_row_panels(n, bad, arr(A), arr(B), arr(C), (ctypes.c_int64 * n)(*rows), N, K, in_dtype,
                                      capi.DTYPE_F32, streams) == -1
+
+
+@pytest.mark.parametrize("case", [
+    # M, N, K, trans_a, trans_b, flags: one extent of at most 16 (tiles that are mostly padding)
+    (700, 10, 1500, False, True, capi.EPI_BIAS_COL | capi.EPI_RELU),   # narrow N: a classifier head
+    (256, 16, 64, False, True, capi.EPI_NONE),
+    (513, 1001, 10, False, False, capi.EPI_BIAS_ROW),                  # short K, ragged columns
+    (2048, 1024, 10, False, False, capi.EPI_NONE),                     # short K: the gradient behind the head
+    (10, 1024, 4096, True, False, capi.EPI_NONE),                      # narrow M: the head's weight gradient
+    (3, 130, 300, True, False, capi.EPI_NONE),
+])
+def test_narrow_products_against_oracle(oracle, case):
+    M, N, K, ta, tb, flags = case
+    a, b = refdata.uniform(17, (M, K)), refdata.uniform(18, (K, N))
+    bias = refdata.normal(19, (M if flags & capi.EPI_BIAS_ROW else N,))
+    want = oracle.matmul(a, b)
+    if flags & capi.EPI_BIAS_COL:
+        want = want + bias[None, :]
+    if flags & capi.EPI_BIAS_ROW:
+        want = want + bias[:, None]
+    if flags & capi.EPI_RELU:
+        want = np.maximum(want, 0)
+    A, B = dev(a.T.copy() if ta else a), dev(b.T.copy() if tb else b)
+    C = gemm_ex(A, B, M, N, K, ta, tb, bias=dev(bias) if flags else None, flags=flags)
+    # and with both operands given as hi / lo planes
+    lda, ldb = (A.shape[1] + 3) // 4 * 4, (B.shape[1] + 3) // 4 * 4
+    ap = torch.full((2, A.shape[0], lda), float("nan"), device="cuda")
+    bp = torch.full((2, B.shape[0], ldb), float("nan"), device="cuda")
+    capi.check(lib.tfb_split_tf32(ptr(A), A.shape[0], A.shape[1], A.shape[1], ptr(ap[0]), ptr(ap[1]), lda, stream_ptr()))
+    capi.check(lib.tfb_split_tf32(ptr(B), B.shape[0], B.shape[1], B.shape[1], ptr(bp[0]), ptr(bp[1]), ldb, stream_ptr()))
+    C2 = torch.full((M, N), float("nan"), device="cuda")
+    bias_d = dev(bias) if flags else None
+    capi.check(lib.tfb_gemm_presplit(ptr(ap[0]), ptr(ap[1]), ptr(bp[0]), ptr(bp[1]), ptr(C2), M, N, K, lda, ldb, N,
+                                     int(ta), int(tb), ptr(bias_d), flags, stream_ptr()))
+    assert_device_ok()
+    for got in (C.cpu().numpy(), C2.cpu().numpy()):
+        assert not np.isnan(got).any()
+        assert rel_err(got, want) < FP32_TOL
