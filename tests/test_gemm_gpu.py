@@ -219,7 +219,7 @@ def test_split_k_shapes_against_oracle(oracle, shape, trans_a, trans_b, in_dtype
 @pytest.mark.parametrize("pinned", [True, False])
 @pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
 def test_matmul_on_host_buffers(oracle, in_dtype, pinned):
-    # three row panels (the last one ragged), copies overlapped with the products inside the call
+    # five row panels (the last one ragged), copies overlapped with the products inside the call
     import ctypes
     M, N, K = 2500, 300, 200
     tdt = torch.float32 if in_dtype == capi.DTYPE_F32 else torch.bfloat16
