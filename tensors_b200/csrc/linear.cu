@@ -15,7 +15,7 @@ namespace tfb {
 
 namespace {
 
-constexpr int kColsumRowsPerBlock = 32;
+constexpr int kColsumRowsPerBlock = 16;
 
 __device__ __forceinline__ float tf32_rna(float x) {
     uint32_t r;
@@ -37,6 +37,7 @@ __global__ void split_mask_colsum_kernel(const float* __restrict__ dY, const flo
     const bool vec = ((ld & 3) == 0) && (c + 4 <= cols) && ((reinterpret_cast<uintptr_t>(dY) & 15u) == 0) &&
                      (Y == nullptr || (reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
     float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
     for (long long r = r0; r < r1; ++r) {
         float x[4] = {0.f, 0.f, 0.f, 0.f};
         if (vec) {
