@@ -1,16 +1,30 @@
 #!/usr/bin/env python
 """Headline benchmark: square GEMM C = A·B at M=N=K=8192 through the C-ABI of libtfb.so.
 
-One "step" is one FP32 product (error-compensated 3xTF32 on the tcgen05 tensor cores: one
-launch that splits both operands plus the GEMM launch). The same run also measures the BF16-input /
-FP32-accumulate product, the GEMM kernel alone for the roofline, and the end-to-end path with
-host buffers (pinned host -> device copies, product, device -> host copy inside the timed region).
+One "step" is one FP32 product (error-compensated 3xTF32 on the tcgen05 tensor cores: one launch that
+splits both operands plus the GEMM launch). Every timed loop runs after a pre-heat of at least one
+second of the same work, so all figures of a line are taken in the same (power-capped) clock state,
+and every loop carries its own clock samples. The same line also holds:
+
+  roofline      the GEMM kernel alone (operands pre-split), timed right before and right after the
+                headline loop, against the measured BF16 peak / 6
+  sustained     the same step back to back for at least two seconds
+  bf16          the BF16-input / FP32-accumulate product
+  e2e           the product through tfb_matmul_host: pinned host buffers in and out, copies inside the
+                timed region
+  sweep         the five sizes of the square sweep, FP32 and BF16
+  strong_16384  one 16384^3 product split into N row panels (B staged per GPU beforehand): the one
+                point of the curve that is not embarrassingly parallel in its size
+  mlp_dp        the data-parallel MLP training step (784-1024-1024-10, global batch 8192 sharded over
+                the ranks, SGD lr 0.1 momentum 0.9): step time with the fused peer-memory exchange and
+                with one NCCL all-reduce, the exchange alone, and loss + gradient norm after exactly one
+                step from identical parameters next to the single-rank values
+  cpu_baseline  the reference's own CPU Tensor::matmul on a bounded sample (rank 0, N = 1 only)
 
 N GPUs (one process per GPU under torch.distributed.run): weak scaling by M row-panels — every rank
-multiplies its own 8192-row panel of A by a replicated B; there is no data-path collective.
-
-`--impl reference` times the reference's own CPU Tensor::matmul (the unmodified reference compiled
-into oracle/_ref, else the C restatement in oracle/) on row panels of the same product.
+multiplies its own 8192-row panel of A by a replicated B; there is no data-path collective in the
+headline. `--impl reference` times the reference's own CPU Tensor::matmul (the unmodified reference
+compiled into oracle/_ref, else the C restatement in oracle/) on row panels of the same product.
 """
 import argparse
 import ctypes
@@ -29,6 +43,7 @@ for _p in (ROOT, os.path.join(ROOT, "tests")):
 
 METRIC = "GEMM TFLOPS (3xTF32-FP32 & BF16) and % tensor-pipe peak at 1/2/4/8 B200"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+MLP_DIMS, MLP_BATCH, MLP_FLOP = (784, 1024, 1024, 10), 8192, 78.35e9
 
 
 def load_peaks():
@@ -89,7 +104,7 @@ class ClockSampler:
         if self.thread is not None:
             self.thread.join(timeout=2)
 
-    def summary(self, t0, t1):
+    def summary(self, t0, t1, ms=None):
         sm, reasons = [], set()
         for ts, mhz, mask in self.samples:
             if ts < t0 or ts > t1:
@@ -100,8 +115,11 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": self.sm_max, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": self.sm_max, "reasons": sorted(reasons),
+               "samples": len(sm)}
+        if ms is not None:
+            out["ms_x_mhz"] = ms * out["sm_mhz"]   # clock-normalised time: compare these between loops
+        return out
 
 
 # ------------------------------------------------------------------------------------------
@@ -109,7 +127,6 @@ def reference_arm(args, rank):
     """The reference's own CPU matmul on row panels of the 8192^3 product, all host threads."""
     if rank != 0:
         return
-    import numpy as np
     import refdata
     from oracle_lib import Oracle, Reference, have_reference
 
@@ -163,24 +180,73 @@ def reference_arm(args, rank):
 
 
 # ------------------------------------------------------------------------------------------
-def ours(args, rank, world, local_rank):
-    import numpy as np
-    import torch
-    import torch.distributed as dist
+class Harness:
+    """Timing plumbing shared by the sections: CUDA events on the launching stream, barrier +
+    synchronize on both sides, maximum over ranks, a pre-heat of the same work, clock samples."""
 
+    def __init__(self, rank, world, local_rank, sampler):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.rank, self.world, self.local_rank, self.sampler = rank, world, local_rank, sampler
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        if self.world == 1:
+            return v
+        t = self.torch.tensor([v], device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def preheat(self, fn, seconds, min_steps):
+        """At least min_steps calls of fn and about `seconds` of device time. Every rank runs the SAME
+        number of calls (fn may contain a collective): the count comes from a first timed batch whose
+        duration is the maximum over ranks."""
+        torch = self.torch
+        first = max(4, int(min_steps))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(first):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = self.max_over_ranks(e0.elapsed_time(e1) / first)
+        extra = int(max(0.0, seconds * 1e3 - ms * first) / max(ms, 1e-3))
+        for _ in range(min(extra, 200000)):
+            fn()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, steps, warmup, preheat_s=1.0):
+        torch = self.torch
+        self.preheat(fn, preheat_s, warmup)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        self.barrier()
+        t1 = time.time()
+        ms = self.max_over_ranks(e0.elapsed_time(e1) / steps)
+        clocks = self.sampler.summary(t0, t1, ms) if self.rank == 0 else None
+        return ms, clocks
+
+    def sustained(self, fn, seconds, ms_hint):
+        """fn back to back for at least `seconds`: the step count is fixed beforehand from ms_hint so
+        that every rank runs the same number."""
+        steps = max(8, int(seconds * 1e3 / max(ms_hint, 1e-3)) + 1)
+        return self.timed(fn, steps, 0, preheat_s=0.0) + (steps,)
+
+
+def section_gemm(h, args, capi, lib, peaks, peak_src):
     import refdata
-    import tensors_b200.capi as capi
-
-    lib = capi.lib
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        # NCCL announces its version on stdout at this level; stdout carries the one JSON line only.
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    capi.check(lib.tfb_init())
+    torch = h.torch
     n = args.n
-    peaks, peak_src = load_peaks()
 
     def stream():
         return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -189,7 +255,7 @@ def ours(args, rank, world, local_rank):
         return ctypes.c_void_p(t.data_ptr())
 
     # Inputs: uniform[-1,1); B is replicated, each rank owns its own row panel of A.
-    A_h = torch.from_numpy(refdata.uniform(1000 + rank, (n, n))).pin_memory()
+    A_h = torch.from_numpy(refdata.uniform(1000 + h.rank, (n, n))).pin_memory()
     B_h = torch.from_numpy(refdata.uniform(1, (n, n))).pin_memory()
     C_h = torch.empty((n, n), dtype=torch.float32).pin_memory()
     A = A_h.cuda(non_blocking=True)
@@ -197,32 +263,6 @@ def ours(args, rank, world, local_rank):
     C = torch.empty((n, n), device="cuda", dtype=torch.float32)
     A16, B16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
     torch.cuda.synchronize()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.time()
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        t1 = time.time()
-        return max_over_ranks(e0.elapsed_time(e1) / steps), t0, t1
 
     def step_fp32():
         capi.check(lib.tfb_matmul(p(A), p(B), p(C), n, n, n, capi.DTYPE_F32, capi.DTYPE_F32, stream()))
@@ -236,12 +276,7 @@ def ours(args, rank, world, local_rank):
                                        ctypes.c_void_p(C_h.data_ptr()), n, n, n, capi.DTYPE_F32, stream()))
 
     flops = 2.0 * n * n * n
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-
-    # GEMM kernel alone (operands split beforehand): the roofline numerator.
+    # GEMM kernel alone (operands split beforehand): the roofline numerator. The split pass alone too.
     hi_lo = torch.empty((4, n, n), device="cuda", dtype=torch.float32)
     capi.check(lib.tfb_split_tf32(p(A), n, n, n, p(hi_lo[0]), p(hi_lo[1]), n, stream()))
     capi.check(lib.tfb_split_tf32(p(B), n, n, n, p(hi_lo[2]), p(hi_lo[3]), n, stream()))
@@ -250,26 +285,25 @@ def ours(args, rank, world, local_rank):
         capi.check(lib.tfb_gemm_presplit(p(hi_lo[0]), p(hi_lo[1]), p(hi_lo[2]), p(hi_lo[3]), p(C), n, n, n, n, n, n,
                                          0, 0, None, 0, stream()))
 
-    ms32, t0, t1 = timed(step_fp32, args.steps, args.warmup)
-    clocks = sampler.summary(t0, t1) if rank == 0 else None
-    msk, _, _ = timed(step_kernel, args.steps, args.warmup)
-    ms16, t0b, t1b = timed(step_bf16, args.steps, args.warmup)
-    clocks16 = sampler.summary(t0b, t1b) if rank == 0 else None
+    def step_split():
+        capi.check(lib.tfb_split_tf32(p(A), n, n, n, p(hi_lo[0]), p(hi_lo[1]), n, stream()))
+        capi.check(lib.tfb_split_tf32(p(B), n, n, n, p(hi_lo[2]), p(hi_lo[3]), n, stream()))
+
+    # kernel alone -> full step -> kernel alone, all after the same pre-heat, then the sustained loop
+    msk0, ck0 = h.timed(step_kernel, args.steps, args.warmup)
+    ms32, clocks = h.timed(step_fp32, args.steps, args.warmup)
+    msk1, ck1 = h.timed(step_kernel, args.steps, args.warmup, preheat_s=0.2)
+    mss, cks, sus_steps = h.sustained(step_fp32, 2.0, ms32)
+    ms_split, _ = h.timed(step_split, args.steps, args.warmup, preheat_s=0.2)
+    ms16, clocks16 = h.timed(step_bf16, args.steps, args.warmup)
+    ms16s, clocks16s, sus16_steps = h.sustained(step_bf16, 2.0, ms16)
     del hi_lo
-    mse, _, _ = timed(step_e2e, max(2, args.steps // 2), 3)
-    if rank == 0:
-        sampler.stop()
-    status = capi.device_status()
+    mse, clocks_e = h.timed(step_e2e, max(2, args.steps // 2), 3, preheat_s=0.0)
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    # CPU baseline on a bounded sample, and a parity spot check of the rows it produced.
-    cpu = None
     parity = None
-    if world == 1 and not args.no_cpu_baseline:
+    cpu = None
+    if h.rank == 0 and h.world == 1 and not args.no_cpu_baseline:
+        import numpy as np
         from oracle_lib import Oracle, Reference, have_reference
         rows = args.cpu_rows * 4
         a_rows = A_h[:rows].numpy()
@@ -294,45 +328,265 @@ def ours(args, rank, world, local_rank):
         got = C[:rows].cpu().numpy().astype(np.float64)
         parity = float(np.linalg.norm(got - want) / np.linalg.norm(want))
 
-    tf32_peak = peaks["bf16_tflops"] / 6.0
-    value = world * flops / (ms32 * 1e-3) / 1e12
-    line = {
-        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms32, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"square GEMM M=N=K={n} per GPU (FP32 in/out, 3xTF32 on tcgen05), uniform[-1,1) seeded; "
-                               f"N GPUs: M row-panels of {n} rows each, B replicated, no communication",
-                   "n": n, "l2": "operands and output (268 MB each) exceed the 126 MB L2; no flush needed",
-                   "parallelism": f"row-panels x{world}"},
-        "roofline": {"bound": "tensor", "achieved": flops / (msk * 1e-3) / 1e12, "peak": tf32_peak, "unit": "TFLOP/s",
-                     "frac": flops / (msk * 1e-3) / 1e12 / tf32_peak,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch at n = 8192, from the ncu
-                     # capture summarised in profiles/bench_8192_launch_list_and_dram.md (algorithmic: 1.34e9)
+    if h.rank != 0:
+        return None
+    w = h.world
+    msk = min(msk0, msk1)
+    tf32_peak, tf32_peak_sus = peaks["bf16_tflops"] / 6.0, peaks["bf16_tflops_sustained"] / 6.0
+    ach = flops / (msk * 1e-3) / 1e12
+    out = {
+        "value": w * flops / (ms32 * 1e-3) / 1e12, "ms_per_step": ms32, "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch at n = 8192 from a one-pass
+                     # ncu capture of this command (algorithmic bytes: 1.34e9); other sizes: not captured
                      "traffic": (7.36e9 + 0.268e9) if n == 8192 else None,
                      "kernel": "gemm_tcgen05_kernel<TF32x3,BN=256,CTA pair> alone, operands pre-split",
-                     "peak_source": f"{peak_src} bf16_tflops {peaks['bf16_tflops']} / 6 (TF32 issues at half the BF16 "
-                                    f"rate and three products make one FP32 product)",
-                     "kernel_ms": msk},
-        "bf16": {"value": world * flops / (ms16 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms16,
+                     "peak_source": f"{peak_src} bf16_tflops {peaks['bf16_tflops']} (burst) / 6: TF32 issues at half the "
+                                    f"BF16 rate and three products make one FP32 product",
+                     "frac_of_sustained_peak": ach / tf32_peak_sus,
+                     "kernel_ms": msk, "kernel_ms_before_step": msk0, "kernel_ms_after_step": msk1,
+                     "split_ms": ms_split, "clocks_before": ck0, "clocks_after": ck1,
+                     "consistent": bool(ms32 >= msk)},
+        "sustained": {"value": w * flops / (mss * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": mss, "steps": sus_steps,
+                      "seconds": mss * sus_steps / 1e3, "clocks": cks,
+                      "frac_of_sustained_peak": flops / (mss * 1e-3) / 1e12 / tf32_peak_sus},
+        "bf16": {"value": w * flops / (ms16 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms16,
                  "dtype": "bf16 in, f32 accumulate and out",
                  "roofline": {"bound": "tensor", "achieved": flops / (ms16 * 1e-3) / 1e12,
                               "traffic": (1.10e9 + 0.252e9) if n == 8192 else None,
                               "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                               "frac": flops / (ms16 * 1e-3) / 1e12 / peaks["bf16_tflops"],
                               "peak_source": f"{peak_src} bf16_tflops (burst)"},
+                 "sustained": {"value": w * flops / (ms16s * 1e-3) / 1e12, "ms_per_step": ms16s, "steps": sus16_steps,
+                               "frac_of_sustained_peak": flops / (ms16s * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                               "clocks": clocks16s},
                  "clocks": clocks16},
-        "e2e": {"value": world * flops / (mse * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": mse,
-                "h2d_bytes_per_step": 2 * n * n * 4, "d2h_bytes_per_step": n * n * 4},
-        "gpu_launches": 2 * args.steps,
-        "clocks": clocks,
-        "device_status": status,
+        "e2e": {"value": w * flops / (mse * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": mse,
+                "h2d_bytes_per_step": 2 * n * n * 4, "d2h_bytes_per_step": n * n * 4, "clocks": clocks_e},
     }
     if cpu is not None:
-        line["cpu_baseline"] = cpu
-        line["parity_rel_err_vs_cpu_rows"] = parity
-    print(json.dumps(line), flush=True)
+        out["cpu_baseline"] = cpu
+        out["parity_rel_err_vs_cpu_rows"] = parity
+    return out
+
+
+def section_sweep(h, args, capi, lib):
+    """The five square sizes, FP32 (3xTF32) and BF16 inputs, per GPU (every rank runs it; rank 0 reports
+    the maximum time over ranks)."""
+    import refdata
+    torch = h.torch
+    rows = []
+    for n in (1024, 2048, 4096, 8192, 16384):
+        if n == 16384 and args.skip_16384:
+            continue
+        src = torch.from_numpy(refdata.uniform(5, (min(n, 4096), n))).cuda()
+        A = src.repeat((n + src.shape[0] - 1) // src.shape[0], 1)[:n].contiguous()
+        B = A.flip(0).contiguous()
+        C = torch.empty((n, n), device="cuda")
+        st = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: ctypes.c_void_p(t.data_ptr())
+        steps = 20 if n <= 8192 else 5
+        f32 = lambda: capi.check(lib.tfb_matmul(p(A), p(B), p(C), n, n, n, 0, 0, st()))
+        ms, _ = h.timed(f32, steps, 3, preheat_s=0.3)
+        A16, B16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
+        del A, B
+        b16 = lambda: capi.check(lib.tfb_matmul(p(A16), p(B16), p(C), n, n, n, 2, 0, st()))
+        ms16, _ = h.timed(b16, steps, 3, preheat_s=0.3)
+        rows.append({"n": n, "fp32_ms": ms, "fp32_tflops": 2.0 * n ** 3 / ms / 1e9, "bf16_ms": ms16,
+                     "bf16_tflops": 2.0 * n ** 3 / ms16 / 1e9})
+        del A16, B16, C, src
+        torch.cuda.empty_cache()
+    return rows
+
+
+def section_strong(h, args, capi, lib):
+    """One 16384^3 FP32 product split into `world` row panels; B is staged on every GPU before timing."""
+    import refdata
+    torch = h.torch
+    n = 16384
+    from tensors_b200.mlp import shard_rows
+    b, e = shard_rows(n, h.rank, h.world)
+    src = torch.from_numpy(refdata.uniform(6, (2048, n))).cuda()
+    B = src.repeat(n // 2048, 1).contiguous()
+    A = src.flip(1).repeat((e - b + 2047) // 2048, 1)[:e - b].contiguous()
+    C = torch.empty((e - b, n), device="cuda")
+    st = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    fn = lambda: capi.check(lib.tfb_matmul(p(A), p(B), p(C), e - b, n, n, 0, 0, st()))
+    ms, clocks = h.timed(fn, 6, 2, preheat_s=0.5)
+    out = {"ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9, "rows_per_gpu": e - b, "scaling": "strong",
+           "what": "16384^3 FP32 (3xTF32) split into row panels, B resident on every GPU, no communication",
+           "clocks": clocks}
+    del A, B, C, src
+    torch.cuda.empty_cache()
+    return out
+
+
+def section_mlp(h, args, capi, lib):
+    """The data-parallel MLP step (see the module docstring)."""
+    import numpy as np
+    import refdata
+    from tensors_b200.mlp import MLP, shard_rows
+    torch, dist = h.torch, h.dist
+    dims, batch = MLP_DIMS, MLP_BATCH
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    x_all, l_all = refdata.mnist_like(7, (batch, 784)), refdata.labels(8, batch)
+    b, e = shard_rows(batch, h.rank, h.world)
+    X_h = torch.from_numpy(x_all[b:e]).pin_memory()
+    L_h = torch.from_numpy(l_all[b:e]).pin_memory()
+    X, L = X_h.cuda(), L_h.cuda()
+    out = {"config": "MLP 784-1024-1024-10, ReLU, log_softmax + NLL, SGD lr 0.1 momentum 0.9, global batch 8192 "
+                     f"sharded over {h.world} rank(s) ({e - b} rows each)", "flop_per_step": MLP_FLOP}
+
+    def one_step(m, Xs, Ls):
+        m.set_option(MLP.OPT_KEEP_REDUCED, 1)
+        m.train_step(Xs, Ls, lr=0.1, momentum=0.9, global_rows=batch)
+        torch.cuda.synchronize()
+        lo, hi = (0, m.numel) if not m._use_peer() else (4 * ((m.numel // 4) * h.rank // h.world),
+                                                         4 * ((m.numel // 4) * (h.rank + 1) // h.world))
+        g2 = (m.reduced[lo:hi].double() ** 2).sum()
+        if m._use_peer():
+            dist.all_reduce(g2)
+        m.set_option(MLP.OPT_KEEP_REDUCED, 0)
+        return float(m.loss.item()), float(g2.sqrt().item()), float(m.params.double().norm().item())
+
+    # ---- exactly one step from identical parameters: N ranks next to one rank -------------------
+    peer_ok = True
+    m = MLP(dims, ws, max_rows=e - b, exchange="peer")
+    if h.world > 1:
+        try:
+            m.connect()
+        except Exception as ex:   # CUDA IPC unavailable in this container: report it, keep the NCCL path
+            peer_ok = False
+            out["peer_exchange_unavailable"] = str(ex)[:200]
+        flag = torch.tensor([1.0 if peer_ok else 0.0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        peer_ok = bool(flag.item() > 0)
+        if not peer_ok:
+            m.exchange = "nccl"
+    loss, gnorm, pnorm = one_step(m, X, L)
+    out["one_step"] = {"loss": loss, "grad_norm": gnorm, "param_norm_after": pnorm}
+    if h.world > 1 and h.rank == 0:
+        m1 = MLP(dims, ws, max_rows=batch, exchange="local")
+        X1, L1 = torch.from_numpy(x_all).cuda(), torch.from_numpy(l_all).cuda()
+        loss1, gnorm1, pnorm1 = one_step(m1, X1, L1)
+        out["one_step"].update({"loss_1rank": loss1, "grad_norm_1rank": gnorm1, "param_norm_after_1rank": pnorm1,
+                                "loss_rel_diff": abs(loss - loss1) / abs(loss1),
+                                "grad_norm_rel_diff": abs(gnorm - gnorm1) / gnorm1,
+                                "params_rel_diff": float((m.params - m1.params).double().norm().item() / pnorm1)})
+        del m1, X1, L1
+    h.barrier()
+
+    # ---- step time: whole step as one CUDA graph (peer exchange inside) ---------------------------
+    def h2d():
+        X.copy_(X_h, non_blocking=True)
+        L.copy_(L_h, non_blocking=True)
+
+    replay = m.capture_train_step(X, L, lr=0.1, momentum=0.9, global_rows=batch, warmup=2)
+    us, clocks = h.timed(replay, 50, 5, preheat_s=0.5)
+    out.update({"step_us": us * 1e3, "tflops": MLP_FLOP / (us * 1e-3) / 1e12, "exchange": m.exchange if h.world > 1 else "none",
+                "clocks": clocks})
+
+    def e2e_step():
+        h2d()
+        replay()
+        return m.loss.item()   # the device -> host read of the step's result
+
+    us_e, _ = h.timed(e2e_step, 30, 3, preheat_s=0.2)
+    out["e2e_step_us"] = us_e * 1e3
+    out["e2e_h2d_bytes_per_step"] = int(X_h.numel() * 4 + L_h.numel() * 8)
+
+    # ---- forward + backward alone, and the exchange alone ---------------------------------------
+    fb = lambda: m.forward_backward(X, L, batch)
+    us_fb, _ = h.timed(fb, 30, 3, preheat_s=0.2)
+    out["forward_backward_us_eager"] = us_fb * 1e3
+    if h.world > 1:
+        if peer_ok:
+            ex = lambda: m.exchange_update(0.0, 0.9)   # lr 0: parameters stay put while the traffic is the real one
+            us_x, _ = h.timed(ex, 50, 5, preheat_s=0.2)
+            out["peer_exchange_us"] = us_x * 1e3
+        scratch = torch.zeros(m.numel + 4, device="cuda")
+        ar = lambda: dist.all_reduce(scratch)
+        us_ar, _ = h.timed(ar, 50, 5, preheat_s=0.2)
+        out["nccl_allreduce_us"] = us_ar * 1e3
+        # the same step with ONE NCCL all-reduce per step (loss in the last slot) and the update kernel
+        m.disconnect()
+        del m
+        m2 = MLP(dims, ws, max_rows=e - b, exchange="nccl")
+        replay2 = m2.capture_train_step(X, L, lr=0.1, momentum=0.9, global_rows=batch, warmup=2)
+        us2, _ = h.timed(replay2, 50, 5, preheat_s=0.3)
+        out["step_us_nccl"] = us2 * 1e3
+        out["exchange_share_of_step"] = (out.get("peer_exchange_us") or out["nccl_allreduce_us"]) / out["step_us"]
+        del m2
+    return out
+
+
+def ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import tensors_b200.capi as capi
+
+    lib = capi.lib
+    torch.cuda.set_device(local_rank)
     if world > 1:
+        # NCCL announces its version on stdout at this level; stdout carries the one JSON line only.
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    capi.check(lib.tfb_init())
+    peaks, peak_src = load_peaks()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    h = Harness(rank, world, local_rank, sampler)
+
+    gemm = section_gemm(h, args, capi, lib, peaks, peak_src)
+    torch.cuda.empty_cache()
+    sections, errors = {}, {}
+    for name, fn in (("sweep", section_sweep), ("strong_16384", section_strong), ("mlp_dp", section_mlp)):
+        if name in args.skip.split(","):
+            continue
+        try:
+            sections[name] = fn(h, args, capi, lib)
+        except Exception as ex:   # a failing side section must not lose the headline; it is reported in the line
+            errors[name] = f"{type(ex).__name__}: {ex}"[:300]
+            if world > 1:
+                raise
+        torch.cuda.empty_cache()
+    if rank == 0:
+        sampler.stop()
+    status = capi.device_status()
+
+    if rank == 0:
+        n = args.n
+        line = {
+            "metric": METRIC, "value": gemm["value"], "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": gemm["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"square GEMM M=N=K={n} per GPU (FP32 in/out, 3xTF32 on tcgen05), uniform[-1,1) seeded; "
+                                   f"N GPUs: M row-panels of {n} rows each, B replicated, no communication",
+                       "n": n, "l2": "operands and output (268 MB each) exceed the 126 MB L2; no flush needed",
+                       "preheat": "every timed loop follows >= 1 s of the same work (>= the warm-up steps)",
+                       "parallelism": f"row-panels x{world}"},
+            "roofline": gemm["roofline"], "sustained": gemm["sustained"], "bf16": gemm["bf16"], "e2e": gemm["e2e"],
+            # per step: split_tf32_pair_kernel + gemm_tcgen05_kernel (the launch list under profiles/)
+            "gpu_launches": 2 * args.steps,
+            "clocks": gemm["clocks"], "device_status": status,
+        }
+        for k in ("cpu_baseline", "parity_rel_err_vs_cpu_rows"):
+            if k in gemm:
+                line[k] = gemm[k]
+        line.update(sections)
+        if errors:
+            line["section_errors"] = errors
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if status != 0:
+        sys.exit(f"a kernel recorded device error {status}")
 
 
 def main():
@@ -345,6 +599,8 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=8, help="rows of A per CPU-baseline panel")
     ap.add_argument("--cpu-threads", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip", default="", help="comma-separated sections to leave out: sweep,strong_16384,mlp_dp")
+    ap.add_argument("--skip-16384", action="store_true", help="leave the largest size out of the sweep")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

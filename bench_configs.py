@@ -6,8 +6,8 @@
   config 4  square sweep 1024..16384, FP32 (3xTF32) and BF16
   config 5  MLP 784-1024-1024-10 training step, batch 8192 / world size (NCCL all-reduce when > 1 rank)
 
-Run:  python -m tensors_b200.bench_configs [--configs 1,2,3,4,5] [--iters 20]
-      torchrun --nproc-per-node N -m tensors_b200.bench_configs --configs 5
+Run:  python bench_configs.py [--configs 1,2,3,4,5] [--iters 20]
+      torchrun --nproc-per-node N bench_configs.py --configs 5 [--exchange peer|nccl]
 Prints one JSON line per measurement (CUDA events on the launching stream, median of `iters` after 3
 warm-up runs, as the reference's benches do: benchmarks/gemm_bench.cpp:99-124).
 """
@@ -20,7 +20,7 @@ import sys
 
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 for _p in (ROOT, os.path.join(ROOT, "tests")):
     if _p not in sys.path:
         sys.path.insert(0, _p)
@@ -101,6 +101,7 @@ def config2(iters):
          hbm_frac=bwd_bytes / gb / 1e3 / HBM_GBS, mflop=51.38)
 
 
+EXCHANGE = "peer"
 CONV_N, CONV_LAYERS, CONV_PASSES = 128, ("1", "2"), ("forward", "dgrad", "wgrad+dbias")
 
 
@@ -157,7 +158,7 @@ def config5(iters):
     b, e = shard_rows(batch, rank, world)
     X = dev(refdata.mnist_like(7, (batch, 784))[b:e])
     labels = torch.from_numpy(refdata.labels(8, batch)[b:e]).cuda()
-    m = MLP(dims, ws)
+    m = MLP(dims, ws, max_rows=e - b, exchange=EXCHANGE)
     step = lambda: m.train_step(X, labels, lr=0.1, momentum=0.9, global_rows=batch)
     us_eager = time_us(step, iters)
     fb = time_us(lambda: m.forward_backward(X, labels, batch), iters)
@@ -171,7 +172,10 @@ def config5(iters):
         us, fb, ar, us_eager = [float(v) for v in t.tolist()]
     if rank == 0:
         emit(config=5, what=f"MLP 784-1024-1024-10 step (CUDA graph replay), global batch 8192 on {world} GPU(s)", us=us,
-             eager_us=us_eager, forward_backward_us=fb, allreduce_us=ar, tflops=78.35e9 / us / 1e6, loss=float(m.loss.item()))
+             exchange=EXCHANGE if world > 1 else "none", eager_us=us_eager, forward_backward_us=fb, allreduce_us=ar,
+             tflops=78.35e9 / us / 1e6, loss=float(m.loss.item()))
+    m.disconnect()
+    del m
     if world > 1:
         dist.destroy_process_group()
 
@@ -183,8 +187,10 @@ def main():
     ap.add_argument("--conv-n", type=int, default=128, help="config 3: batch size")
     ap.add_argument("--conv-layers", default="1,2", help="config 3: which layers")
     ap.add_argument("--conv-passes", default="forward,dgrad,wgrad+dbias", help="config 3: which passes")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="config 5 with more than one rank")
     a = ap.parse_args()
-    global CONV_N, CONV_LAYERS, CONV_PASSES
+    global CONV_N, CONV_LAYERS, CONV_PASSES, EXCHANGE
+    EXCHANGE = a.exchange
     CONV_N, CONV_LAYERS, CONV_PASSES = a.conv_n, tuple(a.conv_layers.split(",")), tuple(a.conv_passes.split(","))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     capi.check(lib.tfb_init())

@@ -54,11 +54,41 @@ int tfb_init(void);
 /* Message of the last failure on the calling thread ("" if none). */
 const char* tfb_last_error_string(void);
 
+/* Tuning knobs. Each starts at its default, or at the value of the environment variable of the same
+ * purpose (TFB_GEMM_BN, TFB_GEMM_PAIR, TFB_GEMM_SPLITK, TFB_GEMM_CHUNK_KB, TFB_CONV_TMA,
+ * TFB_CONV_DIRECT, TFB_CONV_PAIR, TFB_HOST_PANEL) read ONCE when the first knob is consulted; no call
+ * path reads the environment. They exist for tests (every kernel must see every shape) and for
+ * measurements; results do not depend on them beyond FP32 summation order.
+ *   GEMM_TILE_N     0 = choose, else 64 / 128 / 256 columns per single-CTA tile
+ *   GEMM_PAIR       -1 = choose, 0 = never pair CTAs, 1 = always
+ *   GEMM_SPLIT_K    0 = choose, else the number of K splits
+ *   GEMM_CHUNK_KB   0 = default (8), else K blocks per TMEM accumulation chunk of the FP32 path
+ *   CONV_TMA        0 = never use the TMA-fed convolution path, 1 = choose, 2 = wherever possible
+ *   CONV_DIRECT     0 = never use the CUDA-core kernels for short contractions, 1 = choose
+ *   CONV_PAIR       -1 = choose, 0 / 1 = CTA pairs off / on in the TMA-fed convolution path
+ *   HOST_PANEL_ROWS rows of A per panel in tfb_matmul_host (default 512)
+ * ref: no counterpart (the reference has one kernel per operation). */
+#define TFB_TUNE_GEMM_TILE_N 0
+#define TFB_TUNE_GEMM_PAIR 1
+#define TFB_TUNE_GEMM_SPLIT_K 2
+#define TFB_TUNE_GEMM_CHUNK_KB 3
+#define TFB_TUNE_CONV_TMA 4
+#define TFB_TUNE_CONV_DIRECT 5
+#define TFB_TUNE_CONV_PAIR 6
+#define TFB_TUNE_HOST_PANEL_ROWS 7
+#define TFB_TUNE_COUNT 8
+int tfb_set_tuning(int knob, int value);
+int tfb_get_tuning(int knob, int* value_out);
+
 /* Synchronises the current device and reports the first error code a kernel recorded
- * (0 = none; 101..106 = a bounded wait inside a kernel ran out), then clears it. The
+ * (0 = none; 101..107 = a bounded wait inside a kernel ran out), then clears it. The
  * reference never checks launches (ref: cuda/kernels/gemm.cu:82-87 has no
  * cudaGetLastError); this is the replacement's fail-soft channel. */
 int tfb_device_status(int* code_out);
+/* Host-side fault injection for tests of a host's error handling: writes `code` into a status word as
+ * a kernel that gave up would have (word 0: the regular one; word 1: the one of tfb_matmul_f32_static,
+ * which must have run on this device before). No kernel is made to fail. ref: no counterpart. */
+int tfb_inject_device_status(int word, int code);
 
 /* ---- GEMM ------------------------------------------------------------------------ */
 
@@ -95,7 +125,9 @@ int tfb_gemm_ex(const void* A, const void* B, void* C, int64_t M, int64_t N, int
  * dimension ld_out (a multiple of 4, >= cols; padding columns are zero-filled). `src` is
  * rows x cols with leading dimension ld.
  * tfb_gemm_presplit: tfb_gemm_ex for FP32 operands given as such hi / lo planes (leading
- * dimensions multiples of 4, 16-byte aligned bases); C is FP32. No scratch memory is used.
+ * dimensions multiples of 4, 16-byte aligned bases); C is FP32. Products with few output tiles and a long
+ * contraction run split along K and then take library-owned scratch for the partial sums; inside a stream
+ * capture that scratch must already exist (run the same call once outside the capture first).
  * ref: no counterpart; the reference has no tensor-core path (cuda/kernels/gemm.cu:60-254). */
 int tfb_split_tf32(const float* src, int64_t rows, int64_t cols, int64_t ld, float* hi, float* lo,
                    int64_t ld_out, void* stream);
@@ -234,6 +266,96 @@ int tfb_log_softmax_nll(const float* logits, const int64_t* labels, float* dlogi
 int tfb_sgd_momentum(float* params, float* velocity, const float* grads, int64_t n, float lr,
                      float momentum, float grad_scale, void* stream);
 
+/* ---- the data-parallel MLP training step as one object ---------------------------------- */
+
+/* Linear -> ReLU -> ... -> Linear -> log_softmax + mean NLL -> backward -> gradient exchange -> SGD with
+ * momentum, with every buffer (flat parameters / gradients / velocity, activations, TF32 planes) owned
+ * by the handle and nothing allocated or read back by a step. dims[0..n_layers] are the layer widths
+ * (ReLU after every layer but the last); a step takes at most max_rows rows. The handle belongs to the
+ * device that is current at creation; that device must be current for every call on it. Weights are
+ * [out,in] row-major as the reference stores them and start at zero: fill them through
+ * tfb_mlp_buffer(TFB_MLP_PARAMS) + tfb_mlp_segment + tfb_memcpy.
+ * ref: the training loop of examples/train_mlp.cpp:161-183 (model :33-52, loss graph :54-76, manual
+ * update :140-159) with the momentum update documented in nn/optim/SGD.hpp:3-6. */
+typedef struct tfb_mlp tfb_mlp;
+int tfb_mlp_create(int n_layers, const int64_t* dims, int64_t max_rows, tfb_mlp** out);
+int tfb_mlp_destroy(tfb_mlp* m);
+/* Floats in the flat parameter / gradient / velocity buffers (each weight and bias padded to a multiple
+ * of 4 floats so that it starts on a 16-byte boundary), and where layer `layer` sits in them. */
+int64_t tfb_mlp_numel(const tfb_mlp* m);
+int tfb_mlp_segment(const tfb_mlp* m, int layer, int64_t* weight_offset, int64_t* bias_offset);
+/* Device pointers of the handle's buffers. PARAMS, VELOCITY, REDUCED_GRADS: numel floats. GRADS:
+ * numel floats followed by this rank's loss contribution (so one collective over numel + 4 floats sums
+ * both). LOSS: one float, the loss of the last step summed over all ranks. ACTIVATION: the output of
+ * layer `layer` of the last forward pass, [rows, dims[layer + 1]]. REGION: the exchange region (what
+ * other ranks map). `layer` is ignored for the others. */
+#define TFB_MLP_PARAMS 0
+#define TFB_MLP_GRADS 1
+#define TFB_MLP_VELOCITY 2
+#define TFB_MLP_LOSS 3
+#define TFB_MLP_REDUCED_GRADS 4
+#define TFB_MLP_ACTIVATION 5
+#define TFB_MLP_REGION 6
+int tfb_mlp_buffer(tfb_mlp* m, int which, int layer, void** ptr_out);
+
+/* This rank's share of the full-batch gradient for its `rows` rows of a global batch of global_rows
+ * rows (<= 0: rows), into GRADS, and its loss contribution. ref: forward + Tensor::backward of
+ * examples/train_mlp.cpp:167-175. */
+int tfb_mlp_forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,
+                             void* stream);
+/* v <- momentum*v + g ; p <- p - lr*v over the whole flat buffers from this rank's own GRADS, and LOSS <-
+ * the loss slot: the update of a single rank, or of every rank after an all-reduce the caller ran over
+ * GRADS (numel + 4 floats, e.g. one ncclAllReduce). ref: nn/optim/SGD.hpp:3-6. */
+int tfb_mlp_update(tfb_mlp* m, float lr, float momentum, void* stream);
+/* The same update fused with the gradient exchange, one kernel over NVLink peer memory: each rank adds
+ * its slice of all ranks' GRADS in rank order, updates that slice of the velocity and the parameters and
+ * stores the new parameters into every rank's PARAMS; LOSS <- the sum of the ranks' loss slots. Every
+ * rank of the group must call it once per step, on a stream that follows its forward_backward; the
+ * kernel waits (bounded, TFB_MLP_OPT_WAIT_LIMIT_NS) for the peers and records device error 107 if one
+ * does not arrive. VELOCITY is then only maintained for this rank's slice, so do not alternate between
+ * this call and tfb_mlp_update on one handle. With a group of one it is tfb_mlp_update.
+ * ref: no counterpart (the reference is single-device, cuda/CudaContext.cpp:57-60). */
+int tfb_mlp_exchange_update(tfb_mlp* m, float lr, float momentum, void* stream);
+/* tfb_mlp_forward_backward followed by tfb_mlp_exchange_update. */
+int tfb_mlp_step(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows, float lr,
+                 float momentum, void* stream);
+/* Records a step into a CUDA graph held by the handle (replacing an earlier one) and replays it:
+ * what = STEP (forward_backward + exchange_update), FORWARD_BACKWARD, or UPDATE (tfb_mlp_update, for
+ * callers that run their own all-reduce between two graphs). X and labels are captured by address:
+ * refill them in place. Run the same call eagerly once before capturing (the library's scratch buffer
+ * must exist), and capture on a stream other than the legacy default stream. */
+#define TFB_MLP_CAPTURE_STEP 0
+#define TFB_MLP_CAPTURE_FORWARD_BACKWARD 1
+#define TFB_MLP_CAPTURE_UPDATE 2
+int tfb_mlp_capture_step(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,
+                         float lr, float momentum, int what, void* stream);
+int tfb_mlp_replay(tfb_mlp* m, void* stream);
+/* WAIT_LIMIT_NS: how long the exchange kernel waits for a peer (default 2 s). EXCHANGE_CTAS: its grid
+ * (0 = choose; every rank of a group must use the same value). KEEP_REDUCED_GRADS: non-zero makes the
+ * exchange also store the summed gradient of this rank's slice into REDUCED_GRADS. */
+#define TFB_MLP_OPT_WAIT_LIMIT_NS 0
+#define TFB_MLP_OPT_EXCHANGE_CTAS 1
+#define TFB_MLP_OPT_KEEP_REDUCED_GRADS 2
+int tfb_mlp_set_option(tfb_mlp* m, int option, int64_t value);
+
+/* Forming a group of `world` <= 8 ranks (one handle per rank, same dims). The library does not own a
+ * rendezvous: the host moves the handles or pointers between ranks by whatever means it has.
+ * One process per GPU: every rank writes tfb_mlp_ipc_handle_bytes() bytes with tfb_mlp_ipc_handle,
+ * the host gathers them in rank order, and every rank calls tfb_mlp_connect_ipc with the gathered array.
+ * Peer regions mapped some other way (a symmetric-memory allocator, a driver-level mapping):
+ * tfb_mlp_connect_ptrs with the regions as this rank addresses them (entry `rank` is ignored).
+ * One process, several devices: tfb_mlp_connect_local over all handles (enables peer access).
+ * ref: no counterpart; the reference has no multi-device support (cuda/CudaContext.cpp:57-60). */
+size_t tfb_mlp_ipc_handle_bytes(void);
+int tfb_mlp_ipc_handle(tfb_mlp* m, void* handle_out);
+int tfb_mlp_connect_ipc(tfb_mlp* m, int rank, int world, const void* handles);
+int tfb_mlp_connect_ptrs(tfb_mlp* m, int rank, int world, void* const* regions);
+int tfb_mlp_connect_local(tfb_mlp* const* ms, int world);
+/* The exchange of a whole group whose handles all live on the current device (ranks emulated on one
+ * GPU), as ONE cooperative launch in which every rank's CTAs are resident together — separate launches
+ * that wait for each other on one GPU have no such guarantee. Handle r must be rank r of `world`. */
+int tfb_mlp_exchange_update_one_device(tfb_mlp* const* ms, int world, float lr, float momentum, void* stream);
+
 /* ---- device-side pieces of the autograd walk (FP32, n elements, any alignment) ---------- */
 
 /* dst[i] = value. The ones-fill of the root gradient that Tensor::backward does in a host loop.
@@ -269,6 +391,10 @@ int tfb_pool_stats(int device, uint64_t* reserved, uint64_t* used, uint64_t* res
                    uint64_t* used_high);
 /* Lets `peer` read and write memory allocated from `device`'s pool (plain peer loads / copies). */
 int tfb_pool_enable_peer(int device, int peer);
+/* The scratch the library itself holds on `device` (TF32 planes, split-K partials; one grow-only
+ * stream-ordered buffer per stream that has needed one): how many buffers and their total size.
+ * ref: no counterpart. */
+int tfb_scratch_stats(int device, uint64_t* buffers_out, uint64_t* bytes_out);
 /* Device and stream plumbing for hosts compiled without CUDA headers: a non-blocking stream per
  * (thread, device) replaces the reference's single stream of device 0.
  * ref: DeviceContext / CudaStream, cuda/CudaContext.cpp:18-60, cuda/CudaContext.hpp:134-140. */

@@ -7,6 +7,8 @@ LIB_PATH = os.path.join(_HERE, "libtfb.so")
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 EPI_NONE, EPI_BIAS_COL, EPI_BIAS_ROW, EPI_RELU = 0, 1, 2, 4
+(TUNE_GEMM_TILE_N, TUNE_GEMM_PAIR, TUNE_GEMM_SPLIT_K, TUNE_GEMM_CHUNK_KB, TUNE_CONV_TMA, TUNE_CONV_DIRECT,
+ TUNE_CONV_PAIR, TUNE_HOST_PANEL_ROWS) = range(8)
 
 
 class TfbError(RuntimeError):
@@ -30,7 +32,10 @@ _ip = ctypes.POINTER(ctypes.c_int)
 PROTOTYPES = {
     "tfb_init": (_i32, []),
     "tfb_last_error_string": (ctypes.c_char_p, []),
+    "tfb_set_tuning": (_i32, [_i32, _i32]),
+    "tfb_get_tuning": (_i32, [_i32, _ip]),
     "tfb_device_status": (_i32, [_ip]),
+    "tfb_inject_device_status": (_i32, [_i32, _i32]),
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tfb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_gemm_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
@@ -54,6 +59,25 @@ PROTOTYPES = {
     "tfb_im2col_index_map": (_i32, [_vp] + [_i64] * 13 + [_vp]),
     "tfb_log_softmax_nll": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "tfb_sgd_momentum": (_i32, [_vp, _vp, _vp, _i64, ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
+    "tfb_mlp_create": (_i32, [_i32, ctypes.POINTER(_i64), _i64, ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_mlp_destroy": (_i32, [_vp]),
+    "tfb_mlp_numel": (_i64, [_vp]),
+    "tfb_mlp_segment": (_i32, [_vp, _i32, ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
+    "tfb_mlp_buffer": (_i32, [_vp, _i32, _i32, ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_mlp_forward_backward": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
+    "tfb_mlp_update": (_i32, [_vp, ctypes.c_float, ctypes.c_float, _vp]),
+    "tfb_mlp_exchange_update": (_i32, [_vp, ctypes.c_float, ctypes.c_float, _vp]),
+    "tfb_mlp_step": (_i32, [_vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _vp]),
+    "tfb_mlp_capture_step": (_i32, [_vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _i32, _vp]),
+    "tfb_mlp_replay": (_i32, [_vp, _vp]),
+    "tfb_mlp_set_option": (_i32, [_vp, _i32, _i64]),
+    "tfb_mlp_ipc_handle_bytes": (_sz, []),
+    "tfb_mlp_ipc_handle": (_i32, [_vp, _vp]),
+    "tfb_mlp_connect_ipc": (_i32, [_vp, _i32, _i32, _vp]),
+    "tfb_mlp_connect_ptrs": (_i32, [_vp, _i32, _i32, ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_mlp_connect_local": (_i32, [ctypes.POINTER(ctypes.c_void_p), _i32]),
+    "tfb_mlp_exchange_update_one_device": (_i32, [ctypes.POINTER(ctypes.c_void_p), _i32, ctypes.c_float,
+                                                   ctypes.c_float, _vp]),
     "tfb_fill": (_i32, [_vp, _i64, ctypes.c_float, _vp]),
     "tfb_relu_forward": (_i32, [_vp, _vp, _i64, _vp]),
     "tfb_relu_backward": (_i32, [_vp, _vp, _vp, _i64, _vp]),
@@ -66,6 +90,7 @@ PROTOTYPES = {
     "tfb_pool_trim": (_i32, [_i32, _sz]),
     "tfb_pool_stats": (_i32, [_i32] + [ctypes.POINTER(ctypes.c_uint64)] * 4),
     "tfb_pool_enable_peer": (_i32, [_i32, _i32]),
+    "tfb_scratch_stats": (_i32, [_i32] + [ctypes.POINTER(ctypes.c_uint64)] * 2),
     "tfb_set_device": (_i32, [_i32]),
     "tfb_get_device": (_i32, [_ip]),
     "tfb_stream_create": (_i32, [_i32, ctypes.POINTER(ctypes.c_void_p)]),

@@ -170,6 +170,9 @@ int tfb_stream_create(int device, void** stream_out) {
 
 int tfb_stream_destroy(void* stream) {
     if (stream == nullptr) return TFB_OK;
+    // The library's scratch buffer of this stream goes with it (a later stream may get the same handle
+    // value and must not inherit a stale entry). The stream belongs to the device that is current.
+    workspace_release(static_cast<cudaStream_t>(stream));
     TFB_CUDA_OK(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
     return TFB_OK;
 }

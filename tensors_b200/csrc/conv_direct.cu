@@ -216,8 +216,7 @@ DirectArgs direct_args(const ConvShape& s) {
 }
 
 bool direct_enabled() {
-    if (const char* e = getenv("TFB_CONV_DIRECT")) return atoi(e) != 0;   // debugging override
-    return true;
+    return tuning(TFB_TUNE_CONV_DIRECT) != 0;
 }
 
 constexpr size_t kDgradSmemLimit = 200 * 1024;

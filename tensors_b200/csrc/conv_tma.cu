@@ -213,8 +213,7 @@ struct SpatialCall {
 int run_spatial(const SpatialCall& c, const ConvShape& s, const DeviceState* st, cudaStream_t stream) {
     const int64_t khw = s.kH * s.kW;
     const int cblks = (int)((c.src_c + 31) / 32);
-    int env_pair = -1;
-    if (const char* e = getenv("TFB_CONV_PAIR")) env_pair = atoi(e);   // debugging override
+    const int env_pair = tuning(TFB_TUNE_CONV_PAIR);
     const int tw_log2 = pow2_ceil_log2(c.out_W < 128 ? c.out_W : 128);
     const int tw = 1 << tw_log2, th = 128 / tw;
     const int64_t tiles_x = (c.out_W + tw - 1) / tw;
@@ -291,13 +290,11 @@ int column_sums(const float* partial, int64_t rows, int64_t cols, int64_t ld, fl
 }
 
 bool conv_tma_forced() {
-    const char* e = getenv("TFB_CONV_TMA");
-    return e != nullptr && atoi(e) == 2;
+    return tuning(TFB_TUNE_CONV_TMA) == 2;
 }
 
 bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels) {
-    int mode = 1;
-    if (const char* e = getenv("TFB_CONV_TMA")) mode = atoi(e);   // debugging override: 0 never, 2 whenever possible
+    const int mode = tuning(TFB_TUNE_CONV_TMA);   // 0 never, 1 by the rules below, 2 whenever possible
     if (mode == 0) return false;
     // A K block holds 32 channels of one tap: with few channels most of it is zero fill and the
     // gather kernel, which packs taps densely, is faster.

@@ -1,5 +1,6 @@
 // Host side of the tcgen05 GEMM: tensor-map construction, operand preparation
 // (TF32 hi/lo split, re-packing of unaligned 16-bit operands), tile-shape choice, launch.
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -240,12 +241,14 @@ int launch_variant(const CUtensorMap maps[5], const GemmArgs& args, int workers,
     using S = GemmSmem<KIND, BN, STAGES, PAIR>;
     static_assert(S::TOTAL <= 232448, "stage ring + staging exceed the 227 KB shared-memory limit");
     auto kern = gemm_tcgen05_kernel<KIND, BN, STAGES, A_MN, B_MN, PAIR>;
-    static bool attr_set[64] = {false};
+    // Once per (kernel variant, device); several host threads may get here at the same time.
+    static std::atomic<bool> attr_set[64];
     int dev = 0;
     TFB_CUDA_OK(cudaGetDevice(&dev));
-    if (!attr_set[dev]) {
+    if (dev < 0 || dev >= 64) return fail(TFB_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
         TFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(PAIR ? 2 * workers : workers));
@@ -329,11 +332,9 @@ struct GemmPlan {
 
 GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
     GemmPlan p;
-    // TFB_GEMM_BN / TFB_GEMM_PAIR / TFB_GEMM_SPLITK: debugging overrides, read on every call.
-    int env_bn = 0, env_pair = -1, env_split = 0;
-    if (const char* e = getenv("TFB_GEMM_BN")) env_bn = atoi(e);
-    if (const char* e = getenv("TFB_GEMM_PAIR")) env_pair = atoi(e);
-    if (const char* e = getenv("TFB_GEMM_SPLITK")) env_split = atoi(e);
+    // Tuning overrides (tfb_set_tuning): 0 / -1 / 0 leave the choice to the rules below.
+    const int env_bn = tuning(TFB_TUNE_GEMM_TILE_N), env_pair = tuning(TFB_TUNE_GEMM_PAIR),
+              env_split = tuning(TFB_TUNE_GEMM_SPLIT_K);
     const int es = c.in_dtype == TFB_DTYPE_F32 ? 4 : 2;
     p.k_blocks = (int)((c.K + 128 / es - 1) / (128 / es));
     // CTA pairs pay off once there are enough 256 x 256 tiles to occupy about half of the SM pairs
@@ -500,8 +501,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     }
 
     // ---- tile shape and tensor maps ---------------------------------------------
-    int env_chunk = 0;
-    if (const char* e = getenv("TFB_GEMM_CHUNK_KB")) env_chunk = atoi(e);   // debugging override
+    const int env_chunk = tuning(TFB_TUNE_GEMM_CHUNK_KB);
     const GemmPlan plan = gemm_plan(c, st->sm_count);
     const bool use_pair = plan.pair;
     const int bn = plan.bn;

@@ -34,6 +34,32 @@ int copy_streams(CopyStreams** out) {
     return TFB_OK;
 }
 
+// Stream-ordered device buffers of one call: whatever was allocated is released on `stream` when the
+// call returns, on the error paths too.
+struct BufferBag {
+    cudaStream_t stream;
+    std::vector<void*> ptrs;
+    explicit BufferBag(cudaStream_t s) : stream(s) {}
+    int make(void** out, size_t bytes) {
+        TFB_CUDA_OK(cudaMallocAsync(out, bytes, stream));
+        ptrs.push_back(*out);
+        return TFB_OK;
+    }
+    // Streams other than `stream` that may still touch the buffers (the copy streams): the frees are
+    // ordered after everything enqueued on them so far.
+    std::vector<cudaStream_t> users;
+    ~BufferBag() {
+        for (cudaStream_t u : users) {
+            cudaEvent_t e = nullptr;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) continue;
+            if (cudaEventRecord(e, u) == cudaSuccess) (void)cudaStreamWaitEvent(stream, e, 0);
+            (void)cudaEventDestroy(e);
+        }
+        for (void* p : ptrs) (void)cudaFreeAsync(p, stream);
+        (void)cudaGetLastError();
+    }
+};
+
 struct EventBag {
     std::vector<cudaEvent_t> events;
     int make(cudaEvent_t* e) {
@@ -74,8 +100,7 @@ extern "C" int tfb_matmul_host(const void* A_host, const void* B_host, void* C_h
     // Panel height: two rows of 256-row tiles (64 pair tiles at N = 8192: most of the SM pairs), small
     // enough that the copy engines interleave finely and the last panel's product and download are a short
     // tail (measured at 8192^3: 13.3 ms per call with 512 rows, 15.7 ms with 1024, 21.1 ms with 2048).
-    int64_t panel = 512;
-    if (const char* e = getenv("TFB_HOST_PANEL")) panel = atoll(e) > 0 ? atoll(e) : panel;   // debugging override
+    int64_t panel = tuning(TFB_TUNE_HOST_PANEL_ROWS) > 0 ? tuning(TFB_TUNE_HOST_PANEL_ROWS) : 512;
     if (panel > M) panel = M;
     const int64_t panels = (M + panel - 1) / panel;
     const int64_t ldb4 = (N + 3) / 4 * 4;
@@ -85,11 +110,15 @@ extern "C" int tfb_matmul_host(const void* A_host, const void* B_host, void* C_h
     float* dBs = nullptr;   // FP32: hi / lo planes of B
     uint8_t* dA[2] = {nullptr, nullptr};
     float* dC[2] = {nullptr, nullptr};
-    TFB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&dB), (size_t)(K * N) * es, stream));
-    if (f32) TFB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&dBs), (size_t)(2 * K * ldb4) * 4, stream));
+    // Declared before the events: the buffers are released (stream-ordered, after the waits below
+    // have been enqueued) when the call returns, whichever way it returns.
+    BufferBag buffers(stream);
+    buffers.users = {cs->h2d, cs->d2h};
+    if ((rc = buffers.make(reinterpret_cast<void**>(&dB), (size_t)(K * N) * es)) != TFB_OK) return rc;
+    if (f32 && (rc = buffers.make(reinterpret_cast<void**>(&dBs), (size_t)(2 * K * ldb4) * 4)) != TFB_OK) return rc;
     for (int i = 0; i < 2; ++i) {
-        TFB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&dA[i]), (size_t)(panel * K) * es, stream));
-        TFB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&dC[i]), (size_t)(panel * N) * 4, stream));
+        if ((rc = buffers.make(reinterpret_cast<void**>(&dA[i]), (size_t)(panel * K) * es)) != TFB_OK) return rc;
+        if ((rc = buffers.make(reinterpret_cast<void**>(&dC[i]), (size_t)(panel * N) * 4)) != TFB_OK) return rc;
     }
     EventBag bag;
     cudaEvent_t ready, b_loaded;
@@ -145,11 +174,5 @@ extern "C" int tfb_matmul_host(const void* A_host, const void* B_host, void* C_h
     // The caller's stream completes when the last panels have reached the host.
     TFB_CUDA_OK(cudaStreamWaitEvent(stream, drained[(size_t)(panels - 1)], 0));
     if (panels >= 2) TFB_CUDA_OK(cudaStreamWaitEvent(stream, drained[(size_t)(panels - 2)], 0));
-    TFB_CUDA_OK(cudaFreeAsync(dB, stream));
-    if (dBs != nullptr) TFB_CUDA_OK(cudaFreeAsync(dBs, stream));
-    for (int i = 0; i < 2; ++i) {
-        TFB_CUDA_OK(cudaFreeAsync(dA[i], stream));
-        TFB_CUDA_OK(cudaFreeAsync(dC[i], stream));
-    }
-    return TFB_OK;
+    return TFB_OK;   // `buffers` frees after the waits just enqueued on `stream`
 }

@@ -30,9 +30,20 @@ struct DeviceState {
     int* status = nullptr;   // device word: first error code a kernel recorded, 0 = none
 };
 int device_state(DeviceState** out);   // for the current device
+// noalloc.cu keeps a second status word (a __device__ variable, so that its entry point never
+// allocates); tfb_device_status consults both.
+int static_status_take(int* code);
+// Writes that word (host-side injection for tests of the reporting channel); fails if the
+// allocation-free entry point has not been used on the current device yet.
+int static_status_put(int code);
+
+// Current value of a TFB_TUNE_* knob.
+int tuning(int knob);
 
 // Stream-ordered scratch owned by the library, one grow-only buffer per (device, stream).
 int workspace_get(cudaStream_t stream, size_t bytes, void** out);
+// Drops the buffer of (current device, stream), stream-ordered; called before the stream is destroyed.
+void workspace_release(cudaStream_t stream);
 
 // Element size of a TFB_DTYPE_* code, 0 if unknown.
 size_t dtype_size(int dtype);
@@ -97,6 +108,17 @@ int linear_forward(const void* X, const void* W, const float* bias, void* Y, int
 int linear_backward(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
                     float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
                     cudaStream_t stream);
+// Planes of an FP32 operand that the caller split beforehand (null hi = not supplied).
+struct SavedPlanes {
+    const float* hi = nullptr;
+    const float* lo = nullptr;
+    int64_t ld = 0;
+};
+// linear_backward with X and / or W optionally given as saved hi / lo planes (FP32 only; X and W are
+// ignored for the operands whose planes are supplied).
+int linear_backward_impl(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+                         float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
+                         cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved);
 
 // ---------------------------------------------------------------------------
 // nn::Conv2d (conv.cu: gather kernel, entry points; conv_tma.cu: stride-1 path on the GEMM kernel)

@@ -134,14 +134,7 @@ int linear_forward(const void* X, const void* W, const float* bias, void* Y, int
     return gemm_run(c, stream);
 }
 
-// Planes of an FP32 operand that the caller split beforehand (null hi = not supplied).
-struct SavedPlanes {
-    const float* hi = nullptr;
-    const float* lo = nullptr;
-    int64_t ld = 0;
-};
-
-static int linear_backward_impl(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
+int linear_backward_impl(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
                                 float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
                                 cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved) {
     DeviceState* st = nullptr;

@@ -60,6 +60,40 @@ int static_state(StaticState** out) {
 }
 
 }  // namespace
+
+// The error word of the kernels launched through tfb_matmul_f32_static on the current device: read,
+// and cleared if set. Nothing to do (code 0) when that entry point was never used on this device.
+// Copies through the address cudaGetSymbolAddress gave; allocates nothing.
+int static_status_take(int* code) {
+    *code = 0;
+    int dev = -1;
+    TFB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return TFB_OK;
+    int* word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        if (!g_static[dev].ready) return TFB_OK;
+        word = g_static[dev].dev.status;
+    }
+    TFB_CUDA_OK(cudaMemcpy(code, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*code != 0) TFB_CUDA_OK(cudaMemset(word, 0, sizeof(int)));
+    return TFB_OK;
+}
+
+int static_status_put(int code) {
+    int dev = -1;
+    TFB_CUDA_OK(cudaGetDevice(&dev));
+    int* word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        if (dev < 0 || dev >= 64 || !g_static[dev].ready)
+            return fail(TFB_ERR_INVALID_ARG, "tfb_matmul_f32_static has not run on device %d yet", dev);
+        word = g_static[dev].dev.status;
+    }
+    TFB_CUDA_OK(cudaMemcpy(word, &code, sizeof(int), cudaMemcpyHostToDevice));
+    return TFB_OK;
+}
+
 }  // namespace tfb
 
 extern "C" {

@@ -105,6 +105,47 @@ static void autograd_checks() {
         Tensor p = upload({1, 2, 3, 4}, Shape{2, 2});
         CHECK(p.matmul(p).grad_fn() == nullptr);
     }
+    // The same product in BFloat16: the result and both gradients have the operands' dtype (the
+    // reference's rule, tensor/Tensor.cpp:350), so the upstream gradient MatmulBackward receives is
+    // read with the dtype it was written in. The values are small integers, exact in BF16.
+    {
+        auto bf16 = [](const std::vector<float>& h) {
+            std::vector<uint16_t> o(h.size());
+            for (size_t i = 0; i < h.size(); ++i) {
+                uint32_t u;
+                std::memcpy(&u, &h[i], 4);
+                o[i] = static_cast<uint16_t>(u >> 16);
+            }
+            return o;
+        };
+        auto widen = [](const Tensor& t) {
+            std::vector<uint16_t> raw(static_cast<size_t>(t.numel()));
+            t.copy_to_host(raw.data());
+            std::vector<float> o(raw.size());
+            for (size_t i = 0; i < raw.size(); ++i) {
+                const uint32_t u = static_cast<uint32_t>(raw[i]) << 16;
+                std::memcpy(&o[i], &u, 4);
+            }
+            return o;
+        };
+        const auto ah = bf16({0, 1, 2, 3, 4, 5}), bh = bf16({0, 1, 2, 3, 4, 5}), gh = bf16({1, 1, 1, 1});
+        Tensor a = Tensor::from_host(ah.data(), Shape{2, 3}, Dtype::BFloat16, Device::cuda(0));
+        Tensor b = Tensor::from_host(bh.data(), Shape{3, 2}, Dtype::BFloat16, Device::cuda(0));
+        Tensor g = Tensor::from_host(gh.data(), Shape{2, 2}, Dtype::BFloat16, Device::cuda(0));
+        a.requires_grad(true);
+        b.requires_grad(true);
+        Tensor c = a.matmul(b);
+        CHECK(c.dtype() == Dtype::BFloat16);
+        auto ch = widen(c);
+        const float ec[4] = {10, 13, 28, 40};
+        for (int i = 0; i < 4; ++i) CHECK(ch[i] == ec[i]);
+        Engine engine;
+        engine.execute(c.grad_fn(), g);
+        CHECK(a.grad().dtype() == Dtype::BFloat16 && b.grad().dtype() == Dtype::BFloat16);
+        auto ga = widen(a.grad()), gb = widen(b.grad());
+        const float ea[6] = {1, 5, 9, 1, 5, 9}, eb[6] = {3, 3, 5, 5, 7, 7};
+        for (int i = 0; i < 6; ++i) CHECK(ga[i] == ea[i] && gb[i] == eb[i]);
+    }
     // relu: mask is 0 at x == 0 (autograd/ops/ReluBackward.hpp:26-30)
     {
         Tensor x = upload({-1.f, 0.f, 2.f, 3.f, -0.5f}, Shape{1, 5});

@@ -75,8 +75,10 @@ DeviceGuard::~DeviceGuard() {
 
 // ---- storage ----------------------------------------------------------------------------------------
 StorageImpl::~StorageImpl() {
+    // Freed on the stream that allocated it, not on the destroying thread's stream: work that thread A
+    // queued on the buffer is ordered before the release even when thread B drops the last reference.
     if (ptr != nullptr && device.type == DeviceType::CUDA)
-        (void)tfb_free(ptr, device.index, DeviceContext::for_device(device.index).current_stream);
+        (void)tfb_free(ptr, device.index, stream != nullptr ? stream : DeviceContext::for_device(device.index).current_stream);
     else if (ptr != nullptr)
         ::operator delete(ptr);
 }
@@ -90,9 +92,10 @@ Storage CudaStorageAllocator::allocate(size_t size_bytes, Device device, Dtype d
     if (device.type != DeviceType::CUDA)
         throw std::invalid_argument("CudaStorageAllocator can only allocate CUDA storage");
     void* p = nullptr;
-    ok(tfb_alloc(device.index, size_bytes, DeviceContext::for_device(device.index).current_stream, &p), "tfb_alloc");
+    void* stream = DeviceContext::for_device(device.index).current_stream;
+    ok(tfb_alloc(device.index, size_bytes, stream, &p), "tfb_alloc");
     auto s = std::make_shared<StorageImpl>();
-    s->ptr = p; s->bytes = size_bytes; s->device = device; s->dtype = dtype;
+    s->ptr = p; s->bytes = size_bytes; s->device = device; s->dtype = dtype; s->stream = stream;
     return s;
 }
 void CudaStorageAllocator::stats(int32_t device_index, uint64_t* reserved, uint64_t* used) const {
@@ -173,8 +176,11 @@ Tensor Tensor::matmul(const Tensor& other) const {
     if (g_cuda_matmul == nullptr) throw std::runtime_error("CUDA matmul kernel not registered");
     const int64_t M = shape_[0], K = shape_[1], N = other.shape_[1];
     DeviceGuard g(device().index);
-    Tensor out = Tensor::empty(Shape{M, N}, Dtype::Float32, device());
-    g_cuda_matmul(data(), other.data(), out.data(), M, N, K, dtype(), Dtype::Float32,
+    // The result has the operands' dtype, the reference's rule (tensor/Tensor.cpp:350); accumulation is
+    // FP32 whatever the storage type. MatmulBackward relies on it: the upstream gradient it receives
+    // then has the dtype it passes to tfb_matmul_backward.
+    Tensor out = Tensor::empty(Shape{M, N}, dtype(), device());
+    g_cuda_matmul(data(), other.data(), out.data(), M, N, K, dtype(), dtype(),
                   DeviceContext::for_device(device().index).current_stream);
     record_matmul(out, *this, other);
     return out;

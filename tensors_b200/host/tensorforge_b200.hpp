@@ -88,6 +88,7 @@ struct StorageImpl {
     size_t bytes = 0;
     Device device;
     Dtype dtype = Dtype::Float32;
+    void* stream = nullptr;   // the stream the memory was allocated on (CUDA storage)
     ~StorageImpl();   // returns device memory to its pool, stream-ordered
 };
 using Storage = std::shared_ptr<StorageImpl>;
@@ -138,8 +139,8 @@ public:
     Dtype dtype() const noexcept { return storage_ ? storage_->dtype : Dtype::Float32; }
     Device device() const noexcept { return storage_ ? storage_->device : Device::cpu(); }
 
-    // C[M,N] = this[M,K] · other[K,N]. CUDA tensors of one device; Float32 -> Float32,
-    // Float16 / BFloat16 -> Float32 (accumulate and output). Same argument checks and messages as
+    // C[M,N] = this[M,K] · other[K,N]. CUDA tensors of one device; the result has the operands' dtype
+    // (Float32, Float16 or BFloat16; FP32 accumulation), as in the reference. Same argument checks and messages as
     // the reference (tensor/Tensor.cpp:335-346) where they still apply. Records a MatmulBackward
     // node when an operand requires a gradient.
     Tensor matmul(const Tensor& other) const;

@@ -1,18 +1,46 @@
-"""Data-parallel MLP training step on libtfb (host side).
+"""Data-parallel MLP training step: a thin ctypes caller of the tfb_mlp object of libtfb.
 
-Mirrors the dataflow of the reference's training example (examples/train_mlp.cpp:161-183):
-Linear -> ReLU -> Linear -> ReLU -> Linear -> log_softmax + mean NLL -> backward -> SGD, with the
-documented momentum update (nn/optim/SGD.hpp:3-6). Every tensor operation is a libtfb call; torch
-only supplies device memory, streams and — for more than one rank — the NCCL all-reduce of the flat
-gradient buffer (one per step, a pure sum because each rank already divides by the global batch).
+The step itself — Linear -> ReLU -> Linear -> ReLU -> Linear -> log_softmax + mean NLL -> backward ->
+gradient exchange -> SGD with momentum (the dataflow of the reference's examples/train_mlp.cpp:161-183,
+update as documented in nn/optim/SGD.hpp:3-6) — lives in C++ behind the C-ABI (csrc/mlp_step.cu) and
+owns every device buffer. This module only maps those buffers as torch tensors for tests and
+benchmarks and moves the ranks' IPC handles through torch.distributed, which is the host's job.
+
+Two ways to exchange gradients between ranks:
+  exchange="peer"  the fused reduce-scatter / SGD / all-gather kernel over NVLink peer memory
+                   (tfb_mlp_exchange_update); the ranks' exchange regions are opened through CUDA IPC.
+  exchange="nccl"  ONE torch.distributed all-reduce over the flat gradient buffer, whose last slot
+                   carries the loss, followed by tfb_mlp_update.
+With device="cpu" the class only keeps the flat layout and the all-reduce (host logic, for CPU tests).
 """
 import ctypes
 
 import torch
 
-from . import capi
 
-lib = capi.lib
+def shard_rows(global_rows, rank, world):
+    """Contiguous row range [begin, end) of the global batch that `rank` owns (sizes differ by at most 1)."""
+    base, extra = divmod(int(global_rows), int(world))
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def flat_layout(dims):
+    """Offsets of (weight 0, bias 0, weight 1, ...) in the flat buffers and their total length: every
+    segment is padded to a multiple of 4 floats, the layout tfb_mlp_segment reports."""
+    offsets, off = [], 0
+    for i in range(len(dims) - 1):
+        for sz in (dims[i + 1] * dims[i], dims[i + 1]):
+            offsets.append(off)
+            off += (sz + 3) // 4 * 4
+    return offsets, off
+
+
+class _DeviceArray:
+    """Exposes library-owned device memory to torch through the CUDA array interface."""
+
+    def __init__(self, ptr, n, typestr="<f4"):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (int(ptr), False), "version": 2}
 
 
 def _p(t):
@@ -23,40 +51,69 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def shard_rows(global_rows, rank, world):
-    """Contiguous row range [begin, end) of the global batch that `rank` owns (sizes differ by at most 1)."""
-    base, extra = divmod(int(global_rows), int(world))
-    begin = rank * base + min(rank, extra)
-    return begin, begin + base + (1 if rank < extra else 0)
-
-
 class MLP:
     """dims = (d0, d1, ..., dL): L Linear layers, ReLU after all but the last."""
 
-    def __init__(self, dims, weights, biases=None, device="cuda", process_group=None):
+    P_PARAMS, P_GRADS, P_VELOCITY, P_LOSS, P_REDUCED, P_ACT, P_REGION = range(7)
+    CAP_STEP, CAP_FB, CAP_UPDATE = range(3)
+    OPT_WAIT_NS, OPT_CTAS, OPT_KEEP_REDUCED = range(3)
+
+    def __init__(self, dims, weights, biases=None, device="cuda", process_group=None, max_rows=8192,
+                 exchange="peer"):
         self.dims = tuple(int(d) for d in dims)
         self.L = len(self.dims) - 1
-        sizes = []
-        for i in range(self.L):
-            sizes += [self.dims[i + 1] * self.dims[i], self.dims[i + 1]]
-        # 16-byte aligned segment starts keep every parameter usable as a TMA operand
-        self.offsets = []
-        off = 0
-        for sz in sizes:
-            self.offsets.append(off)
-            off += (sz + 3) // 4 * 4
-        self.numel = off
-        self.params = torch.zeros(off, device=device, dtype=torch.float32)
-        self.grads = torch.zeros(off, device=device, dtype=torch.float32)
-        self.velocity = torch.zeros(off, device=device, dtype=torch.float32)
+        self.offsets, self.numel = flat_layout(self.dims)
         self.group = process_group
+        self.exchange = exchange
+        self.handle = None
+        self.max_rows = int(max_rows)
+        self._rows = 0
+        self._graph = None
+        if device == "cpu":
+            self.params = torch.zeros(self.numel)
+            self.grads_and_loss = torch.zeros(self.numel + 4)
+            self.velocity = torch.zeros(self.numel)
+            self.loss = torch.zeros(1)
+        else:
+            from . import capi
+            self.capi, self.lib = capi, capi.lib
+            arr = (ctypes.c_int64 * (self.L + 1))(*self.dims)
+            h = ctypes.c_void_p()
+            capi.check(self.lib.tfb_mlp_create(self.L, arr, self.max_rows, ctypes.byref(h)))
+            self.handle = h
+            assert int(self.lib.tfb_mlp_numel(h)) == self.numel
+            for i in range(self.L):
+                wo, bo = ctypes.c_int64(), ctypes.c_int64()
+                capi.check(self.lib.tfb_mlp_segment(h, i, ctypes.byref(wo), ctypes.byref(bo)))
+                assert (wo.value, bo.value) == (self.offsets[2 * i], self.offsets[2 * i + 1])
+            self.params = self._map(self.P_PARAMS, self.numel)
+            self.grads_and_loss = self._map(self.P_GRADS, self.numel + 4)
+            self.velocity = self._map(self.P_VELOCITY, self.numel)
+            self.loss = self._map(self.P_LOSS, 1)
+            self.reduced = self._map(self.P_REDUCED, self.numel)
+        self.grads = self.grads_and_loss[:self.numel]
         for i in range(self.L):
             self.weight(i).copy_(torch.as_tensor(weights[i], dtype=torch.float32).reshape(self.dims[i + 1], self.dims[i]))
             if biases is not None and biases[i] is not None:
                 self.bias(i).copy_(torch.as_tensor(biases[i], dtype=torch.float32))
-        self.loss = torch.zeros(1, device=device, dtype=torch.float32)
-        self._acts = None
-        self._plane_bufs = {}
+        self._connected = False
+
+    def __del__(self):
+        try:
+            if self.handle is not None:
+                self.lib.tfb_mlp_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+    # ---- buffers ---------------------------------------------------------------------------------
+    def _ptr(self, which, layer=0):
+        p = ctypes.c_void_p()
+        self.capi.check(self.lib.tfb_mlp_buffer(self.handle, which, layer, ctypes.byref(p)))
+        return p.value
+
+    def _map(self, which, n, layer=0):
+        return torch.as_tensor(_DeviceArray(self._ptr(which, layer), n), device="cuda")
 
     def _seg(self, buf, k, shape):
         n = 1
@@ -70,115 +127,118 @@ class MLP:
     def bias(self, i, buf=None):
         return self._seg(self.params if buf is None else buf, 2 * i + 1, (self.dims[i + 1],))
 
-    def _planes(self, key, rows, cols, device):
-        """Persistent hi / lo plane buffer [2, rows, ld] for a rows x cols FP32 operand."""
-        ld = (cols + 3) // 4 * 4
-        buf = self._plane_bufs.get(key)
-        if buf is None or buf.shape != (2, rows, ld) or buf.device != device:
-            buf = torch.empty((2, rows, ld), device=device, dtype=torch.float32)
-            self._plane_bufs[key] = buf
-        return buf, ld
+    def activation(self, i):
+        """Output of layer i of the last forward pass, [rows, dims[i + 1]] (a view of library memory)."""
+        return self._map(self.P_ACT, self._rows * self.dims[i + 1], i).view(self._rows, self.dims[i + 1])
 
-    def _split(self, key, t):
-        rows, cols = t.shape
-        buf, ld = self._planes(key, rows, cols, t.device)
-        capi.check(lib.tfb_split_tf32(_p(t), rows, cols, cols, _p(buf[0]), _p(buf[1]), ld, _stream()))
-        return buf, ld
+    @property
+    def _acts(self):
+        return [None] + [self.activation(i) for i in range(self.L)]
 
-    def forward(self, X):
-        """Each operand is split into its TF32 hi / lo planes once per step; the planes made for the
-        forward products are kept for the backward ones."""
-        batch = X.shape[0]
-        acts = [X]
-        self._xs, self._ws = [], []
-        # All weights live in one flat buffer with 16-byte aligned segments, so one launch splits them
-        # all; a weight whose row length is a multiple of 4 is then a view of the flat planes.
-        flat, _ = self._split(("params",), self.params.view(1, -1))
-        for i in range(self.L):
-            xs, ldx = self._split(("x", i), acts[-1])
-            if self.dims[i] % 4 == 0:
-                n = self.dims[i + 1] * self.dims[i]
-                ws = flat[:, 0, self.offsets[2 * i]:self.offsets[2 * i] + n].view(2, self.dims[i + 1], self.dims[i])
-                ldw = self.dims[i]
-            else:
-                ws, ldw = self._split(("w", i), self.weight(i))
-            Y = torch.empty((batch, self.dims[i + 1]), device=X.device, dtype=torch.float32)
-            flags = capi.EPI_BIAS_COL | (capi.EPI_RELU if i < self.L - 1 else 0)
-            capi.check(lib.tfb_gemm_presplit(_p(xs[0]), _p(xs[1]), _p(ws[0]), _p(ws[1]), _p(Y), batch,
-                                             self.dims[i + 1], self.dims[i], ldx, ldw, self.dims[i + 1], 0, 1,
-                                             _p(self.bias(i)), flags, _stream()))
-            acts.append(Y)
-            self._xs.append((xs, ldx))
-            self._ws.append((ws, ldw))
-        self._acts = acts
-        return acts[-1]
+    def set_option(self, option, value):
+        self.capi.check(self.lib.tfb_mlp_set_option(self.handle, option, int(value)))
 
-    def forward_backward(self, X, labels, global_rows=None):
-        """Fills self.grads (this rank's share of the full-batch gradient) and self.loss."""
-        batch = X.shape[0]
-        global_rows = int(global_rows or batch)
-        logits = self.forward(X)
-        acts = self._acts
-        dz = torch.empty_like(logits)
-        capi.check(lib.tfb_log_softmax_nll(_p(logits), _p(labels), _p(dz), _p(self.loss), batch, self.dims[-1],
-                                           global_rows, _stream()))
-        upstream = dz
-        for i in reversed(range(self.L)):
-            relu = i < self.L - 1
-            dX = torch.empty_like(acts[i]) if i > 0 else None
-            (xs, ldx), (ws, ldw) = self._xs[i], self._ws[i]
-            capi.check(lib.tfb_linear_backward_presplit(
-                _p(xs[0]), _p(xs[1]), ldx, _p(ws[0]), _p(ws[1]), ldw, _p(acts[i + 1]), _p(upstream), _p(dX),
-                _p(self.weight(i, self.grads)), _p(self.bias(i, self.grads)), batch, self.dims[i],
-                self.dims[i + 1], int(relu), _stream()))
-            upstream = dX
-        return self.loss
-
-    def allreduce_grads(self):
-        if self._distributed():
-            torch.distributed.all_reduce(self.grads, group=self.group)
-            torch.distributed.all_reduce(self.loss, group=self.group)
-
-    def sgd_step(self, lr, momentum):
-        capi.check(lib.tfb_sgd_momentum(_p(self.params), _p(self.velocity), _p(self.grads), self.numel,
-                                        float(lr), float(momentum), 1.0, _stream()))
-
+    # ---- group -----------------------------------------------------------------------------------
     def _distributed(self):
+        """exchange="local" keeps a handle out of the process group (a single-rank reference run next to
+        a distributed one)."""
+        if self.exchange == "local":
+            return False
         return self.group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
                                           and torch.distributed.get_world_size() > 1)
 
-    def capture_train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None, warmup=2):
-        """Records one training step into CUDA graphs and returns a callable that replays it: the
-        step's ~40 launches then cost one or two graph launches on the host. Forward + backward and the
-        SGD update are captured; with more than one rank the NCCL all-reduce stays an ordinary call
-        between the two graphs (a collective is not recorded into a graph here). X and labels are
-        captured by address — refill them in place for the next batch. The warm-up steps run eagerly
-        first so that every scratch buffer exists before capture."""
-        for _ in range(max(1, warmup)):
-            self.train_step(X, labels, lr, momentum, global_rows)
-        torch.cuda.synchronize()
-        distributed = self._distributed()
-        g_fb, g_sgd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_fb):
-            self.forward_backward(X, labels, global_rows)
-            if not distributed:
-                self.sgd_step(lr, momentum)
-        if distributed:
-            with torch.cuda.graph(g_sgd):
-                self.sgd_step(lr, momentum)
+    def connect(self):
+        """Opens the other ranks' exchange regions (CUDA IPC handles gathered through the process group).
+        Collective: every rank of the group calls it; raises on every rank if any rank could not map its
+        peers (the group then stays unconnected and the NCCL exchange remains available)."""
+        if self._connected or not self._distributed():
+            return
+        dist = torch.distributed
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        nbytes = int(self.lib.tfb_mlp_ipc_handle_bytes())
+        mine = (ctypes.c_ubyte * nbytes)()
+        rc = self.lib.tfb_mlp_ipc_handle(self.handle, mine)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, bytes(mine) if rc == 0 else b"", group=self.group)
+        err = ""
+        if all(len(g) == nbytes for g in gathered):
+            rc = self.lib.tfb_mlp_connect_ipc(self.handle, rank, world, b"".join(gathered))
+        if rc != 0:
+            err = self.capi.last_error()
+        ok = torch.tensor([0.0 if rc != 0 else 1.0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)   # also the barrier: all peers are mapped
+        if ok.item() == 0:
+            self.disconnect()
+            raise RuntimeError("peer exchange unavailable: " + (err or "another rank could not map its peers"))
+        self._connected = True
 
-        def replay():
-            g_fb.replay()
-            if distributed:
-                self.allreduce_grads()
-                g_sgd.replay()
-            return self.loss
+    def disconnect(self):
+        """Unmaps the peers' regions. Collective when distributed: a region must not be freed while
+        another process still maps it, so every rank unmaps first and then all meet at a barrier."""
+        if self.handle is not None:
+            self.lib.tfb_mlp_connect_ptrs(self.handle, 0, 1, None)
+        if self._connected and self._distributed():
+            torch.distributed.barrier(group=self.group)
+        self._connected = False
 
-        replay.graphs = (g_fb, g_sgd)
-        return replay
+    # ---- the step --------------------------------------------------------------------------------
+    def forward_backward(self, X, labels, global_rows=None):
+        """Fills self.grads (this rank's share of the full-batch gradient) and its loss contribution."""
+        self._rows = int(X.shape[0])
+        self.capi.check(self.lib.tfb_mlp_forward_backward(self.handle, _p(X), _p(labels), self._rows,
+                                                          int(global_rows or self._rows), _stream()))
+        return self.grads_and_loss[self.numel:self.numel + 1]
+
+    def allreduce_grads(self):
+        """One collective: the flat gradient buffer with the loss contribution in its last slot."""
+        if self._distributed():
+            torch.distributed.all_reduce(self.grads_and_loss, group=self.group)
+
+    def sgd_step(self, lr, momentum):
+        if self.handle is None:
+            self.loss[0] = self.grads_and_loss[self.numel]
+            return
+        self.capi.check(self.lib.tfb_mlp_update(self.handle, float(lr), float(momentum), _stream()))
+
+    def exchange_update(self, lr, momentum):
+        self.capi.check(self.lib.tfb_mlp_exchange_update(self.handle, float(lr), float(momentum), _stream()))
+
+    def _use_peer(self):
+        return self.exchange == "peer" and self._distributed()
 
     def train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None):
         self.forward_backward(X, labels, global_rows)
-        self.allreduce_grads()
-        self.sgd_step(lr, momentum)
+        if self._use_peer():
+            self.connect()
+            self.exchange_update(lr, momentum)
+        else:
+            self.allreduce_grads()
+            self.sgd_step(lr, momentum)
         return self.loss
+
+    def capture_train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None, warmup=2):
+        """Records one training step into CUDA graphs held by the library and returns a callable that
+        replays it. With the peer exchange (or a single rank) the whole step is one graph; with the NCCL
+        exchange forward + backward is a graph, the all-reduce an ordinary call after it, and the update
+        a second handle-free launch. X and labels are captured by address — refill them in place. The
+        warm-up steps run eagerly first so that every scratch buffer exists before capture."""
+        for _ in range(max(1, warmup)):
+            self.train_step(X, labels, lr, momentum, global_rows)
+        torch.cuda.synchronize()
+        rows, g = int(X.shape[0]), int(global_rows or X.shape[0])
+        self._rows = rows
+        side = torch.cuda.Stream()
+        whole = self._use_peer() or not self._distributed()
+        what = self.CAP_STEP if whole else self.CAP_FB
+        self.capi.check(self.lib.tfb_mlp_capture_step(self.handle, _p(X), _p(labels), rows, g, float(lr), float(momentum),
+                                                      what, ctypes.c_void_p(side.cuda_stream)))
+        torch.cuda.synchronize()
+
+        def replay():
+            self.capi.check(self.lib.tfb_mlp_replay(self.handle, _stream()))
+            if not whole:
+                self.allreduce_grads()
+                self.sgd_step(lr, momentum)
+            return self.loss
+
+        return replay

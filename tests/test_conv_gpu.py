@@ -1,5 +1,6 @@
 """Parity of the implicit-GEMM Conv2d (forward, dgrad, wgrad, bias gradient) with the oracle, with the
 reference's own known answers and golden outputs, and the bit-exact im2col index map."""
+import ctypes
 import os
 
 import numpy as np
@@ -50,22 +51,23 @@ def feed(request):
     """By default a stride-1 product with at least 16 contraction channels runs on the TMA-fed GEMM
     kernel, short contractions (forward with Cin*kH*kW <= 128, input gradient with Cin <= 4, weight
     gradient with Cin*kH*kW < 32) on the CUDA-core kernels and everything else on the kernel with software gather producers.
-    TFB_CONV_TMA=2 sends every stride-1 product to the first, TFB_CONV_TMA=0 with TFB_CONV_DIRECT=0
+    The CONV_TMA knob at 2 sends every stride-1 product to the first; CONV_TMA = 0 with CONV_DIRECT = 0
     everything to the last, so each kernel gets every case it can take."""
-    old = {k: os.environ.get(k) for k in ("TFB_CONV_TMA", "TFB_CONV_DIRECT")}
-    for k in old:
-        os.environ.pop(k, None)
+    def get(knob):
+        v = ctypes.c_int(0)
+        capi.check(lib.tfb_get_tuning(knob, ctypes.byref(v)))
+        return v.value
+    old = {k: get(k) for k in (capi.TUNE_CONV_TMA, capi.TUNE_CONV_DIRECT)}
+    capi.check(lib.tfb_set_tuning(capi.TUNE_CONV_TMA, 1))
+    capi.check(lib.tfb_set_tuning(capi.TUNE_CONV_DIRECT, 1))
     if request.param == "gather_kernel":
-        os.environ["TFB_CONV_TMA"] = "0"
-        os.environ["TFB_CONV_DIRECT"] = "0"
+        capi.check(lib.tfb_set_tuning(capi.TUNE_CONV_TMA, 0))
+        capi.check(lib.tfb_set_tuning(capi.TUNE_CONV_DIRECT, 0))
     elif request.param == "tma_feed":
-        os.environ["TFB_CONV_TMA"] = "2"
+        capi.check(lib.tfb_set_tuning(capi.TUNE_CONV_TMA, 2))
     yield request.param
     for k, v in old.items():
-        if v is None:
-            os.environ.pop(k, None)
-        else:
-            os.environ[k] = v
+        capi.check(lib.tfb_set_tuning(k, v))
 
 
 def test_reference_known_answers(feed):
@@ -182,6 +184,54 @@ def test_im2col_index_map_bit_exact(oracle):
         got = index_map(0, 3, *args)
         want = oracle.im2col_index_range(0, got.size, *args)
         assert np.array_equal(got, want)
+
+
+def _own_index_tensor(N, C, H, W):
+    """x[n, c, h, w] = 1 + its own linear index inside sample n (exact in FP32 and in the hi + lo split:
+    at most 17 bits); 0 is left for the padding."""
+    per = C * H * W
+    return np.tile((np.arange(per, dtype=np.float32) + 1).reshape(1, C, H, W), (N, 1, 1, 1))
+
+
+@pytest.mark.parametrize("layer", [1, 2])
+def test_index_map_through_the_production_kernels_bit_exact(oracle, layer):
+    # The index map of the kernels the named configuration really runs (default dispatch: layer 1 on the
+    # CUDA-core kernels, layer 2 on the TMA-fed tensor-core path), forward and input gradient. The input
+    # holds each element's own linear index and every filter is one-hot, so an output element IS the
+    # index the kernel read (0 in the padding): integers, compared exactly with the reference formula
+    # (cuda/kernels/im2col.cu:67-98, restated in the oracle; the scheme of cuda/kernels/im2col_test.cpp:75-107).
+    Cin, Cout = (3, 64) if layer == 1 else (64, 128)
+    N, H, W, k, pad = 4, 32, 32, 3, 1
+    K, P = Cin * k * k, H * W
+    per = Cin * H * W
+    x = _own_index_tensor(N, Cin, H, W)
+    want_map = oracle.im2col_index_range(0, N * K * P, Cin, H, W, k, k, 1, 1, pad, pad, 1, 1).reshape(N, K, P)
+    sample_base = (np.arange(N, dtype=np.int64) * per).reshape(N, 1, 1)
+    want_val = np.where(want_map >= 0, want_map - sample_base + 1, 0)          # [N, K, P]
+    # forward: output channel j of a pass reads tap first + j and nothing else
+    for first in range(0, K, Cout):
+        taps = np.arange(first, min(first + Cout, K))
+        w = np.zeros((Cout, K), np.float32)
+        w[np.arange(len(taps)), taps] = 1.0
+        y = conv_forward(x, w.reshape(Cout, Cin, k, k), None, pad=(pad, pad)).reshape(N, Cout, P)
+        got = y[:, :len(taps)].astype(np.int64)
+        assert np.array_equal(got, want_val[:, taps]), (layer, first)
+        assert not y[:, len(taps):].any()
+    # input gradient: dY holds its own index, channel c of dX receives exactly one (co, ki, kj) per pass
+    dy = _own_index_tensor(N, Cout, H, W)                                      # out extent = in extent here
+    for tap in range(k * k):
+        w = np.zeros((Cout, Cin, k * k), np.float32)
+        co_of = (np.arange(Cin) * 7 + tap * 5) % Cout
+        w[co_of, np.arange(Cin), tap] = 1.0
+        gi, _, _ = conv_backward(x, w.reshape(Cout, Cin, k, k), dy, pad=(pad, pad))
+        want = np.zeros((N, per), np.int64)
+        for c in range(Cin):
+            t = c * k * k + tap
+            src = want_map[:, t, :]                                            # [N, P] offsets into x, or -1
+            val = (co_of[c] * P + np.arange(P, dtype=np.int64) + 1)[None, :].repeat(N, 0)
+            nn, pp = np.nonzero(src >= 0)
+            want[nn, src[nn, pp] - nn * per] = val[nn, pp]
+        assert np.array_equal(gi.reshape(N, per).astype(np.int64), want), (layer, tap)
 
 
 def test_config3_full_size_properties_and_sampled_oracle(oracle):

@@ -34,8 +34,9 @@ def _worker(rank, world, port, out_dir):
     for i in range(3):
         m.weight(i, m.grads).copy_(torch.from_numpy(dws[i]))
         m.bias(i, m.grads).copy_(torch.from_numpy(dbs[i]))
-    m.loss[0] = loss
-    m.allreduce_grads()
+    m.grads_and_loss[m.numel] = loss   # the loss contribution rides in the slot behind the gradients
+    m.allreduce_grads()                # one collective for both
+    m.sgd_step(0.1, 0.9)               # host-logic mode: only moves the summed loss into m.loss
     np.save(os.path.join(out_dir, f"grads_{rank}.npy"), m.grads.numpy())
     np.save(os.path.join(out_dir, f"loss_{rank}.npy"), m.loss.numpy())
     dist.destroy_process_group()

@@ -194,6 +194,40 @@ def test_square_sweep_sampled_rows_and_columns(oracle, n):
     assert rel_err(Cb[torch.from_numpy(rows[:16]).cuda()].cpu().numpy(), want) < BF16_TOL
 
 
+@pytest.mark.parametrize("n", [1024, 2048, 16384])
+def test_square_sweep_ends_fp32_and_bf16(oracle, n):
+    # The remaining sizes of the sweep, both input types: 64 full rows and 64 full columns against the
+    # reference's sequential FP32 loop, and the same rows against an FP64 product. At K = 16384 the
+    # reference's own sequential sum sits ~7e-6 from the exact result, so the distance to FP64 is
+    # reported next to the distance to the oracle: both must stay inside the budget.
+    a, b = refdata.uniform(2, (n, n)), refdata.uniform(3, (n, n))
+    A, B = dev(a), dev(b)
+    rows = np.linspace(0, n - 1, 64).astype(np.int64)
+    cols = np.linspace(0, n - 1, 64).astype(np.int64)
+    rows_t, cols_t = torch.from_numpy(rows).cuda(), torch.from_numpy(cols).cuda()
+    C = gemm_ex(A, B, n, n, n)
+    assert_device_ok()
+    got_rows, got_cols = C[rows_t].cpu().numpy(), C[:, cols_t].cpu().numpy()
+    exact_rows = (A[rows_t].double() @ B.double()).cpu().numpy()
+    want_rows, want_cols = oracle.matmul_rows(a, b, rows), oracle.matmul_cols(a, b, cols)
+    err_oracle = max(rel_err(got_rows, want_rows), rel_err(got_cols, want_cols))
+    err_exact, oracle_vs_exact = rel_err(got_rows, exact_rows), rel_err(want_rows, exact_rows)
+    print(f"n={n} fp32: vs oracle {err_oracle:.2e}, vs fp64 {err_exact:.2e} (oracle vs fp64 {oracle_vs_exact:.2e})")
+    assert err_oracle < FP32_TOL
+    assert err_exact < FP32_TOL
+    del C
+    a16, b16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
+    Cb = gemm_ex(a16, b16, n, n, n, in_dtype=capi.DTYPE_BF16)
+    assert_device_ok()
+    a16h, b16h = a16.float().cpu().numpy(), b16.float().cpu().numpy()
+    want = oracle.matmul_rows(a16h, b16h, rows[:16])
+    assert rel_err(Cb[rows_t[:16]].cpu().numpy(), want) < BF16_TOL
+    want = oracle.matmul_cols(a16h, b16h, cols[:16])
+    assert rel_err(Cb[:, cols_t[:16]].cpu().numpy(), want) < BF16_TOL
+    exact16 = (a16[rows_t[:16]].double() @ b16.double()).cpu().numpy()
+    assert rel_err(Cb[rows_t[:16]].cpu().numpy(), exact16) < BF16_TOL
+
+
 @pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
 @pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True)])
 @pytest.mark.parametrize("shape", [(512, 384, 8192), (1024, 1024, 4096), (1024, 784, 8192), (100, 130, 3000),

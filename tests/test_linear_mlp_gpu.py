@@ -140,15 +140,20 @@ def test_log_softmax_nll_and_sgd(oracle, golden):
     assert np.array_equal(P.cpu().numpy(), op)
 
 
+def local_loss(m):
+    """This rank's loss contribution: the slot behind the flat gradients."""
+    return float(m.grads_and_loss[m.numel].item())
+
+
 def test_mlp_step_against_reference_golden_and_oracle(oracle, golden):
     from tensors_b200.mlp import MLP
     dims = (784, 64, 48, 10)
     ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
     xb, lab = refdata.mnist_like(42, (32, 784)), refdata.labels(43, 32)
-    m = MLP(dims, ws)
+    m = MLP(dims, ws, max_rows=32)
     m.forward_backward(dev(xb), torch.from_numpy(lab).cuda())
     assert_device_ok()
-    assert abs(float(m.loss.item()) - float(golden["mlp_loss"][0])) < 1e-5
+    assert abs(local_loss(m) - float(golden["mlp_loss"][0])) < 1e-5
     assert rel_err(m.weight(2, m.grads).cpu().numpy(), golden["mlp_dW3"]) < 2e-5
     assert rel_err(m.weight(1, m.grads).cpu().numpy(), golden["mlp_dW2"]) < 2e-5
     assert rel_err(m.weight(0, m.grads).cpu().numpy()[[0, 7, 63]], golden["mlp_dW1_rows"]) < 2e-5
@@ -160,7 +165,7 @@ def test_mlp_step_config5_shapes_reduced_batch(oracle):
     dims = (784, 1024, 1024, 10)
     ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
     xb, lab = refdata.mnist_like(7, (256, 784)), refdata.labels(8, 256)
-    m = MLP(dims, ws)
+    m = MLP(dims, ws, max_rows=256)
     p0 = m.params.clone()
     m.train_step(dev(xb), torch.from_numpy(lab).cuda(), lr=0.1, momentum=0.9)
     assert_device_ok()
@@ -169,20 +174,22 @@ def test_mlp_step_config5_shapes_reduced_batch(oracle):
     for i in range(3):
         assert rel_err(m.weight(i, m.grads).cpu().numpy(), odw[i]) < 2e-5, i
         assert rel_err(m.bias(i, m.grads).cpu().numpy(), odb[i]) < 2e-5, i
-    # velocity starts at zero: p1 = p0 - lr * g
-    assert torch.allclose(m.params, p0 - 0.1 * m.grads, rtol=0, atol=1e-7)
+    # velocity starts at zero: v1 = g, p1 = p0 - lr * g — the host formula, bit for bit
+    op, ov = oracle.sgd_momentum(p0.cpu().numpy(), np.zeros(m.numel, np.float32), m.grads.cpu().numpy(), 0.1, 0.9)
+    assert np.array_equal(m.velocity.cpu().numpy(), ov)
+    assert np.array_equal(m.params.cpu().numpy(), op)
 
 
 def test_mlp_graph_replay_matches_eager_steps(oracle):
-    # three eager steps and three replays of the captured step must walk the same trajectory
+    # five eager steps and two eager + three replays of the captured step must walk the same trajectory
     from tensors_b200.mlp import MLP
     dims = (784, 128, 64, 10)
     ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
     X, L = dev(refdata.mnist_like(7, (512, 784))), torch.from_numpy(refdata.labels(8, 512)).cuda()
-    eager = MLP(dims, ws)
+    eager = MLP(dims, ws, max_rows=512)
     for _ in range(5):
         eager.train_step(X, L, lr=0.1, momentum=0.9)
-    graphed = MLP(dims, ws)
+    graphed = MLP(dims, ws, max_rows=512)
     replay = graphed.capture_train_step(X, L, lr=0.1, momentum=0.9, warmup=2)   # 2 eager + 1 captured (not run)
     for _ in range(3):
         replay()
@@ -206,20 +213,20 @@ def test_mlp_full_batch_data_parallel_invariance(oracle):
     ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
     xb, lab = refdata.mnist_like(7, (batch, 784)), refdata.labels(8, batch)
     X, L = dev(xb), torch.from_numpy(lab).cuda()
-    full = MLP(dims, ws)
+    full = MLP(dims, ws, max_rows=batch)
     full.forward_backward(X, L)
     assert_device_ok()
-    g1, loss1 = full.grads.clone(), float(full.loss.item())
+    g1, loss1 = full.grads.clone(), local_loss(full)
     hidden1 = [a.clone() for a in full._acts[1:3]]
     assert np.isfinite(loss1) and 2.0 < loss1 < 2.7   # ten classes, small random weights: about ln 10
     for G in (2, 4, 8):
         total, loss, ties = torch.zeros_like(g1), 0.0, 0
+        m = MLP(dims, ws, max_rows=batch // G + 1)
         for r in range(G):
             b, e = shard_rows(batch, r, G)
-            m = MLP(dims, ws)
             m.forward_backward(X[b:e], L[b:e], global_rows=batch)
             total += m.grads
-            loss += float(m.loss.item())
+            loss += local_loss(m)
             for h_full, h_shard in zip(hidden1, m._acts[1:3]):
                 flipped = (h_full[b:e] > 0) != (h_shard > 0)
                 ties += int(flipped.sum())
@@ -233,9 +240,9 @@ def test_mlp_full_batch_data_parallel_invariance(oracle):
         bound = 1e-5 + 1e-3 * ties
         assert float((total - g1).norm() / g1.norm()) < bound, (G, ties)
     # sampled oracle: the first 64 rows as one rank's shard of the global batch
-    sub = MLP(dims, ws)
+    sub = MLP(dims, ws, max_rows=64)
     sub.forward_backward(X[:64], L[:64], global_rows=batch)
     ol, odw, _ = oracle.mlp_grads(xb[:64], lab[:64], ws, bs=[np.zeros(d, np.float32) for d in dims[1:]],
                                   global_rows=batch)
-    assert abs(float(sub.loss.item()) - ol) < 1e-6
+    assert abs(local_loss(sub) - ol) < 1e-6
     assert rel_err(sub.weight(2, sub.grads).cpu().numpy(), odw[2]) < 2e-5
