@@ -102,6 +102,7 @@ def config2(iters):
 
 
 EXCHANGE = "peer"
+MLP_ROWS = 0
 CONV_N, CONV_LAYERS, CONV_PASSES = 128, ("1", "2"), ("forward", "dgrad", "wgrad+dbias")
 
 
@@ -156,6 +157,8 @@ def config5(iters):
     dims, batch = (784, 1024, 1024, 10), 8192
     ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
     b, e = shard_rows(batch, rank, world)
+    if MLP_ROWS > 0:   # one rank's shard of a larger group, run alone: the per-rank compute of that group size
+        b, e = 0, MLP_ROWS
     X = dev(refdata.mnist_like(7, (batch, 784))[b:e])
     labels = torch.from_numpy(refdata.labels(8, batch)[b:e]).cuda()
     m = MLP(dims, ws, max_rows=e - b, exchange=EXCHANGE)
@@ -172,6 +175,7 @@ def config5(iters):
         us, fb, ar, us_eager = [float(v) for v in t.tolist()]
     if rank == 0:
         emit(config=5, what=f"MLP 784-1024-1024-10 step (CUDA graph replay), global batch 8192 on {world} GPU(s)", us=us,
+             rows_per_rank=e - b,
              exchange=EXCHANGE if world > 1 else "none", eager_us=us_eager, forward_backward_us=fb, allreduce_us=ar,
              tflops=78.35e9 / us / 1e6, loss=float(m.loss.item()))
     m.disconnect()
@@ -187,10 +191,13 @@ def main():
     ap.add_argument("--conv-n", type=int, default=128, help="config 3: batch size")
     ap.add_argument("--conv-layers", default="1,2", help="config 3: which layers")
     ap.add_argument("--conv-passes", default="forward,dgrad,wgrad+dbias", help="config 3: which passes")
+    ap.add_argument("--mlp-rows", type=int, default=0,
+                    help="config 5 on one GPU: run only this many rows of the global batch of 8192 (the shard of one "
+                         "rank of a larger group)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="config 5 with more than one rank")
     a = ap.parse_args()
-    global CONV_N, CONV_LAYERS, CONV_PASSES, EXCHANGE
-    EXCHANGE = a.exchange
+    global CONV_N, CONV_LAYERS, CONV_PASSES, EXCHANGE, MLP_ROWS
+    EXCHANGE, MLP_ROWS = a.exchange, a.mlp_rows
     CONV_N, CONV_LAYERS, CONV_PASSES = a.conv_n, tuple(a.conv_layers.split(",")), tuple(a.conv_passes.split(","))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     capi.check(lib.tfb_init())

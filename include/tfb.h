@@ -67,6 +67,9 @@ const char* tfb_last_error_string(void);
  *   CONV_DIRECT     0 = never use the CUDA-core kernels for short contractions, 1 = choose
  *   CONV_PAIR       -1 = choose, 0 / 1 = CTA pairs off / on in the TMA-fed convolution path
  *   HOST_PANEL_ROWS rows of A per panel in tfb_matmul_host (default 512)
+ *   PDL             1 (default) = kernels are launched so that each may start its prologue while the one
+ *                   before it on the stream is finishing (programmatic dependent launch); 0 = plain
+ *                   stream order (environment: TFB_PDL)
  * ref: no counterpart (the reference has one kernel per operation). */
 #define TFB_TUNE_GEMM_TILE_N 0
 #define TFB_TUNE_GEMM_PAIR 1
@@ -76,7 +79,8 @@ const char* tfb_last_error_string(void);
 #define TFB_TUNE_CONV_DIRECT 5
 #define TFB_TUNE_CONV_PAIR 6
 #define TFB_TUNE_HOST_PANEL_ROWS 7
-#define TFB_TUNE_COUNT 8
+#define TFB_TUNE_PDL 8
+#define TFB_TUNE_COUNT 9
 int tfb_set_tuning(int knob, int value);
 int tfb_get_tuning(int knob, int* value_out);
 

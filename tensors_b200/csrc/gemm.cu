@@ -166,12 +166,16 @@ __device__ __forceinline__ void split_tf32_body(const SplitJob& job, long long b
 __global__ void split_tf32_kernel(const float* __restrict__ src, long long rows, long long cols,
                                   long long ld, const float* __restrict__ mask,
                                   float* __restrict__ hi, float* __restrict__ lo, long long ld_out) {
+    pdl_wait();
+    pdl_launch_dependents();
     const SplitJob job{src, rows, cols, ld, mask, hi, lo, ld_out};
     split_tf32_body(job, blockIdx.x, gridDim.x);
 }
 
 // Both operands of a product in one launch: blocks [0, blocks_a) split A, the rest split B.
 __global__ void split_tf32_pair_kernel(const SplitJob a, const SplitJob b, int blocks_a) {
+    pdl_wait();
+    pdl_launch_dependents();
     if ((int)blockIdx.x < blocks_a) split_tf32_body(a, blockIdx.x, blocks_a);
     else split_tf32_body(b, (long long)blockIdx.x - blocks_a, (long long)gridDim.x - blocks_a);
 }
@@ -179,6 +183,8 @@ __global__ void split_tf32_pair_kernel(const SplitJob a, const SplitJob b, int b
 // Copies a 16-bit matrix into a buffer whose leading dimension is a multiple of 8.
 __global__ void pack16_kernel(const uint16_t* __restrict__ src, long long rows, long long cols,
                               long long ld, uint16_t* __restrict__ dst, long long ld_out) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long total = rows * ld_out;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -190,6 +196,8 @@ __global__ void pack16_kernel(const uint16_t* __restrict__ src, long long rows, 
 
 // C = epilogue(0) for a contraction of length zero.
 __global__ void empty_k_kernel(const GemmArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long total = (long long)a.M * a.N;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -209,6 +217,8 @@ __global__ void empty_k_kernel(const GemmArgs a) {
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long M, long long N,
                                      long long ld, long long split_stride, void* __restrict__ C, long long ldc,
                                      int out_type, const float* __restrict__ bias, int bias_mode, int relu) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long total = M * N;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -255,13 +265,17 @@ int launch_variant(const CUtensorMap maps[5], const GemmArgs& args, int workers,
     cfg.blockDim = dim3((unsigned)gemm_threads(KIND));
     cfg.dynamicSmemBytes = S::TOTAL;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = PAIR ? 2 : 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // The kernel's prologue (barriers, tensor memory, descriptor prefetch) may overlap the tail of the
+    // kernel before it; its pdl_wait() precedes every access to global memory.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tuning(TFB_TUNE_PDL) != 0 ? 2 : 1;
     TFB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], args));
     return TFB_OK;
 }
@@ -304,10 +318,8 @@ int split_operand_on(int sm_count, const float* src, int64_t rows, int64_t cols,
                      float* hi, float* lo, int64_t ld_out, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return TFB_OK;
     const long long items = rows * (ld_out >> 2);
-    split_tf32_kernel<<<grid_for(items, 256, sm_count), 256, 0, stream>>>(
-        src, rows, cols, ld, mask, hi, lo, ld_out);
-    TFB_CUDA_OK(cudaGetLastError());
-    return TFB_OK;
+    return launch_pdl(split_tf32_kernel, dim3((unsigned)grid_for(items, 256, sm_count)), dim3(256), 0, stream, src,
+                      (long long)rows, (long long)cols, (long long)ld, mask, hi, lo, (long long)ld_out);
 }
 
 int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
@@ -475,8 +487,8 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
                 // one launch for both operands, blocks shared out in proportion to their sizes
                 const long long ia = jobs[0].rows * (jobs[0].ld_out >> 2), ib = jobs[1].rows * (jobs[1].ld_out >> 2);
                 const int ga = grid_for(ia, 256, st->sm_count), gb = grid_for(ib, 256, st->sm_count);
-                split_tf32_pair_kernel<<<ga + gb, 256, 0, stream>>>(jobs[0], jobs[1], ga);
-                TFB_CUDA_OK(cudaGetLastError());
+                rc = launch_pdl(split_tf32_pair_kernel, dim3((unsigned)(ga + gb)), dim3(256), 0, stream, jobs[0], jobs[1], ga);
+                if (rc != TFB_OK) return rc;
             }
         } else {
             if (c.a_mask != nullptr)
@@ -484,17 +496,19 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
             if (!aligned16(c.A) || (c.lda & 7)) {
                 const int64_t ldp = round_up(a_cols, 8);
                 uint16_t* d = reinterpret_cast<uint16_t*>(carve((size_t)(a_rows * ldp * 2)));
-                pack16_kernel<<<grid_for(a_rows * ldp, 256, st->sm_count), 256, 0, stream>>>(
-                    static_cast<const uint16_t*>(c.A), a_rows, a_cols, c.lda, d, ldp);
-                TFB_CUDA_OK(cudaGetLastError());
+                rc = launch_pdl(pack16_kernel, dim3((unsigned)grid_for(a_rows * ldp, 256, st->sm_count)), dim3(256), 0, stream,
+                                static_cast<const uint16_t*>(c.A), (long long)a_rows, (long long)a_cols, (long long)c.lda, d,
+                                (long long)ldp);
+                if (rc != TFB_OK) return rc;
                 a_ptr[0] = d; lda = ldp;
             }
             if (!aligned16(c.B) || (c.ldb & 7)) {
                 const int64_t ldp = round_up(b_cols, 8);
                 uint16_t* d = reinterpret_cast<uint16_t*>(carve((size_t)(b_rows * ldp * 2)));
-                pack16_kernel<<<grid_for(b_rows * ldp, 256, st->sm_count), 256, 0, stream>>>(
-                    static_cast<const uint16_t*>(c.B), b_rows, b_cols, c.ldb, d, ldp);
-                TFB_CUDA_OK(cudaGetLastError());
+                rc = launch_pdl(pack16_kernel, dim3((unsigned)grid_for(b_rows * ldp, 256, st->sm_count)), dim3(256), 0, stream,
+                                static_cast<const uint16_t*>(c.B), (long long)b_rows, (long long)b_cols, (long long)c.ldb, d,
+                                (long long)ldp);
+                if (rc != TFB_OK) return rc;
                 b_ptr[0] = d; ldb = ldp;
             }
         }
@@ -531,9 +545,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     if (c.K <= 0) {
         // Empty contraction: the product is zero and only the epilogue remains.
         const long long total = (long long)c.M * c.N;
-        empty_k_kernel<<<grid_for(total, 256, st->sm_count), 256, 0, stream>>>(args);
-        TFB_CUDA_OK(cudaGetLastError());
-        return TFB_OK;
+        return launch_pdl(empty_k_kernel, dim3((unsigned)grid_for(total, 256, st->sm_count)), dim3(256), 0, stream, args);
     }
 
     CUtensorMap maps[5];
@@ -598,12 +610,11 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     }
     if (rc != TFB_OK || plan.split_k == 1) return rc;
     const long long total = (long long)c.M * c.N;
-    splitk_reduce_kernel<<<grid_for(total, 256, st->sm_count), 256, 0, stream>>>(
-        partial, plan.split_k, c.M, c.N, plan.ld_partial, plan.rows_per_split * plan.ld_partial, c.C, c.ldc,
-        c.out_dtype == TFB_DTYPE_F32 ? kOutF32 : (c.out_dtype == TFB_DTYPE_F16 ? kOutF16 : kOutBF16), c.bias,
-        c.bias_mode, c.relu ? 1 : 0);
-    TFB_CUDA_OK(cudaGetLastError());
-    return TFB_OK;
+    return launch_pdl(splitk_reduce_kernel, dim3((unsigned)grid_for(total, 256, st->sm_count)), dim3(256), 0, stream,
+                      (const float*)partial, plan.split_k, (long long)c.M, (long long)c.N, (long long)plan.ld_partial,
+                      (long long)(plan.rows_per_split * plan.ld_partial), c.C, (long long)c.ldc,
+                      (int)(c.out_dtype == TFB_DTYPE_F32 ? kOutF32 : (c.out_dtype == TFB_DTYPE_F16 ? kOutF16 : kOutBF16)),
+                      c.bias, c.bias_mode, c.relu ? 1 : 0);
 }
 
 }  // namespace tfb

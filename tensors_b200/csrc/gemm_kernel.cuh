@@ -309,6 +309,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    // Everything above touched only shared and tensor memory; operands and outputs of the kernels
+    // before this one are first accessed below.
+    pdl_wait();
+    pdl_launch_dependents();
 
     const int num_units = args.num_tiles * args.split_k;
 

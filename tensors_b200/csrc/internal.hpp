@@ -45,6 +45,26 @@ int workspace_get(cudaStream_t stream, size_t bytes, void** out);
 // Drops the buffer of (current device, stream), stream-ordered; called before the stream is destroyed.
 void workspace_release(cudaStream_t stream);
 
+// Launches `kernel` with the programmatic-serialization attribute (unless the PDL knob is off): the
+// kernel may begin while its predecessor on the stream is still finishing, which hides launch latency
+// and the kernel's own prologue in chains of short kernels. Every kernel launched through this MUST
+// execute pdl_wait() (ptx.cuh) in every thread before its first access to global memory.
+template <typename... KArgs, typename... Args>
+int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning(TFB_TUNE_PDL) != 0 ? 1 : 0;
+    TFB_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+    return TFB_OK;
+}
+
 // Element size of a TFB_DTYPE_* code, 0 if unknown.
 size_t dtype_size(int dtype);
 

@@ -10,12 +10,24 @@
 #include <cuda_fp16.h>
 
 #include "internal.hpp"
+#include "ptx.cuh"
 
 namespace tfb {
 
 namespace {
 
-constexpr int kColsumRowsPerBlock = 16;
+// Rows one block of the mask / split pass walks (and sums for the bias gradient): 16 for large batches,
+// fewer for small ones so that the grid still fills the GPU. A function of the shape alone, so the
+// summation order of the bias gradient is fixed for a given problem.
+constexpr int kColsumMaxRowsPerBlock = 16;
+inline int colsum_rows_per_block(int64_t rows, int64_t ld_out) {
+    // Fewer rows per block while the grid is short of ~64 K threads, but never more than 512 row blocks:
+    // the finish kernel adds the blocks' partial sums sequentially (8 at a time).
+    const int64_t vecs = rows * (ld_out / 4);
+    int r = kColsumMaxRowsPerBlock;
+    while (r > 1 && vecs / r < 65536 && rows / (r / 2) <= 512) r >>= 1;
+    return r;
+}
 
 __device__ __forceinline__ float tf32_rna(float x) {
     uint32_t r;
@@ -23,17 +35,19 @@ __device__ __forceinline__ float tf32_rna(float x) {
     return __uint_as_float(r);
 }
 
-// One block covers kColsumRowsPerBlock rows x (4 * blockDim.x) columns. Each thread owns four
+// One block covers rows_per_block rows x (4 * blockDim.x) columns. Each thread owns four
 // adjacent columns, walks the block's rows in ascending order, writes the masked value's hi / lo
 // planes and keeps the running column sums, which land in partial[blockIdx.y][col].
 __global__ void split_mask_colsum_kernel(const float* __restrict__ dY, const float* __restrict__ Y,
                                          long long rows, long long cols, long long ld,
                                          float* __restrict__ hi, float* __restrict__ lo, long long ld_out,
-                                         float* __restrict__ partial) {
+                                         float* __restrict__ partial, int rows_per_block) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long c = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (c >= ld_out) return;
-    const long long r0 = (long long)blockIdx.y * kColsumRowsPerBlock;
-    const long long r1 = min(r0 + (long long)kColsumRowsPerBlock, rows);
+    const long long r0 = (long long)blockIdx.y * rows_per_block;
+    const long long r1 = min(r0 + (long long)rows_per_block, rows);
     const bool vec = ((ld & 3) == 0) && (c + 4 <= cols) && ((reinterpret_cast<uintptr_t>(dY) & 15u) == 0) &&
                      (Y == nullptr || (reinterpret_cast<uintptr_t>(Y) & 15u) == 0);
     float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -78,11 +92,13 @@ __global__ void split_mask_colsum_kernel(const float* __restrict__ dY, const flo
 template <typename T>
 __global__ void mask_colsum16_kernel(const T* __restrict__ dY, const T* __restrict__ Y, long long rows,
                                      long long cols, long long ld, T* __restrict__ dZ, long long ld_out,
-                                     float* __restrict__ partial) {
+                                     float* __restrict__ partial, int rows_per_block) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= ld_out) return;
-    const long long r0 = (long long)blockIdx.y * kColsumRowsPerBlock;
-    const long long r1 = min(r0 + (long long)kColsumRowsPerBlock, rows);
+    const long long r0 = (long long)blockIdx.y * rows_per_block;
+    const long long r1 = min(r0 + (long long)rows_per_block, rows);
     float s = 0.f;
     for (long long r = r0; r < r1; ++r) {
         float v = 0.f;
@@ -102,6 +118,9 @@ __global__ void mask_colsum16_kernel(const T* __restrict__ dY, const T* __restri
 __global__ void colsum_finish_kernel(const float* __restrict__ partial, long long blocks, long long cols,
                                      long long ld, float* __restrict__ out) {
     __shared__ float sm[8][33];
+    pdl_wait();
+    pdl_launch_dependents();
+
     const long long c = (long long)blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
     if (c < cols)
@@ -143,7 +162,8 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
     if (batch <= 0 || in_f <= 0 || out_f <= 0) return TFB_OK;
     const bool f32 = dtype == TFB_DTYPE_F32;
     const int64_t ldz = round_up(out_f, f32 ? 4 : 8);
-    const int64_t row_blocks = (batch + kColsumRowsPerBlock - 1) / kColsumRowsPerBlock;
+    const int rpb = colsum_rows_per_block(batch, ldz);
+    const int64_t row_blocks = (batch + rpb - 1) / rpb;
 
     // The two products, described first so that their scratch needs are known.
     GemmCall gx, gw;
@@ -187,24 +207,27 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
         float* hi = static_cast<float*>(dz);
         float* lo = hi + batch * ldz;
         dim3 block(128), grid((unsigned)((ldz / 4 + 127) / 128), (unsigned)row_blocks);
-        split_mask_colsum_kernel<<<grid, block, 0, stream>>>(static_cast<const float*>(dY),
-                                                             static_cast<const float*>(mask), batch, out_f,
-                                                             out_f, hi, lo, ldz, partial);
+        rc = launch_pdl(split_mask_colsum_kernel, grid, block, 0, stream, static_cast<const float*>(dY),
+                        static_cast<const float*>(mask), (long long)batch, (long long)out_f, (long long)out_f, hi, lo,
+                        (long long)ldz, partial, rpb);
+        if (rc != TFB_OK) return rc;
     } else {
         dim3 block(128), grid((unsigned)((ldz + 127) / 128), (unsigned)row_blocks);
         if (dtype == TFB_DTYPE_BF16)
-            mask_colsum16_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(
-                static_cast<const __nv_bfloat16*>(dY), static_cast<const __nv_bfloat16*>(mask), batch, out_f,
-                out_f, static_cast<__nv_bfloat16*>(dz), ldz, partial);
+            rc = launch_pdl(mask_colsum16_kernel<__nv_bfloat16>, grid, block, 0, stream,
+                            static_cast<const __nv_bfloat16*>(dY), static_cast<const __nv_bfloat16*>(mask), (long long)batch,
+                            (long long)out_f, (long long)out_f, static_cast<__nv_bfloat16*>(dz), (long long)ldz, partial,
+                            rpb);
         else
-            mask_colsum16_kernel<__half><<<grid, block, 0, stream>>>(
-                static_cast<const __half*>(dY), static_cast<const __half*>(mask), batch, out_f, out_f,
-                static_cast<__half*>(dz), ldz, partial);
+            rc = launch_pdl(mask_colsum16_kernel<__half>, grid, block, 0, stream, static_cast<const __half*>(dY),
+                            static_cast<const __half*>(mask), (long long)batch, (long long)out_f, (long long)out_f,
+                            static_cast<__half*>(dz), (long long)ldz, partial, rpb);
+        if (rc != TFB_OK) return rc;
     }
-    TFB_CUDA_OK(cudaGetLastError());
     if (db != nullptr) {
-        colsum_finish_kernel<<<(unsigned)((out_f + 31) / 32), dim3(32, 8), 0, stream>>>(partial, row_blocks, out_f, ldz, db);
-        TFB_CUDA_OK(cudaGetLastError());
+        rc = launch_pdl(colsum_finish_kernel, dim3((unsigned)((out_f + 31) / 32)), dim3(32, 8), 0, stream,
+                        (const float*)partial, (long long)row_blocks, (long long)out_f, (long long)ldz, db);
+        if (rc != TFB_OK) return rc;
     }
     gx.A = gw.A = dz;
     gx.workspace = gw.workspace = gemm_ws;

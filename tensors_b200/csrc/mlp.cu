@@ -2,6 +2,7 @@
 // log_softmax + mean negative log-likelihood (loss and gradient with respect to the logits) and
 // SGD with momentum. Both are one pass over their data; neither is a contraction.
 #include "internal.hpp"
+#include "ptx.cuh"
 
 namespace tfb {
 
@@ -13,6 +14,8 @@ namespace {
 __global__ void log_softmax_nll_kernel(const float* __restrict__ logits, const long long* __restrict__ labels,
                                        float* __restrict__ dlogits, float* __restrict__ row_loss,
                                        long long rows, int cols, float n_inv) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -43,6 +46,9 @@ __global__ void log_softmax_nll_kernel(const float* __restrict__ logits, const l
 __global__ void loss_finish_kernel(const float* __restrict__ row_loss, long long rows, float n_inv,
                                    float* __restrict__ loss_out) {
     __shared__ float sm[1024];
+    pdl_wait();
+    pdl_launch_dependents();
+
     float s = 0.f;
     for (long long r = threadIdx.x; r < rows; r += blockDim.x) s += row_loss[r];
     sm[threadIdx.x] = s;
@@ -57,6 +63,8 @@ __global__ void loss_finish_kernel(const float* __restrict__ row_loss, long long
 // v <- mu * v + g; p <- p - lr * v   (separate multiply and add, like the host formula).
 __global__ void sgd_momentum_kernel(float* __restrict__ p, float* __restrict__ v, const float* __restrict__ g,
                                     long long n, float lr, float mu, float grad_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (long long)gridDim.x * blockDim.x) {
         const float gi = g[i] * grad_scale;
@@ -95,14 +103,13 @@ int tfb_log_softmax_nll(const float* logits, const int64_t* labels, float* dlogi
     const float n_inv = (float)(1.0 / (double)global_rows);
     const int block = 256;
     const long long grid = (rows * 32 + block - 1) / block;
-    log_softmax_nll_kernel<<<(unsigned)grid, block, 0, stream>>>(
-        logits, reinterpret_cast<const long long*>(labels), dlogits, row_loss, rows, (int)cols, n_inv);
-    TFB_CUDA_OK(cudaGetLastError());
-    if (loss_out != nullptr) {
-        loss_finish_kernel<<<1, 1024, 0, stream>>>(row_loss, rows, n_inv, loss_out);
-        TFB_CUDA_OK(cudaGetLastError());
-    }
-    return TFB_OK;
+    rc = launch_pdl(log_softmax_nll_kernel, dim3((unsigned)grid), dim3(block), 0, stream, logits,
+                    reinterpret_cast<const long long*>(labels), dlogits, row_loss, (long long)rows, (int)cols, n_inv);
+    if (rc != TFB_OK) return rc;
+    if (loss_out != nullptr)
+        rc = launch_pdl(loss_finish_kernel, dim3(1), dim3(1024), 0, stream, (const float*)row_loss, (long long)rows, n_inv,
+                        loss_out);
+    return rc;
 }
 
 int tfb_sgd_momentum(float* params, float* velocity, const float* grads, int64_t n, float lr,
@@ -118,10 +125,8 @@ int tfb_sgd_momentum(float* params, float* velocity, const float* grads, int64_t
     long long grid = (n + 255) / 256;
     const long long cap = (long long)st->sm_count * 8;
     if (grid > cap) grid = cap;
-    sgd_momentum_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream_v)>>>(
-        params, velocity, grads, n, lr, momentum, grad_scale);
-    TFB_CUDA_OK(cudaGetLastError());
-    return TFB_OK;
+    return launch_pdl(sgd_momentum_kernel, dim3((unsigned)grid), dim3(256), 0, static_cast<cudaStream_t>(stream_v), params,
+                      velocity, grads, (long long)n, lr, momentum, grad_scale);
 }
 
 }  // extern "C"

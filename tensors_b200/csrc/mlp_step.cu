@@ -99,6 +99,54 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
     }
 }
 
+// WORLD > 0: compile-time group size (all loads of one vector are issued before the first add);
+// U vectors per thread and iteration keep U * WORLD 16-byte loads in flight per thread.
+template <int WORLD, int U>
+__device__ __forceinline__ void exchange_slice_unrolled(const DpParams& p, const DpRank& me) {
+    const int rank = me.rank;
+    const long long v0 = p.n_vec * rank / WORLD, v1 = p.n_vec * (rank + 1) / WORLD;
+    const float lr = p.lr, mu = p.mu;
+    float4* my_params = reinterpret_cast<float4*>(me.region[rank] + p.params_off);
+    float4* vel = reinterpret_cast<float4*>(me.velocity);
+    const long long threads = (long long)gridDim.x * blockDim.x;
+    for (long long base = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; base < v1; base += threads * U) {
+        float4 g[U][WORLD], v[U], w[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long i = base + u * threads;
+            if (i < v1) {
+#pragma unroll
+                for (int r = 0; r < WORLD; ++r)
+                    g[u][r] = ld_peer(reinterpret_cast<const float4*>(me.region[r] + p.grads_off) + i);
+                v[u] = vel[i];
+                w[u] = my_params[i];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long i = base + u * threads;
+            if (i < v1) {
+                float4 s = g[u][0];
+#pragma unroll
+                for (int r = 1; r < WORLD; ++r) {
+                    s.x = __fadd_rn(s.x, g[u][r].x); s.y = __fadd_rn(s.y, g[u][r].y);
+                    s.z = __fadd_rn(s.z, g[u][r].z); s.w = __fadd_rn(s.w, g[u][r].w);
+                }
+                if (me.reduced != nullptr) reinterpret_cast<float4*>(me.reduced)[i] = s;
+                float4 vv = v[u], ww = w[u];
+                // v <- mu * v + g ; p <- p - lr * v, separate multiply and add like the host formula.
+                vv.x = __fadd_rn(__fmul_rn(mu, vv.x), s.x); vv.y = __fadd_rn(__fmul_rn(mu, vv.y), s.y);
+                vv.z = __fadd_rn(__fmul_rn(mu, vv.z), s.z); vv.w = __fadd_rn(__fmul_rn(mu, vv.w), s.w);
+                ww.x = __fsub_rn(ww.x, __fmul_rn(lr, vv.x)); ww.y = __fsub_rn(ww.y, __fmul_rn(lr, vv.y));
+                ww.z = __fsub_rn(ww.z, __fmul_rn(lr, vv.z)); ww.w = __fsub_rn(ww.w, __fmul_rn(lr, vv.w));
+                vel[i] = vv;
+#pragma unroll
+                for (int r = 0; r < WORLD; ++r) st_peer(reinterpret_cast<float4*>(me.region[r] + p.params_off) + i, ww);
+            }
+        }
+    }
+}
+
 template <int WORLD>
 __device__ __forceinline__ void exchange_slice(const DpParams& p, const DpRank& me, int world) {
     const int rank = me.rank;
@@ -137,6 +185,8 @@ __device__ __forceinline__ void exchange_slice(const DpParams& p, const DpRank& 
 
 __global__ void __launch_bounds__(kExchangeThreads)
 dp_exchange_kernel(const __grid_constant__ DpParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     const DpRank& me = p.ranks[blockIdx.y];
     const int world = p.world, rank = me.rank, cta = blockIdx.x;
     uint8_t* mine = me.region[rank];
@@ -166,10 +216,10 @@ dp_exchange_kernel(const __grid_constant__ DpParams p) {
             *me.loss_out = l;
         }
         switch (world) {
-        case 1: exchange_slice<1>(p, me, 1); break;
-        case 2: exchange_slice<2>(p, me, 2); break;
-        case 4: exchange_slice<4>(p, me, 4); break;
-        case 8: exchange_slice<8>(p, me, 8); break;
+        case 1: exchange_slice_unrolled<1, 4>(p, me); break;
+        case 2: exchange_slice_unrolled<2, 4>(p, me); break;
+        case 4: exchange_slice_unrolled<4, 2>(p, me); break;
+        case 8: exchange_slice_unrolled<8, 1>(p, me); break;
         default: exchange_slice<0>(p, me, world); break;
         }
     }
@@ -284,7 +334,9 @@ int exchange_grid(const tfb_mlp* m, int sm_count, int ranks_in_launch, int world
     // At most one CTA per SM (all CTAs must be resident while they wait for their peers), and enough
     // of them to keep a few MB of peer loads in flight.
     int g = m->exchange_ctas > 0 ? m->exchange_ctas : 128;
-    if (g > sm_count / ranks_in_launch) g = sm_count / ranks_in_launch;
+    // A group of one waits for nobody, so its CTAs need not all be resident: fill the GPU.
+    if (world == 1 && m->exchange_ctas == 0) g = 4 * sm_count;
+    else if (g > sm_count / ranks_in_launch) g = sm_count / ranks_in_launch;
     if (g > kMaxExchangeCtas) g = kMaxExchangeCtas;
     const long long vec_per_rank = m->numel / 4 / (world > 0 ? world : 1) + 1;
     const long long want = (vec_per_rank + kExchangeThreads - 1) / kExchangeThreads;
@@ -308,9 +360,7 @@ int launch_update(tfb_mlp* m, int world_in_kernel, float lr, float mu, cudaStrea
         p.ranks[0].region[0] = m->region;
     }
     const int grid = exchange_grid(m, st->sm_count, 1, world_in_kernel);
-    dp_exchange_kernel<<<dim3((unsigned)grid, 1), kExchangeThreads, 0, stream>>>(p);
-    TFB_CUDA_OK(cudaGetLastError());
-    return TFB_OK;
+    return launch_pdl(dp_exchange_kernel, dim3((unsigned)grid, 1), dim3(kExchangeThreads), 0, stream, p);
 }
 
 int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,

@@ -36,6 +36,19 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute
+// may start while the kernel before it on the stream is still running; pdl_wait() blocks until that
+// kernel has completed and its memory is visible, so it must come before the first access to global
+// memory. pdl_launch_dependents() lets the NEXT kernel start its own prologue early; since that
+// kernel waits for this whole grid in its own pdl_wait(), triggering early is always safe. Both are
+// no-ops in a kernel that was launched the ordinary way.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

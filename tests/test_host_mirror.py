@@ -29,6 +29,55 @@ def test_host_mirror_known_answers_on_gpu():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("ranks", [1, 2, 4])
+def test_data_parallel_mlp_step_from_plain_cpp(tmp_path, oracle, ranks):
+    # train_mlp_dp_b200 drives the tfb_mlp C-ABI from C++ alone: R ranks in one process (all on one GPU
+    # when fewer than R are visible), one step from the reference's own initial weights. The summed
+    # gradient must be the oracle's full-batch gradient, the update the momentum formula bit for bit, and
+    # every rank's replica of the parameters identical.
+    import numpy as np
+    import refdata
+    build()
+    dims, batch = (784, 128, 96, 10), 203   # ragged shards
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    bs = [np.zeros(d, np.float32) for d in dims[1:]]
+    x, lab = refdata.mnist_like(5, (batch, 784)), refdata.labels(6, batch)
+    prob, out = tmp_path / "problem.bin", tmp_path / "out.bin"
+    with open(prob, "wb") as f:
+        f.write(np.array([3, *dims, batch], np.int64).tobytes())
+        for w, b in zip(ws, bs):
+            f.write(np.ascontiguousarray(w, np.float32).tobytes())
+            f.write(b.tobytes())
+        f.write(np.ascontiguousarray(x, np.float32).tobytes())
+        f.write(np.ascontiguousarray(lab, np.int64).tobytes())
+    r = subprocess.run([os.path.join(HOST, "train_mlp_dp_b200"), str(prob), str(ranks), "1", str(out)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    raw = open(out, "rb").read()
+    loss = np.frombuffer(raw, np.float32, 1, 0)[0]
+    numel = int(np.frombuffer(raw, np.int64, 1, 4)[0])
+    params = np.frombuffer(raw, np.float32, numel, 12)
+    grads = np.frombuffer(raw, np.float32, numel, 12 + 4 * numel)
+    same = np.frombuffer(raw, np.int64, ranks, 12 + 8 * numel)
+    assert same.tolist() == [1] * ranks
+    ol, odw, odb = oracle.mlp_grads(x, lab, ws, bs=bs)
+    assert abs(float(loss) - ol) < 1e-5
+    from tensors_b200.mlp import flat_layout
+    offsets, n = flat_layout(dims)
+    assert n == numel
+    p0 = np.zeros(numel, np.float32)
+    for i in range(3):
+        wseg = slice(offsets[2 * i], offsets[2 * i] + ws[i].size)
+        bseg = slice(offsets[2 * i + 1], offsets[2 * i + 1] + bs[i].size)
+        p0[wseg] = ws[i].ravel()
+        err_w = np.linalg.norm(grads[wseg] - odw[i].ravel()) / np.linalg.norm(odw[i])
+        err_b = np.linalg.norm(grads[bseg] - odb[i]) / np.linalg.norm(odb[i])
+        assert err_w < 2e-5 and err_b < 2e-5, (i, err_w, err_b)
+    want_p, _ = oracle.sgd_momentum(p0, np.zeros(numel, np.float32), grads, 0.1, 0.9)
+    assert np.array_equal(params, want_p)
+
+
+@pytest.mark.gpu
 def test_training_loop_on_the_host_mirror_learns():
     # Linear -> relu -> Linear -> cross_entropy -> backward -> SGD, all on the device; exits 0 when the
     # loss at least halves

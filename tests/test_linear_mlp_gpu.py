@@ -198,6 +198,34 @@ def test_mlp_graph_replay_matches_eager_steps(oracle):
     assert float(eager.loss.item()) == float(graphed.loss.item())
 
 
+def test_mlp_steps_do_not_depend_on_programmatic_dependent_launch():
+    # With the PDL knob on (default) every kernel of the step may start while its predecessor is still
+    # finishing and waits inside the kernel instead; the trajectory must be bit-identical to plain stream order.
+    import ctypes
+    from tensors_b200.mlp import MLP
+    dims = (784, 256, 192, 10)
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    X, L = dev(refdata.mnist_like(7, (1024, 784))), torch.from_numpy(refdata.labels(8, 1024)).cuda()
+    old = ctypes.c_int(0)
+    capi.check(lib.tfb_get_tuning(capi.TUNE_PDL, ctypes.byref(old)))
+    out = {}
+    try:
+        for pdl in (1, 0):
+            capi.check(lib.tfb_set_tuning(capi.TUNE_PDL, pdl))
+            m = MLP(dims, ws, max_rows=1024)
+            for _ in range(4):
+                m.train_step(X, L, lr=0.1, momentum=0.9)
+            replay = m.capture_train_step(X, L, lr=0.1, momentum=0.9, warmup=1)
+            for _ in range(3):
+                replay()
+            assert_device_ok()
+            out[pdl] = (m.params.clone(), float(m.loss.item()))
+    finally:
+        capi.check(lib.tfb_set_tuning(capi.TUNE_PDL, old.value))
+    assert torch.equal(out[0][0], out[1][0])
+    assert out[0][1] == out[1][1]
+
+
 def test_mlp_full_batch_data_parallel_invariance(oracle):
     # The named configuration at its full global batch of 8192 rows. The batch is cut into G row shards
     # as G data-parallel ranks would hold them; each shard's gradient is scaled by the GLOBAL batch, so
