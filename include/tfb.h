@@ -111,6 +111,16 @@ int tfb_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_
 int tfb_matmul(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                int in_dtype, int out_dtype, void* stream);
 
+/* Batched product over the leading dimensions of N-D operands: C[b] = A[b] · B[b] for b < batch, every
+ * matrix row-major and dense; stride_* are the distances in elements between consecutive matrices
+ * (0 = the same matrix for every b). A shared B under densely stacked A and C (stride_b == 0,
+ * stride_a == M·K, stride_c == M·N) runs as ONE product of batch·M rows; every other case enqueues one
+ * product per matrix on `stream`. ref: no counterpart — Tensor::matmul refuses anything but two 2-D
+ * operands (tensor/Tensor.cpp:335-338); this is the N-D extension of the same contraction. */
+int tfb_matmul_batched(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N, int64_t K,
+                       int64_t stride_a, int64_t stride_b, int64_t stride_c, int in_dtype, int out_dtype,
+                       void* stream);
+
 /* General form. op(A) is M x K, op(B) is K x N:
  *   trans_a = 0: A stored [M,K] row-major (lda >= K); 1: A stored [K,M] row-major (lda >= M)
  *   trans_b = 0: B stored [K,N] row-major (ldb >= N); 1: B stored [N,K] row-major (ldb >= K)
@@ -222,7 +232,9 @@ int tfb_linear_backward_presplit(const float* X_hi, const float* X_lo, int64_t l
 int64_t tfb_conv_out_dim(int64_t in, int64_t k, int64_t stride, int64_t pad, int64_t dilation);
 
 /* out[N,Cout,outH,outW] = conv2d(x[N,Cin,H,W], w[Cout,Cin,kH,kW]) (+ bias[Cout]) (then ReLU if
- * relu != 0), NCHW, FP32. The producers of the GEMM kernel evaluate the im2col index map on the
+ * relu != 0), NCHW. dtype is the type of x, w and out (FP32, FP16 or BF16, the reference launchers'
+ * dtype surface: cuda/kernels/im2col.cu:124-157); bias is FP32; accumulation is FP32 and 16-bit
+ * results are rounded once (16-bit tensors are widened and run through the FP32 kernels). The producers of the GEMM kernel evaluate the im2col index map on the
  * fly; the bias is added in the epilogue. ref: nn::Conv2d::forward, nn/Conv2d.cpp:77-138
  * (launch_im2col cuda/kernels/im2col.cu:58-99 + per-sample launch_gemm_tiled_16x16 +
  * launch_bias_add cuda/kernels/bias_add.cu:49-58). */
@@ -232,7 +244,8 @@ int tfb_conv2d_forward(const void* x, const void* w, const float* bias, void* ou
                        int dtype, void* stream);
 
 /* grad_input[N,Cin,H,W], grad_weight[Cout,Cin,kH,kW] and grad_bias[Cout] for the upstream gradient
- * grad_out[N,Cout,outH,outW]; any output may be NULL. grad_input is computed in gather form (no
+ * grad_out[N,Cout,outH,outW]; any output may be NULL. dtype as in tfb_conv2d_forward (grad_bias is
+ * always FP32). grad_input is computed in gather form (no
  * atomics, fixed summation order); grad_weight is a split-K product over (sample, position) with a
  * second-stage reduction in fixed order, and the bias gradient comes out of the same product.
  * Uses library-owned scratch memory. ref: nn::Conv2d::backward, nn/Conv2d.cpp:140-260
@@ -300,6 +313,7 @@ int tfb_mlp_segment(const tfb_mlp* m, int layer, int64_t* weight_offset, int64_t
 #define TFB_MLP_REDUCED_GRADS 4
 #define TFB_MLP_ACTIVATION 5
 #define TFB_MLP_REGION 6
+#define TFB_MLP_INPUT_GRAD 7   /* gradient with respect to the input of layer `layer` >= 1, [rows, dims[layer]] */
 int tfb_mlp_buffer(tfb_mlp* m, int which, int layer, void** ptr_out);
 
 /* This rank's share of the full-batch gradient for its `rows` rows of a global batch of global_rows
@@ -359,6 +373,44 @@ int tfb_mlp_connect_local(tfb_mlp* const* ms, int world);
  * GPU), as ONE cooperative launch in which every rank's CTAs are resident together — separate launches
  * that wait for each other on one GPU have no such guarantee. Handle r must be rank r of `world`. */
 int tfb_mlp_exchange_update_one_device(tfb_mlp* const* ms, int world, float lr, float momentum, void* stream);
+
+/* ---- summing small FP32 buffers across GPUs through peer memory ------------------------------- */
+
+/* A member of a group of up to 8 ranks that add FP32 buffers of at most capacity_floats elements: one
+ * kernel per rank over NVLink peer memory (flag barrier, rank r adds slice r of all contributions in
+ * rank order — a fixed order — and stores it to every rank, flag barrier). Made for the gradient
+ * exchange of batch-sharded layers whose gradient is small, where a library collective is pure latency.
+ * The member belongs to the device current at creation. Each rank writes its contribution into the
+ * `in` buffer and reads the sum from the `out` buffer (tfb_peer_group_buffers). Connecting the ranks
+ * works as for tfb_mlp: IPC handles (one process per GPU) or already mapped regions. Waits are bounded
+ * (default 2 s; device error 107 when a peer does not arrive).
+ * ref: no counterpart (the reference is single-device, cuda/CudaContext.cpp:57-60). */
+typedef struct tfb_peer_group tfb_peer_group;
+int tfb_peer_group_create(int64_t capacity_floats, tfb_peer_group** out);
+int tfb_peer_group_destroy(tfb_peer_group* g);
+int tfb_peer_group_buffers(tfb_peer_group* g, float** in_out, float** out_out, void** region_out);
+int tfb_peer_group_set_wait_limit(tfb_peer_group* g, int64_t nanoseconds);
+int tfb_peer_group_ipc_handle(tfb_peer_group* g, void* handle_out);   /* tfb_mlp_ipc_handle_bytes() bytes */
+int tfb_peer_group_connect_ipc(tfb_peer_group* g, int rank, int world, const void* handles);
+int tfb_peer_group_connect_ptrs(tfb_peer_group* g, int rank, int world, void* const* regions);
+/* out[0..n) on every rank = sum over ranks of in[0..n). Every rank calls it once per exchange. */
+int tfb_peer_allreduce_sum(tfb_peer_group* g, int64_t n, void* stream);
+/* The same for a group whose members all live on the current device (ranks emulated on one GPU), as
+ * one cooperative launch; member r must be rank r of `world`. */
+int tfb_peer_allreduce_sum_one_device(tfb_peer_group* const* gs, int world, int64_t n, void* stream);
+
+/* Backward of a convolution whose BATCH is sharded over the ranks of a group (FP32): grad_input for
+ * this rank's N_local samples, and this rank's share of grad_weight and grad_bias written into the
+ * group's `in` buffer — grad_weight at offset 0, grad_bias at offset round_up(Cout·Cin·kH·kW, 4) —
+ * followed (allreduce != 0) by tfb_peer_allreduce_sum, after which `out` holds the full-batch weight
+ * and bias gradients on every rank in the same layout. The forward pass of a batch shard is
+ * tfb_conv2d_forward on the local samples; it needs no exchange.
+ * ref: nn::Conv2d::backward, nn/Conv2d.cpp:140-260 (its per-sample accumulation of grad_weight,
+ * :215-243, is the sum this exchange completes across ranks). */
+int tfb_conv2d_backward_sharded(tfb_peer_group* g, const void* x, const void* w, const void* grad_out, void* grad_input,
+                                int64_t N_local, int64_t Cin, int64_t H, int64_t W, int64_t Cout, int64_t kH, int64_t kW,
+                                int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w, int64_t dil_h,
+                                int64_t dil_w, int allreduce, void* stream);
 
 /* ---- device-side pieces of the autograd walk (FP32, n elements, any alignment) ---------- */
 

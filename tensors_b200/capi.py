@@ -38,6 +38,7 @@ PROTOTYPES = {
     "tfb_inject_device_status": (_i32, [_i32, _i32]),
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tfb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tfb_matmul_batched": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_gemm_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
                            _vp, _i32, _vp]),
     "tfb_split_tf32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),
@@ -78,6 +79,17 @@ PROTOTYPES = {
     "tfb_mlp_connect_local": (_i32, [ctypes.POINTER(ctypes.c_void_p), _i32]),
     "tfb_mlp_exchange_update_one_device": (_i32, [ctypes.POINTER(ctypes.c_void_p), _i32, ctypes.c_float,
                                                    ctypes.c_float, _vp]),
+    "tfb_peer_group_create": (_i32, [_i64, ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_peer_group_destroy": (_i32, [_vp]),
+    "tfb_peer_group_buffers": (_i32, [_vp, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                      ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_peer_group_set_wait_limit": (_i32, [_vp, _i64]),
+    "tfb_peer_group_ipc_handle": (_i32, [_vp, _vp]),
+    "tfb_peer_group_connect_ipc": (_i32, [_vp, _i32, _i32, _vp]),
+    "tfb_peer_group_connect_ptrs": (_i32, [_vp, _i32, _i32, ctypes.POINTER(ctypes.c_void_p)]),
+    "tfb_peer_allreduce_sum": (_i32, [_vp, _i64, _vp]),
+    "tfb_peer_allreduce_sum_one_device": (_i32, [ctypes.POINTER(ctypes.c_void_p), _i32, _i64, _vp]),
+    "tfb_conv2d_backward_sharded": (_i32, [_vp, _vp, _vp, _vp, _vp] + [_i64] * 13 + [_i32, _vp]),
     "tfb_fill": (_i32, [_vp, _i64, ctypes.c_float, _vp]),
     "tfb_relu_forward": (_i32, [_vp, _vp, _i64, _vp]),
     "tfb_relu_backward": (_i32, [_vp, _vp, _vp, _i64, _vp]),

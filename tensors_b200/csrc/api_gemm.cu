@@ -37,6 +37,28 @@ int tfb_matmul(const void* A, const void* B, void* C, int64_t M, int64_t N, int6
     return tfb_gemm_ex(A, B, C, M, N, K, K, N, N, 0, 0, in_dtype, out_dtype, nullptr, TFB_EPI_NONE, stream);
 }
 
+int tfb_matmul_batched(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N, int64_t K,
+                       int64_t stride_a, int64_t stride_b, int64_t stride_c, int in_dtype, int out_dtype, void* stream) {
+    if (batch < 0 || M < 0 || N < 0 || K < 0 || stride_a < 0 || stride_b < 0 || stride_c < 0)
+        return fail(TFB_ERR_INVALID_ARG, "matmul_batched: negative extent or stride");
+    if (!known_dtype(in_dtype) || !known_dtype(out_dtype))
+        return fail(TFB_ERR_UNSUPPORTED, "matmul_batched: unknown dtype (in %d, out %d)", in_dtype, out_dtype);
+    if (batch == 0 || M == 0 || N == 0) return TFB_OK;
+    if (A == nullptr || B == nullptr || C == nullptr) return fail(TFB_ERR_INVALID_ARG, "matmul_batched: null pointer");
+    if (batch > 1 && stride_c < M * N) return fail(TFB_ERR_INVALID_ARG, "matmul_batched: output matrices overlap");
+    const size_t ei = dtype_size(in_dtype), eo = dtype_size(out_dtype);
+    // A shared right-hand side under densely stacked left-hand sides is one tall product.
+    if (stride_b == 0 && stride_a == M * K && stride_c == M * N)
+        return tfb_matmul(A, B, C, batch * M, N, K, in_dtype, out_dtype, stream);
+    for (int64_t b = 0; b < batch; ++b) {
+        int rc = tfb_matmul(static_cast<const uint8_t*>(A) + (size_t)(b * stride_a) * ei,
+                            static_cast<const uint8_t*>(B) + (size_t)(b * stride_b) * ei,
+                            static_cast<uint8_t*>(C) + (size_t)(b * stride_c) * eo, M, N, K, in_dtype, out_dtype, stream);
+        if (rc != TFB_OK) return rc;
+    }
+    return TFB_OK;
+}
+
 int tfb_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int dtype,
              void* stream) {
     // Mirrors the reference launchers: nothing happens for empty problems or unknown dtypes.

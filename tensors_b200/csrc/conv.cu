@@ -2,6 +2,10 @@
 // and the extern "C" entry points of nn::Conv2d forward / backward.
 #include <cstring>
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <vector>
+
 #include "conv_kernel.cuh"
 #include "internal.hpp"
 
@@ -385,6 +389,102 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
 
 }  // namespace tfb
 
+namespace {
+
+// Float16 / BFloat16 tensors. The reference's launchers take all three dtypes for every convolution
+// kernel with FP32 accumulation and a result of the input type (cuda/kernels/im2col.cu:124-157,
+// cuda/kernels/gemm.cu:280-299). Here 16-bit tensors are widened to FP32 (exact), run through the
+// same FP32 kernels (FP32 accumulation; no 16-bit rounding between the im2col and GEMM stages because
+// those stages do not exist) and the results are rounded to the tensor type once.
+template <typename T>
+__global__ void widen16_kernel(const T* __restrict__ src, float* __restrict__ dst, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = static_cast<float>(src[i]);
+}
+template <typename T>
+__global__ void narrow16_kernel(const float* __restrict__ src, T* __restrict__ dst, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = static_cast<T>(src[i]);
+}
+
+// Stream-ordered FP32 staging buffers of one call (separate from the library's scratch buffer, which
+// the FP32 kernels underneath use themselves).
+struct Staging {
+    cudaStream_t stream;
+    std::vector<void*> ptrs;
+    explicit Staging(cudaStream_t s) : stream(s) {}
+    int make(float** out, int64_t n) {
+        *out = nullptr;
+        if (n <= 0) n = 1;
+        TFB_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(out), (size_t)n * 4, stream));
+        ptrs.push_back(*out);
+        return TFB_OK;
+    }
+    ~Staging() {
+        for (void* p : ptrs) (void)cudaFreeAsync(p, stream);
+        (void)cudaGetLastError();
+    }
+};
+
+int grid_1d(int64_t n) {
+    int64_t g = (n + 255) / 256;
+    if (g > 148 * 16) g = 148 * 16;
+    return (int)(g < 1 ? 1 : g);
+}
+
+int widen(const void* src, float* dst, int64_t n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return TFB_OK;
+    if (dtype == TFB_DTYPE_BF16)
+        widen16_kernel<__nv_bfloat16><<<grid_1d(n), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), dst, n);
+    else
+        widen16_kernel<__half><<<grid_1d(n), 256, 0, stream>>>(static_cast<const __half*>(src), dst, n);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+int narrow(const float* src, void* dst, int64_t n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return TFB_OK;
+    if (dtype == TFB_DTYPE_BF16)
+        narrow16_kernel<__nv_bfloat16><<<grid_1d(n), 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+    else
+        narrow16_kernel<__half><<<grid_1d(n), 256, 0, stream>>>(src, static_cast<__half*>(dst), n);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
+int conv2d_forward_16(const void* x, const void* w, const float* bias, void* out, const tfb::ConvShape& s, bool relu,
+                      int dtype, cudaStream_t stream) {
+    const int64_t nx = s.N * s.Cin * s.H * s.W, nw = s.Cout * s.Cin * s.kH * s.kW, ny = s.N * s.Cout * s.outH * s.outW;
+    Staging st(stream);
+    float *xf, *wf, *yf;
+    int rc;
+    if ((rc = st.make(&xf, nx)) != TFB_OK || (rc = st.make(&wf, nw)) != TFB_OK || (rc = st.make(&yf, ny)) != TFB_OK) return rc;
+    if ((rc = widen(x, xf, nx, dtype, stream)) != TFB_OK || (rc = widen(w, wf, nw, dtype, stream)) != TFB_OK) return rc;
+    rc = tfb::conv2d_forward(xf, wf, bias, yf, s, relu, stream);
+    if (rc != TFB_OK) return rc;
+    return narrow(yf, out, ny, dtype, stream);
+}
+
+int conv2d_backward_16(const void* x, const void* w, const void* dY, void* dX, void* dW, float* db,
+                       const tfb::ConvShape& s, int dtype, cudaStream_t stream) {
+    const int64_t nx = s.N * s.Cin * s.H * s.W, nw = s.Cout * s.Cin * s.kH * s.kW, ny = s.N * s.Cout * s.outH * s.outW;
+    Staging st(stream);
+    float *xf = nullptr, *wf = nullptr, *gf = nullptr, *dxf = nullptr, *dwf = nullptr;
+    int rc;
+    if ((rc = st.make(&gf, ny)) != TFB_OK || (rc = widen(dY, gf, ny, dtype, stream)) != TFB_OK) return rc;
+    if (x != nullptr && ((rc = st.make(&xf, nx)) != TFB_OK || (rc = widen(x, xf, nx, dtype, stream)) != TFB_OK)) return rc;
+    if (w != nullptr && ((rc = st.make(&wf, nw)) != TFB_OK || (rc = widen(w, wf, nw, dtype, stream)) != TFB_OK)) return rc;
+    if (dX != nullptr && (rc = st.make(&dxf, nx)) != TFB_OK) return rc;
+    if (dW != nullptr && (rc = st.make(&dwf, nw)) != TFB_OK) return rc;
+    rc = tfb::conv2d_backward(xf, wf, gf, dxf, dwf, db, s, stream);
+    if (rc != TFB_OK) return rc;
+    if (dX != nullptr && (rc = narrow(dxf, dX, nx, dtype, stream)) != TFB_OK) return rc;
+    if (dW != nullptr && (rc = narrow(dwf, dW, nw, dtype, stream)) != TFB_OK) return rc;
+    return TFB_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
 using tfb::fail;
@@ -407,11 +507,16 @@ int tfb_conv2d_forward(const void* x, const void* w, const float* bias, void* ou
                        int64_t H, int64_t W, int64_t Cout, int64_t kH, int64_t kW, int64_t stride_h,
                        int64_t stride_w, int64_t pad_h, int64_t pad_w, int64_t dil_h, int64_t dil_w, int relu,
                        int dtype, void* stream) {
-    if (dtype != TFB_DTYPE_F32) return fail(TFB_ERR_UNSUPPORTED, "conv2d_forward: only F32 tensors are supported");
+    if (tfb::dtype_size(dtype) == 0) return fail(TFB_ERR_UNSUPPORTED, "conv2d_forward: unknown dtype %d", dtype);
     if (x == nullptr || w == nullptr || out == nullptr) return fail(TFB_ERR_INVALID_ARG, "conv2d_forward: null pointer");
     tfb::ConvShape s;
     int rc = make_shape(s, N, Cin, H, W, Cout, kH, kW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w);
     if (rc != TFB_OK) return rc;
+    if (dtype != TFB_DTYPE_F32) {
+        rc = tfb::check_shape(s);
+        if (rc != TFB_OK) return rc;
+        return conv2d_forward_16(x, w, bias, out, s, relu != 0, dtype, static_cast<cudaStream_t>(stream));
+    }
     return tfb::conv2d_forward(static_cast<const float*>(x), static_cast<const float*>(w), bias,
                                static_cast<float*>(out), s, relu != 0, static_cast<cudaStream_t>(stream));
 }
@@ -420,7 +525,7 @@ int tfb_conv2d_backward(const void* x, const void* w, const void* grad_out, void
                         float* grad_bias, int64_t N, int64_t Cin, int64_t H, int64_t W, int64_t Cout, int64_t kH,
                         int64_t kW, int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w,
                         int64_t dil_h, int64_t dil_w, int dtype, void* stream) {
-    if (dtype != TFB_DTYPE_F32) return fail(TFB_ERR_UNSUPPORTED, "conv2d_backward: only F32 tensors are supported");
+    if (tfb::dtype_size(dtype) == 0) return fail(TFB_ERR_UNSUPPORTED, "conv2d_backward: unknown dtype %d", dtype);
     if (grad_out == nullptr) return fail(TFB_ERR_INVALID_ARG, "conv2d_backward: null upstream gradient");
     if (grad_input != nullptr && w == nullptr) return fail(TFB_ERR_INVALID_ARG, "conv2d_backward: grad_input needs the weights");
     if ((grad_weight != nullptr || grad_bias != nullptr) && x == nullptr)
@@ -428,6 +533,12 @@ int tfb_conv2d_backward(const void* x, const void* w, const void* grad_out, void
     tfb::ConvShape s;
     int rc = make_shape(s, N, Cin, H, W, Cout, kH, kW, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w);
     if (rc != TFB_OK) return rc;
+    if (dtype != TFB_DTYPE_F32) {
+        rc = tfb::check_shape(s);
+        if (rc != TFB_OK) return rc;
+        return conv2d_backward_16(x, w, grad_out, grad_input, grad_weight, grad_bias, s, dtype,
+                                  static_cast<cudaStream_t>(stream));
+    }
     return tfb::conv2d_backward(static_cast<const float*>(x), static_cast<const float*>(w),
                                 static_cast<const float*>(grad_out), static_cast<float*>(grad_input),
                                 static_cast<float*>(grad_weight), grad_bias, s, static_cast<cudaStream_t>(stream));

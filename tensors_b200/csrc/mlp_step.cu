@@ -31,14 +31,12 @@
 #include <vector>
 
 #include "internal.hpp"
+#include "peer_sync.cuh"
 #include "ptx.cuh"
 
 namespace tfb {
 
-constexpr int kMaxWorld = 8;          // ranks of one exchange group (the GPUs of one NVSwitch box)
-constexpr int kMaxExchangeCtas = 256; // flag rows reserved per region
 constexpr int kExchangeThreads = 512;
-constexpr int kDevTimeoutExchange = 107;   // a rank gave up waiting for a peer's flag
 
 namespace {
 
@@ -59,45 +57,6 @@ struct DpParams {
     float lr, mu;
     unsigned long long wait_ns;
 };
-
-// Flag area of a region: epoch[kMaxExchangeCtas], then two barriers of [kMaxExchangeCtas][kMaxWorld] words.
-constexpr size_t kFlagBytes = sizeof(uint32_t) * (kMaxExchangeCtas + 2 * kMaxExchangeCtas * kMaxWorld);
-
-__device__ __forceinline__ uint32_t* flag_word(uint8_t* region, long long flags_off, int barrier, int cta, int src) {
-    return reinterpret_cast<uint32_t*>(region + flags_off) + kMaxExchangeCtas +
-           (barrier * kMaxExchangeCtas + cta) * kMaxWorld + src;
-}
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// Loads of data another GPU wrote: served by the owning GPU's L2, never by this SM's L1.
-__device__ __forceinline__ float4 ld_peer(const float4* p) {
-    float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_peer(float4* p, const float4& v) {
-    asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
-                 ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
-}
-
-// Waits until *flag has reached `epoch` (wrap-safe) or the wall-clock limit runs out.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long limit_ns) {
-    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t polls = 0;
-    while (true) {
-        if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-        if (((++polls) & 15u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
-    }
-}
 
 // WORLD > 0: compile-time group size (all loads of one vector are issued before the first add);
 // U vectors per thread and iteration keep U * WORLD 16-byte loads in flight per thread.
@@ -569,6 +528,10 @@ int tfb_mlp_buffer(tfb_mlp* m, int which, int layer, void** ptr_out) {
         *ptr_out = m->act[(size_t)layer + 1];
         break;
     case TFB_MLP_REGION: *ptr_out = m->region; break;
+    case TFB_MLP_INPUT_GRAD:
+        if (layer < 1 || layer >= m->L) return fail(TFB_ERR_INVALID_ARG, "mlp_buffer: layer %d has no input gradient", layer);
+        *ptr_out = m->dx[(size_t)layer];
+        break;
     default: return fail(TFB_ERR_INVALID_ARG, "mlp_buffer: unknown buffer %d", which);
     }
     return TFB_OK;

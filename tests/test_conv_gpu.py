@@ -264,7 +264,7 @@ def test_config3_full_size_properties_and_sampled_oracle(oracle):
 def test_conv_argument_errors():
     t = torch.zeros(16, device="cuda")
     args = [ptr(t), ptr(t), None, ptr(t), 1, 1, 2, 2, 1, 1, 1, 1, 1, 0, 0, 1, 1, 0]
-    assert lib.tfb_conv2d_forward(*args, capi.DTYPE_BF16, stream_ptr()) == -2
+    assert lib.tfb_conv2d_forward(*args, 3, stream_ptr()) == -2   # Int32: not a dtype of this path
     bad = list(args)
     bad[11] = 0  # stride_h
     assert lib.tfb_conv2d_forward(*bad, capi.DTYPE_F32, stream_ptr()) == -1
@@ -281,3 +281,33 @@ def test_empty_batch(feed):
                                        stream_ptr()))
     assert_device_ok()
     assert float(gw.abs().sum()) == 0.0 and float(gb.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_BF16, capi.DTYPE_F16])
+@pytest.mark.parametrize("case", [(4, 16, 12, 12, 32, 3, (1, 1), (1, 1)), (2, 3, 17, 15, 8, 3, (2, 1), (1, 0)),
+                                  (3, 64, 16, 16, 64, 3, (1, 1), (1, 1))])
+def test_16bit_tensors_forward_and_backward(oracle, dtype, case):
+    # The reference launchers' dtype surface (cuda/kernels/im2col.cu:124-157): tensors of the 16-bit type,
+    # FP32 accumulation, results rounded to the tensor type. Oracle on the rounded inputs, 1e-2 budget.
+    N, C, H, W, Cout, k, stride, pad = case
+    tdt = torch.bfloat16 if dtype == capi.DTYPE_BF16 else torch.float16
+    rnd = lambda a: torch.from_numpy(a).to(tdt).float().numpy()
+    x, w = rnd(refdata.normal(1, (N, C, H, W))), rnd(refdata.conv_weight(C, Cout, k))
+    b = refdata.normal(2, (Cout,)) * np.float32(0.1)
+    oH, oW = out_dim(H, k, stride[0], pad[0], 1), out_dim(W, k, stride[1], pad[1], 1)
+    g = rnd(refdata.normal(3, (N, Cout, oH, oW)))
+    X, Wt, G, B = dev(x, tdt), dev(w, tdt), dev(g, tdt), dev(b)
+    y = torch.full((N, Cout, oH, oW), float("nan"), device="cuda", dtype=tdt)
+    args = (N, C, H, W, Cout, k, k, stride[0], stride[1], pad[0], pad[1], 1, 1)
+    capi.check(lib.tfb_conv2d_forward(ptr(X), ptr(Wt), ptr(B), ptr(y), *args, 0, dtype, stream_ptr()))
+    gi = torch.full(x.shape, float("nan"), device="cuda", dtype=tdt)
+    gw = torch.full(w.shape, float("nan"), device="cuda", dtype=tdt)
+    gb = torch.full((Cout,), float("nan"), device="cuda")
+    capi.check(lib.tfb_conv2d_backward(ptr(X), ptr(Wt), ptr(G), ptr(gi), ptr(gw), ptr(gb), *args, dtype, stream_ptr()))
+    assert_device_ok()
+    tol = 1e-2
+    assert rel_err(y.float().cpu().numpy(), oracle.conv2d_forward(x, w, b, stride, pad, (1, 1))) < tol
+    oi, ow, ob = oracle.conv2d_backward(x, w, g, stride, pad, (1, 1))
+    assert rel_err(gi.float().cpu().numpy(), oi) < tol
+    assert rel_err(gw.float().cpu().numpy(), ow) < tol
+    assert rel_err(gb.cpu().numpy(), ob) < tol

@@ -161,3 +161,105 @@ def test_two_process_group_peer_exchange_equals_nccl(tmp_path):
     assert np.array_equal(r0["nccl"], r1["nccl"])
     assert np.array_equal(r0["peer"], r0["nccl"])
     assert r0["losses"][0] == r0["losses"][1] == r1["losses"][0]
+
+
+# ---- tfb_peer_group: small all-reduce through peer memory, and the batch-sharded convolution ---------
+def make_peer_groups(world, capacity):
+    from tensors_b200.peer import PeerGroup
+    gs = [PeerGroup(capacity) for _ in range(world)]
+    regions = (ctypes.c_void_p * world)(*[g.region for g in gs])
+    for r, g in enumerate(gs):
+        capi.check(lib.tfb_peer_group_connect_ptrs(g.handle, r, world, regions))
+    handles = (ctypes.c_void_p * world)(*[g.handle.value for g in gs])
+    return gs, handles
+
+
+@pytest.mark.parametrize("world,n", [(2, 1000), (3, 7), (4, 295040), (8, 1863690)])
+def test_peer_allreduce_emulated_group_bit_exact(world, n):
+    gs, handles = make_peer_groups(world, n)
+    for rep in range(2):   # twice: the flags and the step counter carry over
+        contrib = [refdata.normal(10 * rep + r, (n,)) for r in range(world)]
+        for g, c in zip(gs, contrib):
+            g.inp[:n].copy_(torch.from_numpy(c))
+            g.out.fill_(float("nan"))
+        capi.check(lib.tfb_peer_allreduce_sum_one_device(handles, world, n, stream_ptr()))
+        assert_device_ok()
+        want = contrib[0].copy()
+        for c in contrib[1:]:
+            want = (want + c).astype(np.float32)
+        for r, g in enumerate(gs):
+            assert np.array_equal(g.out[:n].cpu().numpy(), want), (rep, r)
+
+
+def test_batch_sharded_conv_backward_sums_to_the_full_batch(oracle):
+    # 4 ranks x 2 samples: each rank's weight / bias gradient share lands in its contribution buffer, the
+    # peer all-reduce completes the sum over the batch (the sum nn/Conv2d.cpp:215-243 runs over samples)
+    world, n_local = 4, 2
+    N, Cin, H, W, Cout, k = world * n_local, 16, 12, 12, 32, 3
+    x, w = refdata.normal(1, (N, Cin, H, W)), refdata.conv_weight(Cin, Cout, k)
+    g = refdata.normal(3, (N, Cout, H, W))
+    nw = Cout * Cin * k * k
+    nw4 = (nw + 3) // 4 * 4
+    gs, handles = make_peer_groups(world, nw4 + Cout)
+    X, Wt, G = dev(x), dev(w), dev(g)
+    gi = torch.full(x.shape, float("nan"), device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    for r, grp in enumerate(gs):
+        sl = slice(r * n_local, (r + 1) * n_local)
+        capi.check(lib.tfb_conv2d_backward_sharded(grp.handle, p(X[sl]), p(Wt), p(G[sl]), p(gi[sl]), n_local, Cin, H, W, Cout,
+                                                   k, k, 1, 1, 1, 1, 1, 1, 0, stream_ptr()))
+    capi.check(lib.tfb_peer_allreduce_sum_one_device(handles, world, nw4 + Cout, stream_ptr()))
+    assert_device_ok()
+    oi, ow, ob = oracle.conv2d_backward(x, w, g, (1, 1), (1, 1), (1, 1))
+    for grp in gs:
+        out = grp.out.cpu().numpy()
+        assert np.linalg.norm(out[:nw] - ow.ravel()) / np.linalg.norm(ow) < 1e-5
+        assert np.linalg.norm(out[nw4:nw4 + Cout] - ob) / np.linalg.norm(ob) < 1e-5
+        assert np.array_equal(out, gs[0].out.cpu().numpy())
+    assert np.linalg.norm(gi.cpu().numpy() - oi) / np.linalg.norm(oi) < 1e-5
+
+
+def _two_process_conv_worker(rank, world, port, out_dir):
+    for p in (ROOT, os.path.join(ROOT, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from tensors_b200.peer import PeerGroup
+    N, Cin, H, W, Cout, k = 8, 64, 32, 32, 128, 3
+    n_local = N // world
+    x, w, g = refdata.normal(1, (N, Cin, H, W)), refdata.conv_weight(Cin, Cout, k), refdata.normal(3, (N, Cout, H, W))
+    nw4 = Cout * Cin * k * k
+    grp = PeerGroup(nw4 + Cout)
+    grp.connect()
+    sl = slice(rank * n_local, (rank + 1) * n_local)
+    X, Wt, G = dev(x[sl]), dev(w), dev(g[sl])
+    gi = torch.empty_like(X)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    for _ in range(3):
+        capi.check(lib.tfb_conv2d_backward_sharded(grp.handle, p(X), p(Wt), p(G), p(gi), n_local, Cin, H, W, Cout, k, k,
+                                                   1, 1, 1, 1, 1, 1, 1, stream_ptr()))
+    torch.cuda.synchronize()
+    mine = grp.inp.clone()
+    both = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(both, mine)
+    want = both[0].clone()
+    for t in both[1:]:
+        want += t
+    np.savez(os.path.join(out_dir, f"conv{rank}.npz"), out=grp.out.cpu().numpy(), want=want.cpu().numpy(),
+             status=np.array([capi.device_status()]))
+    grp.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_process_batch_sharded_conv_backward(tmp_path):
+    # the layer-2 convolution of the CIFAR-shaped configuration, batch split over two processes / GPUs
+    import torch.multiprocessing as mp
+    mp.spawn(_two_process_conv_worker, args=(2, 29543, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "conv0.npz"), np.load(tmp_path / "conv1.npz")
+    assert r0["status"][0] == 0 and r1["status"][0] == 0
+    assert np.array_equal(r0["out"], r1["out"])
+    assert np.array_equal(r0["out"], r0["want"])   # g0 + g1 in rank order

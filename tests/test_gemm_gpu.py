@@ -350,3 +350,36 @@ def test_narrow_products_against_oracle(oracle, case):
     for got in (C.cpu().numpy(), C2.cpu().numpy()):
         assert not np.isnan(got).any()
         assert rel_err(got, want) < FP32_TOL
+
+
+@pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
+def test_batched_matmul_against_oracle(oracle, in_dtype):
+    # N-D operands: [batch, M, K] x [batch, K, N], a shared right-hand side (stride 0: one tall product
+    # under the hood) and a padded batch stride; every matrix against the oracle's 2-D loop
+    tdt = torch.float32 if in_dtype == capi.DTYPE_F32 else torch.bfloat16
+    tol = FP32_TOL if in_dtype == capi.DTYPE_F32 else BF16_TOL
+    batch, M, N, K = 5, 96, 80, 112
+    a = dev(refdata.uniform(1, (batch, M, K)), tdt)
+    b = dev(refdata.uniform(2, (batch, K, N)), tdt)
+    ah, bh = a.float().cpu().numpy(), b.float().cpu().numpy()
+    C = torch.full((batch, M, N), float("nan"), device="cuda")
+    capi.check(lib.tfb_matmul_batched(ptr(a), ptr(b), ptr(C), batch, M, N, K, M * K, K * N, M * N, in_dtype,
+                                      capi.DTYPE_F32, stream_ptr()))
+    assert_device_ok()
+    for i in range(batch):
+        assert rel_err(C[i].cpu().numpy(), oracle.matmul(ah[i], bh[i])) < tol, i
+    C.fill_(float("nan"))
+    capi.check(lib.tfb_matmul_batched(ptr(a), ptr(b), ptr(C), batch, M, N, K, M * K, 0, M * N, in_dtype,
+                                      capi.DTYPE_F32, stream_ptr()))
+    assert_device_ok()
+    for i in range(batch):
+        assert rel_err(C[i].cpu().numpy(), oracle.matmul(ah[i], bh[0])) < tol, i
+    pad = torch.full((batch, M + 3, N), float("nan"), device="cuda")   # output matrices (M + 3) * N apart
+    capi.check(lib.tfb_matmul_batched(ptr(a), ptr(b), ptr(pad), batch, M, N, K, M * K, K * N, (M + 3) * N, in_dtype,
+                                      capi.DTYPE_F32, stream_ptr()))
+    assert_device_ok()
+    assert rel_err(pad[3, :M].cpu().numpy(), oracle.matmul(ah[3], bh[3])) < tol
+    assert torch.isnan(pad[:, M:]).all()
+    assert lib.tfb_matmul_batched(ptr(a), ptr(b), ptr(C), batch, M, N, K, M * K, K * N, M * N - 1, in_dtype,
+                                  capi.DTYPE_F32, stream_ptr()) == -1   # overlapping outputs
+    assert lib.tfb_matmul_batched(ptr(a), ptr(b), ptr(C), 0, M, N, K, 0, 0, 0, in_dtype, capi.DTYPE_F32, stream_ptr()) == 0
