@@ -159,6 +159,11 @@ int tfb_gemm_presplit(const float* A_hi, const float* A_lo, const float* B_hi, c
  * the Tensor::to(Device) round trip a CUDA caller would add (tensor/Tensor.hpp:78-84). */
 int tfb_matmul_host(const void* A_host, const void* B_host, void* C_host, int64_t M, int64_t N, int64_t K,
                     int dtype, void* stream);
+/* The same with B already in DEVICE memory (ordered before the call on `stream`): several GPUs that
+ * share one B each upload a slice of it, exchange the slices over NVLink (an all-gather) and then
+ * stream their own rows of A, so that B crosses the host link once instead of once per GPU. */
+int tfb_matmul_host_b_resident(const void* A_host, const void* B_device, void* C_host, int64_t M, int64_t N,
+                               int64_t K, int dtype, void* stream);
 
 /* One large product sharded over the GPUs of this process by row panels: device devices[g] computes
  * C_panels[g][panel_rows[g], N] = A_panels[g][panel_rows[g], K] · B_replicas[g][K, N] on streams[g]

@@ -45,6 +45,7 @@ PROTOTYPES = {
     "tfb_gemm_presplit": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp,
                                  _i32, _vp]),
     "tfb_matmul_host": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
+    "tfb_matmul_host_b_resident": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tfb_matmul_row_panels": (_i32, [_i32, _ip, ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                      ctypes.POINTER(_i64), _i64, _i64, _i32, _i32, ctypes.POINTER(_vp)]),
     "tfb_matmul_f32_static_limit": (_sz, []),

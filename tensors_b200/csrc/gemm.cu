@@ -216,7 +216,8 @@ __global__ void empty_k_kernel(const GemmArgs a) {
 // C = epilogue(sum over splits, in split order, of the partial products).
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long long M, long long N,
                                      long long ld, long long split_stride, void* __restrict__ C, long long ldc,
-                                     int out_type, const float* __restrict__ bias, int bias_mode, int relu) {
+                                     int out_type, const float* __restrict__ bias, int bias_mode, int relu,
+                                     float* __restrict__ planes_hi, float* __restrict__ planes_lo) {
     pdl_wait();
     pdl_launch_dependents();
     const long long total = M * N;
@@ -231,6 +232,11 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
         if (out_type == kOutF32) static_cast<float*>(C)[r * ldc + c] = v;
         else if (out_type == kOutBF16) static_cast<__nv_bfloat16*>(C)[r * ldc + c] = __float2bfloat16_rn(v);
         else static_cast<__half*>(C)[r * ldc + c] = __float2half_rn(v);
+        if (planes_hi != nullptr) {   // leading dimension N
+            const float h = tf32_round(v);
+            planes_hi[i] = h;
+            planes_lo[i] = v - h;
+        }
     }
 }
 
@@ -541,6 +547,14 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     args.bias = c.bias; args.bias_mode = c.bias_mode; args.relu = c.relu ? 1 : 0;
     args.is_bf16 = c.in_dtype == TFB_DTYPE_BF16 ? 1 : 0;
     args.status = st->status;
+    if (c.planes_hi != nullptr || c.planes_lo != nullptr) {
+        if (!f32 || c.out_dtype != TFB_DTYPE_F32 || (c.N & 3) || c.planes_hi == nullptr || c.planes_lo == nullptr ||
+            !aligned16(c.planes_hi) || !aligned16(c.planes_lo) || c.K <= 0)
+            return fail(TFB_ERR_UNSUPPORTED, "gemm: result planes need FP32 in and out, N a multiple of 4 and aligned planes");
+        args.planes_hi = c.planes_hi;
+        args.planes_lo = c.planes_lo;
+        args.ld_planes = c.N;
+    }
 
     if (c.K <= 0) {
         // Empty contraction: the product is zero and only the epilogue remains.
@@ -575,6 +589,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
         args.split_stride = plan.rows_per_split * plan.ld_partial;
         args.out_type = kOutF32;
         args.bias = nullptr; args.bias_mode = 0; args.relu = 0;
+        args.planes_hi = nullptr; args.planes_lo = nullptr;   // the reduction kernel writes them
         args.c_tma = 1;
         rc = make_map(&maps[4], TFB_DTYPE_F32, partial, (uint64_t)c.N, (uint64_t)(plan.split_k * plan.rows_per_split),
                       (uint64_t)plan.ld_partial * 4, 32, 32);
@@ -614,7 +629,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
                       (const float*)partial, plan.split_k, (long long)c.M, (long long)c.N, (long long)plan.ld_partial,
                       (long long)(plan.rows_per_split * plan.ld_partial), c.C, (long long)c.ldc,
                       (int)(c.out_dtype == TFB_DTYPE_F32 ? kOutF32 : (c.out_dtype == TFB_DTYPE_F16 ? kOutF16 : kOutBF16)),
-                      c.bias, c.bias_mode, c.relu ? 1 : 0);
+                      c.bias, c.bias_mode, c.relu ? 1 : 0, c.planes_hi, c.planes_lo);
 }
 
 }  // namespace tfb

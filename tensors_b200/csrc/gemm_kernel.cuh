@@ -98,6 +98,11 @@ struct GemmArgs {
     int is_bf16;          // kKind16 only: 1 = bf16 operands, 0 = f16
     int c_tma;            // 1: FP32 output goes through the TMA-store path (tmC is valid)
     int* status;          // device error word (0 = ok)
+    // Optional second output of the FP32 path: the TF32 hi / lo planes of the final values (after bias and
+    // ReLU), row-major with leading dimension ld_planes, for a consumer that multiplies them next.
+    float* planes_hi;
+    float* planes_lo;
+    long long ld_planes;
     ConvGeom cv;          // only read when CONV != kConvNone
 };
 
@@ -203,6 +208,28 @@ __device__ __forceinline__ void epilogue_store32_tma(const float (&v)[32], const
         tma_store_commit();
     }
     buf_idx = (buf_idx + 1 == NBUF) ? 0 : buf_idx + 1;
+}
+
+// hi = v rounded to TF32, lo = v - hi for 32 consecutive columns of one row, written straight from
+// registers (16 bytes per store; the columns are whole vectors because N is a multiple of 4).
+__device__ __forceinline__ void epilogue_store_planes32(const float (&v)[32], const GemmArgs& args, int row, int col0) {
+    float* hi = args.planes_hi + (long long)row * args.ld_planes + col0;
+    float* lo = args.planes_lo + (long long)row * args.ld_planes + col0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (col0 + 4 * i < args.N) {
+            float h[4], l[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint32_t r;
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v[4 * i + j]));
+                h[j] = __uint_as_float(r);
+                l[j] = v[4 * i + j] - h[j];
+            }
+            reinterpret_cast<float4*>(hi)[i] = make_float4(h[0], h[1], h[2], h[3]);
+            reinterpret_cast<float4*>(lo)[i] = make_float4(l[0], l[1], l[2], l[3]);
+        }
+    }
 }
 
 __device__ __forceinline__ void tile_coords(int t, const GemmArgs& a, int& tm, int& tn) {
@@ -599,6 +626,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             epilogue_apply32(v, args, col0, row_bias);
                             if (c_tma) epilogue_store32_tma<S::STAGING_BUFS>(v, &tmC, staging, stage_buf, lane, row0, col0);
                             else epilogue_store32(v, args, row, col0);
+                            if (args.planes_hi != nullptr && row_ok) epilogue_store_planes32(v, args, row, col0);
                         }
                     }
                 }

@@ -75,8 +75,23 @@ struct EventBag {
 }  // namespace
 }  // namespace tfb
 
+namespace tfb {
+static int matmul_host_impl(const void* A_host, const void* B_host, bool b_on_device, void* C_host, int64_t M,
+                            int64_t N, int64_t K, int dtype, void* stream_v);
+}
+
 extern "C" int tfb_matmul_host(const void* A_host, const void* B_host, void* C_host, int64_t M, int64_t N,
                                int64_t K, int dtype, void* stream_v) {
+    return tfb::matmul_host_impl(A_host, B_host, false, C_host, M, N, K, dtype, stream_v);
+}
+
+extern "C" int tfb_matmul_host_b_resident(const void* A_host, const void* B_device, void* C_host, int64_t M,
+                                          int64_t N, int64_t K, int dtype, void* stream_v) {
+    return tfb::matmul_host_impl(A_host, B_device, true, C_host, M, N, K, dtype, stream_v);
+}
+
+static int tfb::matmul_host_impl(const void* A_host, const void* B_host, bool b_on_device, void* C_host, int64_t M,
+                                 int64_t N, int64_t K, int dtype, void* stream_v) {
     using namespace tfb;
     if (M < 0 || N < 0 || K < 0) return fail(TFB_ERR_INVALID_ARG, "matmul_host: negative extent");
     const size_t es = dtype_size(dtype);
@@ -114,7 +129,8 @@ extern "C" int tfb_matmul_host(const void* A_host, const void* B_host, void* C_h
     // have been enqueued) when the call returns, whichever way it returns.
     BufferBag buffers(stream);
     buffers.users = {cs->h2d, cs->d2h};
-    if ((rc = buffers.make(reinterpret_cast<void**>(&dB), (size_t)(K * N) * es)) != TFB_OK) return rc;
+    if (b_on_device) dB = static_cast<uint8_t*>(const_cast<void*>(B_host));   // already where it is needed
+    else if ((rc = buffers.make(reinterpret_cast<void**>(&dB), (size_t)(K * N) * es)) != TFB_OK) return rc;
     if (f32 && (rc = buffers.make(reinterpret_cast<void**>(&dBs), (size_t)(2 * K * ldb4) * 4)) != TFB_OK) return rc;
     for (int i = 0; i < 2; ++i) {
         if ((rc = buffers.make(reinterpret_cast<void**>(&dA[i]), (size_t)(panel * K) * es)) != TFB_OK) return rc;
@@ -128,9 +144,11 @@ extern "C" int tfb_matmul_host(const void* A_host, const void* B_host, void* C_h
     TFB_CUDA_OK(cudaStreamWaitEvent(cs->h2d, ready, 0));
     TFB_CUDA_OK(cudaStreamWaitEvent(cs->d2h, ready, 0));
 
-    TFB_CUDA_OK(cudaMemcpyAsync(dB, B_host, (size_t)(K * N) * es, cudaMemcpyHostToDevice, cs->h2d));
-    TFB_CUDA_OK(cudaEventRecord(b_loaded, cs->h2d));
-    TFB_CUDA_OK(cudaStreamWaitEvent(stream, b_loaded, 0));
+    if (!b_on_device) {
+        TFB_CUDA_OK(cudaMemcpyAsync(dB, B_host, (size_t)(K * N) * es, cudaMemcpyHostToDevice, cs->h2d));
+        TFB_CUDA_OK(cudaEventRecord(b_loaded, cs->h2d));
+        TFB_CUDA_OK(cudaStreamWaitEvent(stream, b_loaded, 0));
+    }
     if (f32) {
         rc = split_operand(reinterpret_cast<const float*>(dB), K, N, N, nullptr, dBs, dBs + K * ldb4, ldb4, stream);
         if (rc != TFB_OK) return rc;

@@ -91,6 +91,10 @@ struct GemmCall {
     // FP32 only: operands already split by gemm_split_operand (hi at ptr, lo at ptr + lo_off).
     bool a_presplit = false, b_presplit = false;
     int64_t a_lo_off = 0, b_lo_off = 0;   // elements
+    // FP32 output only, N a multiple of 4: also write the TF32 hi / lo planes of the result (after bias
+    // and ReLU) with leading dimension N, for a product that consumes this output next.
+    float* planes_hi = nullptr;
+    float* planes_lo = nullptr;
     int force_bn = 0;          // 0 = choose; else 64 / 128 / 256
     int chunk_kb = 0;          // FP32: K blocks (of 32) per TMEM accumulation chunk; 0 = default
     void* workspace = nullptr; // optional caller scratch; nullptr = library-owned

@@ -335,8 +335,13 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         const int64_t ldx = round_up(in_f, 4);
         float* xh = m->xplanes[(size_t)i];
         float* xl = xh + rows * ldx;
-        rc = split_operand(in, rows, in_f, in_f, nullptr, xh, xl, ldx, stream);
-        if (rc != TFB_OK) return rc;
+        // The planes of a hidden layer's input were written by the product that made it (its epilogue);
+        // only the batch itself, and inputs whose width is not a multiple of 4, are split here.
+        const bool planes_ready = i > 0 && (in_f & 3) == 0;
+        if (!planes_ready) {
+            rc = split_operand(in, rows, in_f, in_f, nullptr, xh, xl, ldx, stream);
+            if (rc != TFB_OK) return rc;
+        }
         xs[(size_t)i].hi = xh; xs[(size_t)i].lo = xl; xs[(size_t)i].ld = ldx;
         if (m->wplanes[(size_t)i] == nullptr) {
             ws[(size_t)i].hi = m->pplanes + m->w_off[(size_t)i];
@@ -359,6 +364,10 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         c.in_dtype = TFB_DTYPE_F32; c.out_dtype = TFB_DTYPE_F32;
         c.bias = m->params + m->b_off[(size_t)i]; c.bias_mode = 1;
         c.relu = i < L - 1;
+        if (i + 1 < L && (out_f & 3) == 0) {
+            c.planes_hi = m->xplanes[(size_t)i + 1];
+            c.planes_lo = c.planes_hi + rows * out_f;
+        }
         rc = gemm_run(c, stream);
         if (rc != TFB_OK) return rc;
     }

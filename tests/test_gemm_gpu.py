@@ -270,6 +270,13 @@ def test_matmul_on_host_buffers(oracle, in_dtype, pinned):
         want = oracle.matmul(a.float().numpy(), b.float().numpy())
         assert rel_err(c.numpy(), want) < FP32_TOL
         c.fill_(float("nan"))
+    # the same with B already on the device
+    Bd = b.cuda()
+    capi.check(lib.tfb_matmul_host_b_resident(ctypes.c_void_p(a.data_ptr()), ptr(Bd), ctypes.c_void_p(c.data_ptr()),
+                                              M, N, K, in_dtype, stream_ptr()))
+    torch.cuda.current_stream().synchronize()
+    assert_device_ok()
+    assert rel_err(c.numpy(), want) < FP32_TOL
 
 
 @pytest.mark.parametrize("in_dtype", [capi.DTYPE_F32, capi.DTYPE_BF16])
