@@ -70,6 +70,10 @@ const char* tfb_last_error_string(void);
  *   PDL             1 (default) = kernels are launched so that each may start its prologue while the one
  *                   before it on the stream is finishing (programmatic dependent launch); 0 = plain
  *                   stream order (environment: TFB_PDL)
+ *   FUSE_PLANES     which products of the MLP step also write the TF32 hi / lo planes of their result for
+ *                   the next layer instead of leaving that to a separate pass: 0 = none, 1 (default) =
+ *                   the split-K products (their reduction kernel writes the planes), 2 = all of them
+ *                   (the GEMM epilogue writes the planes too) (environment: TFB_FUSE_PLANES)
  * ref: no counterpart (the reference has one kernel per operation). */
 #define TFB_TUNE_GEMM_TILE_N 0
 #define TFB_TUNE_GEMM_PAIR 1
@@ -80,7 +84,8 @@ const char* tfb_last_error_string(void);
 #define TFB_TUNE_CONV_PAIR 6
 #define TFB_TUNE_HOST_PANEL_ROWS 7
 #define TFB_TUNE_PDL 8
-#define TFB_TUNE_COUNT 9
+#define TFB_TUNE_FUSE_PLANES 9
+#define TFB_TUNE_COUNT 10
 int tfb_set_tuning(int knob, int value);
 int tfb_get_tuning(int knob, int* value_out);
 

@@ -393,6 +393,8 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
     return p;
 }
 
+bool gemm_uses_split_k(const GemmCall& c, int sm_count) { return gemm_plan(c, sm_count).split_k > 1; }
+
 size_t gemm_workspace_bytes(const GemmCall& c, int sm_count) {
     size_t bytes = 0;
     const int64_t a_rows = c.a_kmajor ? c.M : c.K, a_cols = c.a_kmajor ? c.K : c.M;
@@ -597,6 +599,8 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     } else {
         args.split_stride = 0;
         args.c_tma = (c.out_dtype == TFB_DTYPE_F32 && aligned16(c.C) && (c.ldc & 3) == 0) ? 1 : 0;
+        if (args.planes_hi != nullptr && !args.c_tma)
+            return fail(TFB_ERR_UNSUPPORTED, "gemm: result planes need a 16-byte aligned output with ldc a multiple of 4");
         if (args.c_tma) {
             rc = make_map(&maps[4], TFB_DTYPE_F32, c.C, (uint64_t)c.N, (uint64_t)c.M, (uint64_t)c.ldc * 4, 32, 32);
             if (rc != TFB_OK) return rc;

@@ -210,26 +210,50 @@ __device__ __forceinline__ void epilogue_store32_tma(const float (&v)[32], const
     buf_idx = (buf_idx + 1 == NBUF) ? 0 : buf_idx + 1;
 }
 
-// hi = v rounded to TF32, lo = v - hi for 32 consecutive columns of one row, written straight from
-// registers (16 bytes per store; the columns are whole vectors because N is a multiple of 4).
-__device__ __forceinline__ void epilogue_store_planes32(const float (&v)[32], const GemmArgs& args, int row, int col0) {
-    float* hi = args.planes_hi + (long long)row * args.ld_planes + col0;
-    float* lo = args.planes_lo + (long long)row * args.ld_planes + col0;
+__device__ __forceinline__ float tf32_hi(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// One warp's 32 rows x 32 columns (lane = row, v = its 32 values) to a row-major FP32 matrix with whole
+// 128-byte lines per store instruction: the block is transposed through the warp's swizzled staging
+// buffer (16-byte chunk j of row r at chunk j ^ (r & 7): conflict-free both ways), then lane
+// (r & 3, chunk) stores 16 bytes of row 4k + (lane >> 3). PLANE selects what is stored: 1 = the value
+// rounded to TF32 (hi), 2 = the value minus that (lo) — computed on the way into the buffer, so no
+// second register array is needed. `m_rows` / `n_cols` clip at the matrix edge (n_cols is a multiple
+// of 4). The caller makes sure nothing else is still reading the buffer.
+template <int PLANE>
+__device__ __forceinline__ void store32x32_via_staging(const float (&v)[32], uint8_t* buf, int lane, float* dst,
+                                                        long long ld, int row0, int col0, int m_rows, int n_cols) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (col0 + 4 * i < args.N) {
-            float h[4], l[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t r;
-                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v[4 * i + j]));
-                h[j] = __uint_as_float(r);
-                l[j] = v[4 * i + j] - h[j];
-            }
-            reinterpret_cast<float4*>(hi)[i] = make_float4(h[0], h[1], h[2], h[3]);
-            reinterpret_cast<float4*>(lo)[i] = make_float4(l[0], l[1], l[2], l[3]);
-        }
+    for (int j = 0; j < 8; ++j) {
+        float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        const float4 h = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
+        if (PLANE == 1) x = h;
+        else x = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+        *reinterpret_cast<float4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = x;
     }
+    __syncwarp();
+    const int chunk = lane & 7;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int r = 4 * k + (lane >> 3);
+        const float4 x = *reinterpret_cast<const float4*>(buf + r * 128 + ((chunk ^ (r & 7)) << 4));
+        if (row0 + r < m_rows && col0 + 4 * chunk < n_cols)
+            *reinterpret_cast<float4*>(dst + (long long)(row0 + r) * ld + col0 + 4 * chunk) = x;
+    }
+    __syncwarp();
+}
+
+// The TF32 hi / lo planes of a 32 x 32 block of final values: hi = v rounded to TF32, lo = v - hi.
+__device__ __forceinline__ void epilogue_store_planes32(const float (&v)[32], const GemmArgs& args, uint8_t* staging,
+                                                         int lane, int row0, int col0) {
+    // the warp's previous TMA store may still be reading the staging buffer
+    if (lane == 0) tma_store_wait_read<0>();
+    __syncwarp();
+    store32x32_via_staging<1>(v, staging, lane, args.planes_hi, args.ld_planes, row0, col0, args.M, args.N);
+    store32x32_via_staging<2>(v, staging, lane, args.planes_lo, args.ld_planes, row0, col0, args.M, args.N);
 }
 
 __device__ __forceinline__ void tile_coords(int t, const GemmArgs& a, int& tm, int& tn) {
@@ -624,9 +648,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] = acc[c * 32 + i];
                             epilogue_apply32(v, args, col0, row_bias);
+                            // planes first (plain stores, the staging buffer is free again at once), then the
+                            // asynchronous TMA store of the values themselves
+                            if (args.planes_hi != nullptr) epilogue_store_planes32(v, args, staging, lane, row0, col0);
                             if (c_tma) epilogue_store32_tma<S::STAGING_BUFS>(v, &tmC, staging, stage_buf, lane, row0, col0);
                             else epilogue_store32(v, args, row, col0);
-                            if (args.planes_hi != nullptr && row_ok) epilogue_store_planes32(v, args, row, col0);
                         }
                     }
                 }

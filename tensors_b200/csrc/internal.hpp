@@ -101,6 +101,9 @@ struct GemmCall {
     size_t workspace_bytes = 0;
 };
 int gemm_run(const GemmCall& call, cudaStream_t stream);
+// True when gemm_run would split this call's contraction between CTAs (its epilogue then runs in the
+// reduction kernel).
+bool gemm_uses_split_k(const GemmCall& call, int sm_count);
 // Same, with the device facts (SM count, status word) supplied by the caller instead of the
 // lazily created per-device state.
 int gemm_run_on(const GemmCall& call, cudaStream_t stream, const DeviceState* st);

@@ -329,6 +329,11 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
                            stream);
     if (rc != TFB_OK) return rc;
     std::vector<SavedPlanes> xs((size_t)L), ws((size_t)L);
+    DeviceState* st = nullptr;
+    rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    const int fuse = tuning(TFB_TUNE_FUSE_PLANES);
+    bool planes_ready = false;   // did the product of the layer below already write this layer's input planes?
     for (int i = 0; i < L; ++i) {
         const int64_t in_f = m->dims[(size_t)i], out_f = m->dims[(size_t)i + 1];
         const float* in = i == 0 ? X : m->act[(size_t)i];
@@ -337,7 +342,6 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         float* xl = xh + rows * ldx;
         // The planes of a hidden layer's input were written by the product that made it (its epilogue);
         // only the batch itself, and inputs whose width is not a multiple of 4, are split here.
-        const bool planes_ready = i > 0 && (in_f & 3) == 0;
         if (!planes_ready) {
             rc = split_operand(in, rows, in_f, in_f, nullptr, xh, xl, ldx, stream);
             if (rc != TFB_OK) return rc;
@@ -364,9 +368,14 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         c.in_dtype = TFB_DTYPE_F32; c.out_dtype = TFB_DTYPE_F32;
         c.bias = m->params + m->b_off[(size_t)i]; c.bias_mode = 1;
         c.relu = i < L - 1;
-        if (i + 1 < L && (out_f & 3) == 0) {
+        // Where it costs nothing the product also writes the planes the next layer multiplies: always in
+        // the reduction kernel of a split-K product; in the GEMM epilogue only on request (measured: the
+        // longer epilogue costs the large-batch products more than the separate pass it saves).
+        planes_ready = false;
+        if (i + 1 < L && (out_f & 3) == 0 && (fuse == 2 || (fuse == 1 && gemm_uses_split_k(c, st->sm_count)))) {
             c.planes_hi = m->xplanes[(size_t)i + 1];
             c.planes_lo = c.planes_hi + rows * out_f;
+            planes_ready = true;
         }
         rc = gemm_run(c, stream);
         if (rc != TFB_OK) return rc;
