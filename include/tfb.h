@@ -112,7 +112,10 @@ int tfb_gemm(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_
 /* The CUDA branch of Tensor::matmul: same contraction, separate input and output dtypes
  * (F32 -> F32; F16/BF16 -> F32 or the input dtype). Unlike tfb_gemm it reports bad
  * arguments. ref: Tensor::matmul, tensor/Tensor.cpp:334-368; the registry slot it fills
- * sits beside register_cuda_add in cuda/CudaKernelRegistry.hpp:15-26. */
+ * sits beside register_cuda_add in cuda/CudaKernelRegistry.hpp:15-26. The slot's function type carries
+ * TWO dtypes (in, out) where the reference's launchers carry one: Tensor::matmul passes its own dtype
+ * for both (the reference's rule), a caller that wants 16-bit operands with an FP32 result passes F32 as
+ * the second. */
 int tfb_matmul(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                int in_dtype, int out_dtype, void* stream);
 
@@ -324,6 +327,7 @@ int tfb_mlp_segment(const tfb_mlp* m, int layer, int64_t* weight_offset, int64_t
 #define TFB_MLP_ACTIVATION 5
 #define TFB_MLP_REGION 6
 #define TFB_MLP_INPUT_GRAD 7   /* gradient with respect to the input of layer `layer` >= 1, [rows, dims[layer]] */
+#define TFB_MLP_EXCHANGE_TRACE 8   /* five uint64 %globaltimer stamps of the last exchange (see TRACE_EXCHANGE) */
 int tfb_mlp_buffer(tfb_mlp* m, int which, int layer, void** ptr_out);
 
 /* This rank's share of the full-batch gradient for its `rows` rows of a global batch of global_rows
@@ -360,10 +364,14 @@ int tfb_mlp_capture_step(tfb_mlp* m, const float* X, const int64_t* labels, int6
 int tfb_mlp_replay(tfb_mlp* m, void* stream);
 /* WAIT_LIMIT_NS: how long the exchange kernel waits for a peer (default 2 s). EXCHANGE_CTAS: its grid
  * (0 = choose; every rank of a group must use the same value). KEEP_REDUCED_GRADS: non-zero makes the
- * exchange also store the summed gradient of this rank's slice into REDUCED_GRADS. */
+ * exchange also store the summed gradient of this rank's slice into REDUCED_GRADS. TRACE_EXCHANGE: non-zero
+ * makes CTA 0 of the exchange kernel record nanosecond timestamps at its phase boundaries (start, after the
+ * first flag barrier, after the slice has been summed / updated / stored, after the system-scope fence,
+ * after the second barrier) into EXCHANGE_TRACE. */
 #define TFB_MLP_OPT_WAIT_LIMIT_NS 0
 #define TFB_MLP_OPT_EXCHANGE_CTAS 1
 #define TFB_MLP_OPT_KEEP_REDUCED_GRADS 2
+#define TFB_MLP_OPT_TRACE_EXCHANGE 3
 int tfb_mlp_set_option(tfb_mlp* m, int option, int64_t value);
 
 /* Forming a group of `world` <= 8 ranks (one handle per rank, same dims). The library does not own a

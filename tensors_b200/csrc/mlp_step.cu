@@ -46,6 +46,7 @@ struct DpRank {
     float* reduced;               // optional: the summed gradient of this rank's slice is also stored here
     float* loss_out;              // sum of all ranks' loss contributions
     int* status;                  // device status word of this rank's device
+    unsigned long long* trace;    // optional: CTA 0 stamps %globaltimer at the five phase boundaries
     int rank;
 };
 
@@ -152,18 +153,23 @@ dp_exchange_kernel(const __grid_constant__ DpParams p) {
     uint32_t* epoch_word = reinterpret_cast<uint32_t*>(mine + p.flags_off) + cta;
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(epoch_word) + 1u;
     const int t = threadIdx.x;
+    const bool tracing = me.trace != nullptr && cta == 0 && t == 0;
+    if (tracing) me.trace[0] = global_timer_ns();
 
     // Barrier 0: every rank's gradients (written by the kernels before this one on its stream) are complete.
     // A group of one has nobody to wait for and leaves the flags and the step counter alone.
     int ok = 1;
     if (world > 1 && t < world) {
-        st_release_sys(flag_word(me.region[t], p.flags_off, 0, cta, rank), epoch);
+        // nothing this kernel wrote is published here (the gradients were completed by the kernels before
+        // it on the stream), so the arrival is a relaxed store
+        st_relaxed_sys(flag_word(me.region[t], p.flags_off, 0, cta, rank), epoch);
         if (!wait_flag(flag_word(mine, p.flags_off, 0, cta, t), epoch, p.wait_ns)) {
             ok = 0;
             if (me.status != nullptr) atomicCAS(me.status, 0, kDevTimeoutExchange);
         }
     }
     ok = __syncthreads_and(ok);
+    if (tracing) me.trace[1] = global_timer_ns();
     if (ok) {
         if (cta == 0 && t == 0) {
             // Loss: the ranks' contributions in rank order (the slot after the gradients).
@@ -186,14 +192,19 @@ dp_exchange_kernel(const __grid_constant__ DpParams p) {
     // signalled even after a failed first barrier so that the other ranks are not kept waiting for long.
     if (world == 1) return;
     __syncthreads();
+    if (tracing) me.trace[2] = global_timer_ns();
     if (t < world) {
+        // one fence at system scope (cumulative over the CTA's stores through the barrier above: all slices
+        // this CTA stored have landed), then relaxed arrivals
         __threadfence_system();
-        st_release_sys(flag_word(me.region[t], p.flags_off, 1, cta, rank), epoch);
+        if (tracing) me.trace[3] = global_timer_ns();
+        st_relaxed_sys(flag_word(me.region[t], p.flags_off, 1, cta, rank), epoch);
         if (ok && !wait_flag(flag_word(mine, p.flags_off, 1, cta, t), epoch, p.wait_ns)) {
             if (me.status != nullptr) atomicCAS(me.status, 0, kDevTimeoutExchange);
         }
     }
     __syncthreads();
+    if (tracing) me.trace[4] = global_timer_ns();
     if (t == 0) *reinterpret_cast<volatile uint32_t*>(epoch_word) = epoch;
 }
 
@@ -220,6 +231,8 @@ struct tfb_mlp {
     float* velocity = nullptr;
     float* reduced = nullptr;
     float* loss = nullptr;
+    unsigned long long* trace = nullptr;  // 8 words behind the loss
+    bool trace_on = false;
     float* pplanes = nullptr;             // hi / lo planes of the flat parameter buffer (2 x numel)
     std::vector<float*> wplanes;          // per layer, only where in_features is not a multiple of 4
     std::vector<float*> act;              // act[i + 1] = output of layer i
@@ -274,6 +287,7 @@ void fill_rank(const tfb_mlp* m, DpRank& r, int* status) {
     r.reduced = m->keep_reduced ? m->reduced : nullptr;
     r.loss_out = m->loss;
     r.status = status;
+    r.trace = m->trace_on ? m->trace : nullptr;
     r.rank = m->rank;
 }
 
@@ -481,6 +495,7 @@ int tfb_mlp_create(int n_layers, const int64_t* dims, int64_t max_rows, tfb_mlp*
     m->velocity = reinterpret_cast<float*>(m->arena + o_vel);
     m->reduced = reinterpret_cast<float*>(m->arena + o_red);
     m->loss = reinterpret_cast<float*>(m->arena + o_loss);
+    m->trace = reinterpret_cast<unsigned long long*>(m->arena + o_loss + 64);
     m->pplanes = reinterpret_cast<float*>(m->arena + o_pp);
     m->wplanes.assign((size_t)n_layers, nullptr);
     m->act.assign((size_t)n_layers + 1, nullptr);
@@ -546,6 +561,7 @@ int tfb_mlp_buffer(tfb_mlp* m, int which, int layer, void** ptr_out) {
         *ptr_out = m->act[(size_t)layer + 1];
         break;
     case TFB_MLP_REGION: *ptr_out = m->region; break;
+    case TFB_MLP_EXCHANGE_TRACE: *ptr_out = m->trace; break;
     case TFB_MLP_INPUT_GRAD:
         if (layer < 1 || layer >= m->L) return fail(TFB_ERR_INVALID_ARG, "mlp_buffer: layer %d has no input gradient", layer);
         *ptr_out = m->dx[(size_t)layer];
@@ -646,6 +662,9 @@ int tfb_mlp_set_option(tfb_mlp* m, int option, int64_t value) {
         return TFB_OK;
     case TFB_MLP_OPT_KEEP_REDUCED_GRADS:
         m->keep_reduced = value != 0;
+        return TFB_OK;
+    case TFB_MLP_OPT_TRACE_EXCHANGE:
+        m->trace_on = value != 0;
         return TFB_OK;
     default:
         return fail(TFB_ERR_INVALID_ARG, "mlp_set_option: unknown option %d", option);

@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(kReduceThreads) peer_allreduce_kernel(const __
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(epoch_word) + 1u;
     int ok = 1;
     if (world > 1 && t < world) {
-        st_release_sys(flag_word(me.region[t], p.flags_off, 0, cta, rank), epoch);
+        st_relaxed_sys(flag_word(me.region[t], p.flags_off, 0, cta, rank), epoch);   // publishes nothing of this kernel
         if (!wait_flag(flag_word(mine, p.flags_off, 0, cta, t), epoch, p.wait_ns)) {
             ok = 0;
             if (me.status != nullptr) atomicCAS(me.status, 0, kDevTimeoutExchange);
@@ -67,8 +67,8 @@ __global__ void __launch_bounds__(kReduceThreads) peer_allreduce_kernel(const __
     if (world == 1) return;
     __syncthreads();
     if (t < world) {
-        __threadfence_system();
-        st_release_sys(flag_word(me.region[t], p.flags_off, 1, cta, rank), epoch);
+        __threadfence_system();   // cumulative over the CTA's stores through the barrier above
+        st_relaxed_sys(flag_word(me.region[t], p.flags_off, 1, cta, rank), epoch);
         if (ok && !wait_flag(flag_word(mine, p.flags_off, 1, cta, t), epoch, p.wait_ns)) {
             if (me.status != nullptr) atomicCAS(me.status, 0, kDevTimeoutExchange);
         }

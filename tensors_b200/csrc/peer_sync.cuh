@@ -45,15 +45,30 @@ __device__ __forceinline__ void st_peer(float4* p, const float4& v) {
                  ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-// Waits until *flag has reached `epoch` (wrap-safe) or the wall-clock limit runs out.
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Waits until *flag has reached `epoch` (wrap-safe) or the wall-clock limit runs out. The polls are
+// relaxed loads; one acquire fence at system scope after the flag has been seen orders everything the
+// waiter reads afterwards behind the writer's release.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long limit_ns) {
-    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t polls = 0;
-    while (true) {
-        if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-        if (((++polls) & 15u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
+    bool seen = (int32_t)(ld_relaxed_sys(flag) - epoch) >= 0;
+    if (!seen) {
+        const uint64_t t0 = global_timer_ns();
+        uint32_t polls = 0;
+        while (true) {
+            if ((int32_t)(ld_relaxed_sys(flag) - epoch) >= 0) { seen = true; break; }
+            if (((++polls) & 15u) == 0 && global_timer_ns() - t0 > limit_ns) break;
+        }
     }
+    if (seen) asm volatile("fence.acquire.sys;" ::: "memory");
+    return seen;
 }
 
 }  // namespace tfb
