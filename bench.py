@@ -388,7 +388,7 @@ def section_gemm(h, args, capi, lib, peaks, peak_src):
         "roofline": {"bound": "tensor", "achieved": ach, "peak": tf32_peak, "unit": "TFLOP/s", "frac": ach / tf32_peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch at n = 8192 from a one-pass
                      # ncu capture of this command (algorithmic bytes: 1.34e9); other sizes: not captured
-                     "traffic": (7.36e9 + 0.268e9) if n == 8192 else None,
+                     "traffic": (7.78e9 + 0.274e9) if n == 8192 else None,
                      "kernel": "gemm_tcgen05_kernel<TF32x3,BN=256,CTA pair> alone, operands pre-split",
                      "peak_source": f"{peak_src} bf16_tflops {peaks['bf16_tflops']} (burst) / 6: TF32 issues at half the "
                                     f"BF16 rate and three products make one FP32 product",

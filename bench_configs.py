@@ -4,7 +4,9 @@
   config 2  Linear 64x784 -> 256 forward + backward (bias, ReLU fused)
   config 3  Conv2d 128x3x32x32 -> 64 -> 128, 3x3 pad 1: forward, backward per layer
   config 4  square sweep 1024..16384, FP32 (3xTF32) and BF16
-  config 5  MLP 784-1024-1024-10 training step, batch 8192 / world size (NCCL all-reduce when > 1 rank)
+  config 5  MLP 784-1024-1024-10 training step, batch 8192 / world size (peer-memory or NCCL exchange when > 1 rank)
+  config 6  probe: the GEMM kernel's rasterisation group width (A panels shared by a wave) at 8192^3, FP32 and BF16
+  config 7  probe: phase timeline of the gradient-exchange kernel (flag barrier, slice, fence, flag barrier); > 1 rank
 
 Run:  python bench_configs.py [--configs 1,2,3,4,5] [--iters 20]
       torchrun --nproc-per-node N bench_configs.py --configs 5 [--exchange peer|nccl]
@@ -184,6 +186,74 @@ def config5(iters):
         dist.destroy_process_group()
 
 
+def config6(iters):
+    n = 8192
+    A, B = torch.rand(n, n, device="cuda") * 2 - 1, torch.rand(n, n, device="cuda") * 2 - 1
+    C = torch.empty(n, n, device="cuda")
+    hl = torch.empty(4, n, n, device="cuda")
+    capi.check(lib.tfb_split_tf32(p(A), n, n, n, p(hl[0]), p(hl[1]), n, stream()))
+    capi.check(lib.tfb_split_tf32(p(B), n, n, n, p(hl[2]), p(hl[3]), n, stream()))
+    A16, B16 = A.bfloat16(), B.bfloat16()
+    f32 = lambda: capi.check(lib.tfb_gemm_presplit(p(hl[0]), p(hl[1]), p(hl[2]), p(hl[3]), p(C), n, n, n, n, n, n, 0, 0,
+                                                   None, 0, stream()))
+    b16 = lambda: capi.check(lib.tfb_matmul(p(A16), p(B16), p(C), n, n, n, 2, 0, stream()))
+    for gm in (8, 1, 2, 4, 16, 32):
+        capi.check(lib.tfb_set_tuning(capi.TUNE_GEMM_GROUP_M, gm))
+        for fn, name in ((f32, "fp32 (3xTF32), operands pre-split"), (b16, "bf16")):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            emit(config=6, what=f"GEMM 8192^3 {name}, raster group of {gm} M tiles", group_m=gm, ms=ms,
+                 tflops=2 * n ** 3 / ms / 1e9)
+    capi.check(lib.tfb_set_tuning(capi.TUNE_GEMM_GROUP_M, 0))
+
+
+def config7(iters):
+    import torch.distributed as dist
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world < 2:
+        emit(config=7, what="exchange phase trace needs more than one rank (run under torchrun)")
+        return
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    dims = (784, 1024, 1024, 10)
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    m = MLP(dims, ws, max_rows=64, exchange="peer")
+    m.connect()
+    m.set_option(3, 1)   # TFB_MLP_OPT_TRACE_EXCHANGE
+    stamps = torch.empty(5, dtype=torch.int64, device="cuda")
+    for ctas in (0, 64, 32, 16):
+        m.set_option(MLP.OPT_CTAS, ctas)
+        for _ in range(10):
+            m.exchange_update(0.0, 0.9)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(max(iters, 20)):
+            m.exchange_update(0.0, 0.9)
+        e1.record()
+        torch.cuda.synchronize()
+        capi.check(lib.tfb_memcpy(p(stamps), ctypes.c_void_p(m._ptr(8)), 40, 3, stream()))   # TFB_MLP_EXCHANGE_TRACE
+        torch.cuda.synchronize()
+        v = stamps.cpu().tolist()
+        emit(config=7, rank=rank, world=world, exchange_ctas=ctas or "default (128)",
+             us_per_exchange=e0.elapsed_time(e1) * 1e3 / max(iters, 20),
+             phases_us={k: (v[i + 1] - v[i]) / 1e3 for i, k in enumerate(("flag_barrier_0", "slice_sum_update_store",
+                                                                          "system_fence", "flag_barrier_1"))})
+        dist.barrier()
+    m.disconnect()
+    del m
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="1,2,3,4,5")
@@ -202,7 +272,7 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     capi.check(lib.tfb_init())
     for c in a.configs.split(","):
-        {"1": config1, "2": config2, "3": config3, "4": config4, "5": config5}[c.strip()](a.iters)
+        {"1": config1, "2": config2, "3": config3, "4": config4, "5": config5, "6": config6, "7": config7}[c.strip()](a.iters)
     code = capi.device_status()
     if code:
         raise SystemExit(f"device error {code}")

@@ -70,6 +70,8 @@ const char* tfb_last_error_string(void);
  *   PDL             1 (default) = kernels are launched so that each may start its prologue while the one
  *                   before it on the stream is finishing (programmatic dependent launch); 0 = plain
  *                   stream order (environment: TFB_PDL)
+ *   GEMM_GROUP_M    0 = default, else the number of M tiles per rasterisation group of the GEMM kernel (tiles
+ *                   of one group are visited M-fastest, so a wave of CTAs shares that many A panels)
  *   FUSE_PLANES     which products of the MLP step also write the TF32 hi / lo planes of their result for
  *                   the next layer instead of leaving that to a separate pass: 0 = none, 1 (default) =
  *                   the split-K products (their reduction kernel writes the planes), 2 = all of them
@@ -85,7 +87,8 @@ const char* tfb_last_error_string(void);
 #define TFB_TUNE_HOST_PANEL_ROWS 7
 #define TFB_TUNE_PDL 8
 #define TFB_TUNE_FUSE_PLANES 9
-#define TFB_TUNE_COUNT 10
+#define TFB_TUNE_GEMM_GROUP_M 10
+#define TFB_TUNE_COUNT 11
 int tfb_set_tuning(int knob, int value);
 int tfb_get_tuning(int knob, int* value_out);
 

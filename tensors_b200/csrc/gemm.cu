@@ -614,6 +614,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     const bool a_mn = !c.a_kmajor, b_mn = !c.b_kmajor;
     if (use_pair) {
         args.group_m = 8;   // 8 pair tiles = 2048 rows, the same raster width as the single-CTA kernel
+        if (tuning(TFB_TUNE_GEMM_GROUP_M) > 0) args.group_m = tuning(TFB_TUNE_GEMM_GROUP_M);
         const int max_pairs = st->sm_count / 2;
         const int pairs = units < max_pairs ? (int)units : max_pairs;
         if (f32) rc = launch_layout<kKindTF32x3, 256, 3, true>(a_mn, b_mn, maps, args, pairs, stream);
