@@ -79,6 +79,86 @@ conv_direct_forward_kernel(const float* __restrict__ x, const float* __restrict_
     }
 }
 
+// The same sums for stride 1, dilation 1 and a filter shape known at compile time, with every loop unrolled
+// and no index arithmetic in it: a block of four warps computes an 8-row x 32-column tile of output
+// positions of one sample for ALL output channels. The input patch the tile reads ((8 + KH - 1) x
+// (32 + KW - 1) x CIN values, zero outside the image, so the padding needs no test) and the whole filter sit
+// in shared memory; a thread owns two vertically adjacent positions (their input rows overlap, so the
+// KH + 1 rows it reads serve both) and a strip of 32 channels at a time: per filter tap 8 broadcast
+// 16-byte reads of the filter row feed 32 two-wide FMAs. Same accumulation order as the kernel above.
+constexpr int kTileRows = 8, kTileCols = 32, kTiledThreads = 128;
+
+template <int CIN, int KH, int KW>
+__global__ void __launch_bounds__(kTiledThreads)
+conv_direct_forward_tiled_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                 float* __restrict__ out, const DirectArgs a, int relu, int cout_pad) {
+    constexpr int TAPS = CIN * KH * KW, PH = kTileRows + KH - 1, PW = kTileCols + KW - 1;
+    extern __shared__ __align__(16) float tiled_s[];
+    float* w_s = tiled_s;                          // [TAPS][cout_pad]
+    float* patch = tiled_s + TAPS * cout_pad;      // [CIN][PH][PW]
+    const int n = blockIdx.z, oy0 = blockIdx.y * kTileRows, ox0 = blockIdx.x * kTileCols;
+    for (int i = threadIdx.x; i < TAPS * cout_pad; i += kTiledThreads) {
+        const int k = i / cout_pad, co = i - k * cout_pad;
+        w_s[i] = co < a.Cout ? __ldg(w + (long long)co * TAPS + k) : 0.f;
+    }
+    const float* xs = x + (long long)n * CIN * a.H * a.W;
+    for (int i = threadIdx.x; i < CIN * PH * PW; i += kTiledThreads) {
+        const int c = i / (PH * PW), r = (i - c * PH * PW) / PW, q = i - c * PH * PW - r * PW;
+        const int iy = oy0 - a.ph + r, ix = ox0 - a.pw + q;
+        patch[i] = (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) ? __ldg(xs + ((long long)c * a.H + iy) * a.W + ix) : 0.f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, ry = 2 * (threadIdx.x >> 5);
+    const int oy = oy0 + ry, ox = ox0 + lane;
+    const long long P = (long long)a.outH * a.outW;
+    for (int strip = 0; strip < cout_pad; strip += 32) {
+        float2 acc0[16], acc1[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc0[j] = acc1[j] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < CIN; ++c) {
+            float v[KH + 1][KW];
+#pragma unroll
+            for (int r = 0; r < KH + 1; ++r)
+#pragma unroll
+                for (int q = 0; q < KW; ++q) v[r][q] = patch[(c * PH + ry + r) * PW + lane + q];
+#pragma unroll
+            for (int ki = 0; ki < KH; ++ki)
+#pragma unroll
+                for (int kj = 0; kj < KW; ++kj) {
+                    const float4* wr = reinterpret_cast<const float4*>(w_s + ((c * KH + ki) * KW + kj) * cout_pad + strip);
+                    const float2 p0 = make_float2(v[ki][kj], v[ki][kj]), p1 = make_float2(v[ki + 1][kj], v[ki + 1][kj]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 ww = wr[j];
+                        acc0[2 * j] = __ffma2_rn(p0, make_float2(ww.x, ww.y), acc0[2 * j]);
+                        acc0[2 * j + 1] = __ffma2_rn(p0, make_float2(ww.z, ww.w), acc0[2 * j + 1]);
+                        acc1[2 * j] = __ffma2_rn(p1, make_float2(ww.x, ww.y), acc1[2 * j]);
+                        acc1[2 * j + 1] = __ffma2_rn(p1, make_float2(ww.z, ww.w), acc1[2 * j + 1]);
+                    }
+                }
+        }
+        if (ox < a.outW) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int co = strip + j;
+                if (co < a.Cout) {
+                    const float b = bias != nullptr ? __ldg(bias + co) : 0.f;
+                    float r0 = ((j & 1) ? acc0[j >> 1].y : acc0[j >> 1].x) + b;
+                    float r1 = ((j & 1) ? acc1[j >> 1].y : acc1[j >> 1].x) + b;
+                    if (relu) {
+                        r0 = r0 > 0.f ? r0 : 0.f;
+                        r1 = r1 > 0.f ? r1 : 0.f;
+                    }
+                    float* o = out + ((long long)n * a.Cout + co) * P + (long long)oy * a.outW + ox;
+                    if (oy < a.outH) o[0] = r0;
+                    if (oy + 1 < a.outH) o[a.outW] = r1;
+                }
+            }
+        }
+    }
+}
+
 // dX[n][c][y][x] = sum over (ki, kj, co) of dY[n][co][oy][ox] * w[co][c][ki][kj] with
 // oy = (y + ph - ki * dh) / sh where that division is exact and in range (x alike) — the gather form
 // of the transposed convolution: no atomics, a fixed order. One thread owns one input position and up
@@ -215,6 +295,18 @@ DirectArgs direct_args(const ConvShape& s) {
                       (int)s.sw, (int)s.ph, (int)s.pw, (int)s.dh, (int)s.dw, (int)s.outH, (int)s.outW};
 }
 
+template <int CIN, int KH, int KW>
+int launch_forward_tiled(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
+                         cudaStream_t stream) {
+    const int cout_pad = (int)((s.Cout + 31) / 32 * 32);
+    const size_t smem = (size_t)(CIN * KH * KW * cout_pad + CIN * (kTileRows + KH - 1) * (kTileCols + KW - 1)) * sizeof(float);
+    dim3 grid((unsigned)((s.outW + kTileCols - 1) / kTileCols), (unsigned)((s.outH + kTileRows - 1) / kTileRows), (unsigned)s.N);
+    conv_direct_forward_tiled_kernel<CIN, KH, KW><<<grid, kTiledThreads, smem, stream>>>(x, w, bias, out, direct_args(s),
+                                                                                         relu ? 1 : 0, cout_pad);
+    TFB_CUDA_OK(cudaGetLastError());
+    return TFB_OK;
+}
+
 bool direct_enabled() {
     return tuning(TFB_TUNE_CONV_DIRECT) != 0;
 }
@@ -235,6 +327,13 @@ bool conv_direct_dgrad_eligible(const ConvShape& s) {
 
 int conv_direct_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,
                         cudaStream_t stream) {
+    // stride 1, no dilation, a filter shape with an unrolled instance, the filter within 40 KB of shared memory
+    if (s.sh == 1 && s.sw == 1 && s.dh == 1 && s.dw == 1 && s.kH == 3 && s.kW == 3 && s.Cout <= 256 &&
+        (s.outH + kTileRows - 1) / kTileRows < 65536) {
+        if (s.Cin == 3) return launch_forward_tiled<3, 3, 3>(x, w, bias, out, s, relu, stream);
+        if (s.Cin == 1) return launch_forward_tiled<1, 3, 3>(x, w, bias, out, s, relu, stream);
+        if (s.Cin == 4) return launch_forward_tiled<4, 3, 3>(x, w, bias, out, s, relu, stream);
+    }
     const long long P = s.outH * s.outW;
     dim3 grid((unsigned)((P + kDirectThreads - 1) / kDirectThreads), (unsigned)((s.Cout + kDirectCout - 1) / kDirectCout),
               (unsigned)s.N);
