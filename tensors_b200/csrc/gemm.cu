@@ -363,31 +363,65 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
     p.bn = p.pair ? 256 : (c.force_bn ? c.force_bn : (env_bn ? env_bn : choose_bn(c.M, c.N, sm_count)));
     p.kb_per_split = p.k_blocks;
     if (!p.pair && c.K > 0) {
-        // Few output tiles but a long contraction (weight gradients: M, N ~ 1k, K = batch): share each
-        // tile's K range between several CTAs; partial sums go to scratch and are added in fixed order.
+        // Few output tiles but a long contraction (weight gradients: M, N ~ 1k, K = batch; every product of
+        // a small-batch shard): share each tile's K range between several CTAs; partial sums go to scratch
+        // and are added in fixed order.
+        struct Split {
+            bool ok = false;
+            int kb_per_split = 0, split_k = 1;
+            int64_t rows_per_split = 0;
+        };
         auto split_plan = [&](long long workers, long long tiles, int tile_rows) {
-            long long s = env_split > 0 ? env_split : workers / tiles;
-            if (s > p.k_blocks / 8) s = p.k_blocks / 8;
-            if (s > 32) s = 32;
-            if (s < 2 || !(env_split > 0 || tiles * 2 <= workers)) return false;
-            p.kb_per_split = (int)((p.k_blocks + s - 1) / s);
-            p.split_k = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;
-            p.rows_per_split = (c.M + tile_rows - 1) / tile_rows * tile_rows;
+            Split r;
+            long long sp = env_split > 0 ? env_split : workers / tiles;
+            if (sp > p.k_blocks / 8) sp = p.k_blocks / 8;
+            if (sp > 32) sp = 32;
+            if (sp < 2 || !(env_split > 0 || tiles * 2 <= workers)) return r;
+            r.kb_per_split = (int)((p.k_blocks + sp - 1) / sp);
+            r.split_k = (p.k_blocks + r.kb_per_split - 1) / r.kb_per_split;
+            r.rows_per_split = (c.M + tile_rows - 1) / tile_rows * tile_rows;
+            r.ok = true;
+            return r;
+        };
+        auto apply = [&](const Split& r, bool pair, int bn) {
+            p.pair = pair;
+            p.bn = bn;
+            p.kb_per_split = r.kb_per_split;
+            p.split_k = r.split_k;
+            p.rows_per_split = r.rows_per_split;
             p.ld_partial = (c.N + 3) / 4 * 4;
             p.partial_bytes = (size_t)p.split_k * p.rows_per_split * p.ld_partial * 4 + 256;
-            return true;
         };
-        // CTA pairs keep the tensor pipe fuller than single CTAs (deeper ring per MMA), so prefer them
-        // whenever whole 256 x 256 tiles exist.
+        // Estimated time of a split plan in SM clocks: the MMA time of one unit's K range per wave, plus
+        // writing and re-reading `split_k` partial copies of the output at ~18 bytes per clock and SM (5 TB/s).
+        // (Measured on a 1024-row MLP shard: single-CTA 128-wide tiles with 2 splits beat CTA pairs with 4
+        // by 13 % although the pair feeds the tensor pipe better, because half as many partials move; for
+        // the K = 8192 weight gradients the pair wins.)
+        auto cost = [&](const Split& r, long long tiles, long long workers, int clk_per_kb) {
+            const long long waves = (tiles * r.split_k + workers - 1) / workers;
+            const double mma = (double)waves * r.kb_per_split * clk_per_kb;
+            const double partials = (double)r.split_k * c.M * c.N * 8.0 / (18.0 * sm_count);
+            return mma + partials;
+        };
+        const bool f32 = c.in_dtype == TFB_DTYPE_F32;
         const bool pair_ok = !c.force_bn && !env_bn && env_pair != 0 && c.M >= 256 && c.N >= 256;
-        if (pair_ok && split_plan(sm_count / 2, pair_tiles, 2 * kBlockM)) {
-            p.pair = true;
-            p.bn = 256;
-        } else {
-            int bn = p.bn;
-            if (!c.force_bn && !env_bn && c.N >= 128) bn = c.N >= 256 ? 256 : 128;   // wide tiles feed the MMA better
-            const long long tiles = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + bn - 1) / bn);
-            if (split_plan(sm_count, tiles, kBlockM)) p.bn = bn;
+        int bn1 = p.bn;
+        if (!c.force_bn && !env_bn && c.N >= 128) bn1 = c.N >= 256 ? 256 : 128;   // wide tiles feed the MMA better
+        const long long tiles1 = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + bn1 - 1) / bn1);
+        const Split sp_pair = pair_ok ? split_plan(sm_count / 2, pair_tiles, 2 * kBlockM) : Split();
+        const Split sp_one = split_plan(sm_count, tiles1, kBlockM);
+        // third candidate: single-CTA tiles of 128 columns, twice as many tiles and half as many splits
+        const long long tiles128 = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + 127) / 128);
+        const Split sp_128 = (pair_ok && env_pair < 0) ? split_plan(sm_count, tiles128, kBlockM) : Split();
+        if (sp_pair.ok && sp_128.ok &&
+            cost(sp_128, tiles128, sm_count, f32 ? 1000 : 340) < cost(sp_pair, pair_tiles, sm_count / 2, f32 ? 1536 : 512)) {
+            apply(sp_128, false, 128);
+        } else if (sp_pair.ok) {
+            // CTA pairs keep the tensor pipe fuller than single CTAs (deeper ring per MMA), so prefer them
+            // whenever whole 256 x 256 tiles exist.
+            apply(sp_pair, true, 256);
+        } else if (sp_one.ok) {
+            apply(sp_one, false, bn1);
         }
     }
     return p;

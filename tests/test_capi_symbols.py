@@ -32,6 +32,38 @@ def test_python_prototypes_match_header():
     assert set(capi.PROTOTYPES) == declared_symbols()
 
 
+def test_tuning_knobs_and_host_only_queries_work_without_gpu():
+    # knobs are plain host state (defaults, or the environment read once); nothing here touches CUDA
+    import ctypes
+    import tensors_b200.capi as capi
+    lib = capi.lib
+    v = ctypes.c_int(-99)
+    assert lib.tfb_get_tuning(capi.TUNE_PDL, ctypes.byref(v)) == 0 and v.value in (0, 1)
+    old = v.value
+    assert lib.tfb_set_tuning(capi.TUNE_PDL, 0) == 0
+    assert lib.tfb_get_tuning(capi.TUNE_PDL, ctypes.byref(v)) == 0 and v.value == 0
+    assert lib.tfb_set_tuning(capi.TUNE_PDL, old) == 0
+    assert lib.tfb_set_tuning(999, 1) == -1 and "knob" in capi.last_error()
+    assert lib.tfb_get_tuning(capi.TUNE_GEMM_TILE_N, None) == -1
+    assert lib.tfb_conv_out_dim(32, 3, 1, 1, 1) == 32 and lib.tfb_conv_out_dim(13, 3, 2, 1, 2) == 6
+    assert lib.tfb_mlp_numel(None) == 0
+    assert lib.tfb_mlp_ipc_handle_bytes() == 64
+    assert lib.tfb_matmul_f32_static_limit() == 16 << 20
+    n, b = ctypes.c_uint64(7), ctypes.c_uint64(7)
+    assert lib.tfb_scratch_stats(0, ctypes.byref(n), ctypes.byref(b)) == 0 and (n.value, b.value) == (0, 0)
+
+
+def test_flat_parameter_layout_matches_the_documented_rule():
+    # every weight and bias starts on a multiple of 4 floats (16 bytes): the layout tfb_mlp_segment reports
+    from tensors_b200.mlp import flat_layout, shard_rows
+    offsets, numel = flat_layout((784, 1024, 1024, 10))
+    assert offsets == [0, 802816, 803840, 1852416, 1853440, 1863680] and numel == 1863692
+    offsets, numel = flat_layout((5, 3, 2))
+    assert offsets == [0, 16, 20, 28] and numel == 32
+    assert all(o % 4 == 0 for o in offsets)
+    assert [shard_rows(8192, r, 8) for r in (0, 7)] == [(0, 1024), (7168, 8192)]
+
+
 def test_error_string_is_callable_without_gpu():
     import tensors_b200.capi as capi
     assert isinstance(capi.last_error(), str)

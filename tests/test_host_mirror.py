@@ -75,7 +75,7 @@ def test_data_parallel_mlp_step_from_plain_cpp(tmp_path, oracle, ranks):
         # mask (the oracle sums in another order), which moves that one unit's gradient of the layer
         # below by a whole term: at most two such units are tolerated, every other unit must agree.
         gw, ow = grads[wseg].reshape(odw[i].shape), odw[i]
-        err_rows = np.linalg.norm(gw - ow, axis=1) / np.linalg.norm(ow, axis=1)
+        err_rows = np.linalg.norm(gw - ow, axis=1) / (np.linalg.norm(ow, axis=1) + 1e-30)   # dead units: 0 / tiny
         err_bias = np.abs(grads[bseg] - odb[i]) / (np.abs(odb[i]) + 1e-3 * np.linalg.norm(odb[i]))
         ties = int(((err_rows > 2e-5) | (err_bias > 2e-4)).sum())
         assert ties <= (2 if i < 2 else 0), (i, ties, np.sort(err_rows)[-4:], np.sort(err_bias)[-4:])
