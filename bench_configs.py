@@ -7,6 +7,8 @@
   config 5  MLP 784-1024-1024-10 training step, batch 8192 / world size (peer-memory or NCCL exchange when > 1 rank)
   config 6  probe: the GEMM kernel's rasterisation group width (A panels shared by a wave) at 8192^3, FP32 and BF16
   config 7  probe: phase timeline of the gradient-exchange kernel (flag barrier, slice, fence, flag barrier); > 1 rank
+  config 8  probe: phase timeline of the GEMM kernel (prologue, first stage, last MMA, epilogue) for the products of
+            an MLP shard, next to the whole call's time under CUDA-graph replay
 
 Run:  python bench_configs.py [--configs 1,2,3,4,5] [--iters 20]
       torchrun --nproc-per-node N bench_configs.py --configs 5 [--exchange peer|nccl]
@@ -254,6 +256,37 @@ def config7(iters):
     dist.destroy_process_group()
 
 
+def config8(iters):
+    stamps = torch.zeros(8, dtype=torch.int64, device="cuda")
+
+    def probe(M, N, K, ta, tb, what):
+        A = torch.randn((K, M) if ta else (M, K), device="cuda")
+        B = torch.randn((N, K) if tb else (K, N), device="cuda")
+        C = torch.empty(M, N, device="cuda")
+        lda, ldb = A.shape[1], B.shape[1]
+        hA, hB = torch.empty(2, *A.shape, device="cuda"), torch.empty(2, *B.shape, device="cuda")
+        capi.check(lib.tfb_split_tf32(p(A), A.shape[0], lda, lda, p(hA[0]), p(hA[1]), lda, stream()))
+        capi.check(lib.tfb_split_tf32(p(B), B.shape[0], ldb, ldb, p(hB[0]), p(hB[1]), ldb, stream()))
+        run = lambda: capi.check(lib.tfb_gemm_presplit(p(hA[0]), p(hA[1]), p(hB[0]), p(hB[1]), p(C), M, N, K, lda, ldb, N,
+                                                       int(ta), int(tb), None, 0, stream()))
+        us = graph_us(run, max(iters, 10))
+        capi.check(lib.tfb_gemm_trace(p(stamps)))
+        run()
+        torch.cuda.synchronize()
+        capi.check(lib.tfb_gemm_trace(None))
+        v = stamps.cpu().tolist()
+        names = ("prologue_done", "first_stage_landed", "last_mma_committed", "accumulator_seen", "epilogue_drained", "exit")
+        emit(config=8, what=what, shape=[M, N, K], call_us_graph=us,
+             kernel_phase_us={n: round((v[i + 1] - v[0]) / 1e3, 2) for i, n in enumerate(names)})
+
+    probe(1024, 1024, 1024, False, True, "forward X W^T of a 1024-row shard")
+    probe(1024, 1024, 784, False, True, "forward layer 1 of a 1024-row shard")
+    probe(1024, 1024, 1024, False, False, "input gradient dZ W")
+    probe(1024, 1024, 1024, True, False, "weight gradient dZ^T X")
+    probe(8192, 1024, 1024, False, True, "forward X W^T, batch 8192")
+    probe(2048, 2048, 2048, False, False, "2048^3")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="1,2,3,4,5")
@@ -272,7 +305,7 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     capi.check(lib.tfb_init())
     for c in a.configs.split(","):
-        {"1": config1, "2": config2, "3": config3, "4": config4, "5": config5, "6": config6, "7": config7}[c.strip()](a.iters)
+        {"1": config1, "2": config2, "3": config3, "4": config4, "5": config5, "6": config6, "7": config7, "8": config8}[c.strip()](a.iters)
     code = capi.device_status()
     if code:
         raise SystemExit(f"device error {code}")

@@ -132,6 +132,13 @@ int tfb_matmul_batched(const void* A, const void* B, void* C, int64_t batch, int
                        int64_t stride_a, int64_t stride_b, int64_t stride_c, int in_dtype, int out_dtype,
                        void* stream);
 
+/* Diagnostics: while `device_stamps` (7 uint64 in device memory) is set, CTA 0 of every GEMM launch of the
+ * library records nanosecond timestamps at its phase boundaries into it — entry, prologue done, first
+ * operand stage landed, last MMA committed, accumulator seen by the epilogue, epilogue drained, exit —
+ * so that the fixed latency of small products can be read off directly. NULL turns it off (the default).
+ * ref: no counterpart. */
+int tfb_gemm_trace(void* device_stamps);
+
 /* General form. op(A) is M x K, op(B) is K x N:
  *   trans_a = 0: A stored [M,K] row-major (lda >= K); 1: A stored [K,M] row-major (lda >= M)
  *   trans_b = 0: B stored [K,N] row-major (ldb >= N); 1: B stored [N,K] row-major (ldb >= K)

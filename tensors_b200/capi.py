@@ -39,6 +39,7 @@ PROTOTYPES = {
     "tfb_gemm": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp]),
     "tfb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_matmul_batched": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
+    "tfb_gemm_trace": (_i32, [_vp]),
     "tfb_gemm_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
                            _vp, _i32, _vp]),
     "tfb_split_tf32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),

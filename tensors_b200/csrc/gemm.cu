@@ -336,6 +336,9 @@ int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, cons
     return split_operand_on(st->sm_count, src, rows, cols, ld, mask, hi, lo, ld_out, stream);
 }
 
+// Diagnostics: device buffer that CTA 0 of every GEMM launch stamps its phase times into (null = off).
+std::atomic<unsigned long long*> g_gemm_trace{nullptr};
+
 // Tile shape, CTA pairing and split-K of one call.
 struct GemmPlan {
     int bn = 256;
@@ -583,6 +586,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     args.bias = c.bias; args.bias_mode = c.bias_mode; args.relu = c.relu ? 1 : 0;
     args.is_bf16 = c.in_dtype == TFB_DTYPE_BF16 ? 1 : 0;
     args.status = st->status;
+    args.trace = g_gemm_trace.load(std::memory_order_relaxed);
     if (c.planes_hi != nullptr || c.planes_lo != nullptr) {
         if (!f32 || c.out_dtype != TFB_DTYPE_F32 || (c.N & 3) || c.planes_hi == nullptr || c.planes_lo == nullptr ||
             !aligned16(c.planes_hi) || !aligned16(c.planes_lo) || c.K <= 0)
@@ -672,3 +676,8 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
 }
 
 }  // namespace tfb
+
+extern "C" int tfb_gemm_trace(void* device_stamps) {
+    tfb::g_gemm_trace.store(static_cast<unsigned long long*>(device_stamps), std::memory_order_relaxed);
+    return TFB_OK;
+}

@@ -103,6 +103,11 @@ struct GemmArgs {
     float* planes_hi;
     float* planes_lo;
     long long ld_planes;
+    // Optional diagnostics: CTA 0 records %globaltimer at its phase boundaries (tfb_gemm_trace):
+    // [0] entry, [1] prologue done (barriers, tensor memory, cluster sync, dependency wait), [2] first
+    // operand stage landed, [3] last MMA of the CTA's last unit committed, [4] its accumulator seen by the
+    // epilogue, [5] epilogue stores issued and drained, [6] exit.
+    unsigned long long* trace;
     ConvGeom cv;          // only read when CONV != kConvNone
 };
 
@@ -325,6 +330,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const bool tracing = args.trace != nullptr && blockIdx.x == 0;
+    if (tracing && threadIdx.x == 0) args.trace[0] = global_timer_ns();
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // 0 = leader of the pair
     const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -364,6 +371,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // before this one are first accessed below.
     pdl_wait();
     pdl_launch_dependents();
+    if (tracing && threadIdx.x == 0) args.trace[1] = global_timer_ns();
 
     const int num_units = args.num_tiles * args.split_k;
 
@@ -527,6 +535,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         ok = mbar_wait(full_bar(s), ph, abort_flag, args.status, kDevTimeoutFull);
                         if (!ok) break;
                         tc_fence_after_sync();
+                        if (tracing && u == worker && kb == ub0) args.trace[2] = global_timer_ns();
                         const uint32_t st = smem_base + s * S::STAGE_BYTES;
                         const uint32_t a_hi = st;
                         const uint32_t a_lo = st + S::A_TILE;
@@ -552,6 +561,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     }
                     if (!ok) break;
                     commit(tfull_bar(buf));
+                    if (tracing) args.trace[3] = global_timer_ns();
                 }
             }
         }
@@ -597,6 +607,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after_sync();
+                    if (tracing && ew == 0 && lane == 0) args.trace[4] = global_timer_ns();
 #pragma unroll
                     for (int c = 0; c < COLS / 32; ++c) {
                         if (n0 + c * 32 < args.N) {
@@ -685,6 +696,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // The staging buffers must outlive the TMA engine's reads, and the stores must be complete
         // before the grid is.
         if (c_tma && lane == 0) tma_store_wait_all<0>();
+        if (tracing && ew == 0 && lane == 0) args.trace[5] = global_timer_ns();
     }
 
     tc_fence_before_sync();
@@ -697,6 +709,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_fence_after_sync();
         tmem_dealloc<CG>(tmem_base, TMEM_COLS);
     }
+    if (tracing && threadIdx.x == 0) args.trace[6] = global_timer_ns();
 }
 
 }  // namespace tfb
