@@ -112,25 +112,33 @@ __global__ void mask_colsum16_kernel(const T* __restrict__ dY, const T* __restri
     if (partial != nullptr) partial[(long long)blockIdx.y * ld_out + c] = s;
 }
 
-// db[c] = sum over row blocks of partial[b][c], in a fixed order: a block of 32 columns x 8 row
-// groups; group g adds blocks g, g+8, ... in ascending order, then the eight group sums are added
-// in ascending order.
+// db[c] = sum over row blocks of partial[b][c], in a fixed order: a block of 32 columns x 32 row
+// groups; group g adds blocks g, g+32, ... in ascending order (four loads in flight), then the 32 group
+// sums are added in ascending order.
+constexpr int kFinishGroups = 32;
 __global__ void colsum_finish_kernel(const float* __restrict__ partial, long long blocks, long long cols,
                                      long long ld, float* __restrict__ out) {
-    __shared__ float sm[8][33];
+    __shared__ float sm[kFinishGroups][33];
     pdl_wait();
     pdl_launch_dependents();
 
     const long long c = (long long)blockIdx.x * 32 + threadIdx.x;
     float s = 0.f;
-    if (c < cols)
-        for (long long b = threadIdx.y; b < blocks; b += 8) s += partial[b * ld + c];
+    if (c < cols) {
+        long long b = threadIdx.y;
+        for (; b + 3 * kFinishGroups < blocks; b += 4 * kFinishGroups) {
+            const float p0 = partial[b * ld + c], p1 = partial[(b + kFinishGroups) * ld + c];
+            const float p2 = partial[(b + 2 * kFinishGroups) * ld + c], p3 = partial[(b + 3 * kFinishGroups) * ld + c];
+            s += p0; s += p1; s += p2; s += p3;
+        }
+        for (; b < blocks; b += kFinishGroups) s += partial[b * ld + c];
+    }
     sm[threadIdx.y][threadIdx.x] = s;
     __syncthreads();
     if (threadIdx.y == 0 && c < cols) {
         float t = 0.f;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) t += sm[g][threadIdx.x];
+        for (int g = 0; g < kFinishGroups; ++g) t += sm[g][threadIdx.x];
         out[c] = t;
     }
 }
@@ -225,7 +233,7 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
         if (rc != TFB_OK) return rc;
     }
     if (db != nullptr) {
-        rc = launch_pdl(colsum_finish_kernel, dim3((unsigned)((out_f + 31) / 32)), dim3(32, 8), 0, stream,
+        rc = launch_pdl(colsum_finish_kernel, dim3((unsigned)((out_f + 31) / 32)), dim3(32, kFinishGroups), 0, stream,
                         (const float*)partial, (long long)row_blocks, (long long)out_f, (long long)ldz, db);
         if (rc != TFB_OK) return rc;
     }
