@@ -72,6 +72,9 @@ const char* tfb_last_error_string(void);
  *                   stream order (environment: TFB_PDL)
  *   GEMM_GROUP_M    0 = default, else the number of M tiles per rasterisation group of the GEMM kernel (tiles
  *                   of one group are visited M-fastest, so a wave of CTAs shares that many A panels)
+ *   SMALL_GEMM      1 (default) = FP32 products with at most 128 rows, at most 16384 outputs and a contraction
+ *                   of 512..2048 run on the one-launch CUDA-core kernel (exact FP32 FMAs, K split over a
+ *                   thread-block cluster), 0 = everything on the tensor-core path
  *   FUSE_PLANES     which products of the MLP step also write the TF32 hi / lo planes of their result for
  *                   the next layer instead of leaving that to a separate pass: 0 = none, 1 (default) =
  *                   the split-K products (their reduction kernel writes the planes), 2 = all of them
@@ -88,7 +91,8 @@ const char* tfb_last_error_string(void);
 #define TFB_TUNE_PDL 8
 #define TFB_TUNE_FUSE_PLANES 9
 #define TFB_TUNE_GEMM_GROUP_M 10
-#define TFB_TUNE_COUNT 11
+#define TFB_TUNE_SMALL_GEMM 11
+#define TFB_TUNE_COUNT 12
 int tfb_set_tuning(int knob, int value);
 int tfb_get_tuning(int knob, int* value_out);
 

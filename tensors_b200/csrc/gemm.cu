@@ -430,9 +430,12 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
     return p;
 }
 
-bool gemm_uses_split_k(const GemmCall& c, int sm_count) { return gemm_plan(c, sm_count).split_k > 1; }
+bool gemm_uses_split_k(const GemmCall& c, int sm_count) {
+    return !small_gemm_eligible(c) && gemm_plan(c, sm_count).split_k > 1;
+}
 
 size_t gemm_workspace_bytes(const GemmCall& c, int sm_count) {
+    if (small_gemm_eligible(c)) return 0;   // the CUDA-core kernel needs no scratch
     size_t bytes = 0;
     const int64_t a_rows = c.a_kmajor ? c.M : c.K, a_cols = c.a_kmajor ? c.K : c.M;
     const int64_t b_rows = c.b_kmajor ? c.N : c.K, b_cols = c.b_kmajor ? c.K : c.N;
@@ -471,6 +474,8 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
         return fail(TFB_ERR_INVALID_ARG, "gemm: leading dimension smaller than the row length");
     if (c.bias_mode != 0 && c.bias == nullptr)
         return fail(TFB_ERR_INVALID_ARG, "gemm: bias epilogue requested without a bias pointer");
+
+    if (small_gemm_eligible(c)) return small_gemm_run(c, stream);
 
     int rc = resolve_encoder();
     if (rc != TFB_OK) return rc;

@@ -101,6 +101,9 @@ struct GemmCall {
     size_t workspace_bytes = 0;
 };
 int gemm_run(const GemmCall& call, cudaStream_t stream);
+// small_gemm.cu: the CUDA-core kernel for FP32 products of at most a few tens of MFLOP (one launch, exact FP32).
+bool small_gemm_eligible(const GemmCall& call);
+int small_gemm_run(const GemmCall& call, cudaStream_t stream);
 // True when gemm_run would split this call's contraction between CTAs (its epilogue then runs in the
 // reduction kernel).
 bool gemm_uses_split_k(const GemmCall& call, int sm_count);

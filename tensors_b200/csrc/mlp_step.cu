@@ -386,7 +386,8 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         // the reduction kernel of a split-K product; in the GEMM epilogue only on request (measured: the
         // longer epilogue costs the large-batch products more than the separate pass it saves).
         planes_ready = false;
-        if (i + 1 < L && (out_f & 3) == 0 && (fuse == 2 || (fuse == 1 && gemm_uses_split_k(c, st->sm_count)))) {
+        if (i + 1 < L && (out_f & 3) == 0 &&
+            (fuse == 2 || (fuse == 1 && (gemm_uses_split_k(c, st->sm_count) || small_gemm_eligible(c))))) {
             c.planes_hi = m->xplanes[(size_t)i + 1];
             c.planes_lo = c.planes_hi + rows * out_f;
             planes_ready = true;

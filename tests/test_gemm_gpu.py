@@ -1,6 +1,8 @@
 """Parity of the tcgen05 GEMM (through the C-ABI) with the oracle: bit patterns of the reference's
 own kernel tests, seeded cases in every operand layout, the BF16 path, fused epilogues, and the
 full-size configurations through sampled rows/columns plus size-independent properties."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -13,6 +15,21 @@ pytestmark = pytest.mark.gpu
 
 FP32_TOL = 1e-5   # normwise, against the reference FP32 matmul
 BF16_TOL = 1e-2
+
+
+@pytest.fixture(autouse=True, params=["small_products_on_cuda_cores", "tensor_cores_only"])
+def product_path(request):
+    """FP32 products with few rows and a long contraction run on the one-launch CUDA-core kernel by default;
+    the tests run a second time with that knob off, so that the tensor-core path keeps seeing those shapes.
+    Tests that only hold large products are not repeated."""
+    large_only = ("test_square_sweep", "test_config1", "test_matmul_on_host_buffers", "test_few_rows_long_contraction")
+    if request.param == "tensor_cores_only" and request.node.name.startswith(large_only):
+        pytest.skip("large products take the tensor-core path either way")
+    old = ctypes.c_int(0)
+    capi.check(lib.tfb_get_tuning(capi.TUNE_SMALL_GEMM, ctypes.byref(old)))
+    capi.check(lib.tfb_set_tuning(capi.TUNE_SMALL_GEMM, 1 if request.param == "small_products_on_cuda_cores" else 0))
+    yield request.param
+    capi.check(lib.tfb_set_tuning(capi.TUNE_SMALL_GEMM, old.value))
 
 
 def tfb_matmul(a, b, in_dtype=capi.DTYPE_F32, out_dtype=capi.DTYPE_F32):
@@ -390,3 +407,37 @@ def test_batched_matmul_against_oracle(oracle, in_dtype):
     assert lib.tfb_matmul_batched(ptr(a), ptr(b), ptr(C), batch, M, N, K, M * K, K * N, M * N - 1, in_dtype,
                                   capi.DTYPE_F32, stream_ptr()) == -1   # overlapping outputs
     assert lib.tfb_matmul_batched(ptr(a), ptr(b), ptr(C), 0, M, N, K, 0, 0, 0, in_dtype, capi.DTYPE_F32, stream_ptr()) == 0
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [(64, 256, 784), (10, 1024, 1024), (1, 7, 513), (128, 128, 600), (33, 100, 1999),
+                                   (16, 1000, 2048)])
+def test_few_rows_long_contraction_on_the_cuda_core_kernel(oracle, shape, trans_a, trans_b):
+    # the window of the one-launch CUDA-core kernel (at most 128 rows and 16384 outputs, K in 512..2048): every
+    # operand layout, ragged tiles, K slices that do not divide evenly between the blocks of a cluster,
+    # bias and ReLU; plain FP32 FMAs, so the distance to an FP64 product is checked as well
+    M, N, K = shape
+    a, b = refdata.uniform(11, (M, K)), refdata.uniform(12, (K, N))
+    bias = refdata.normal(13, (N,))
+    A, B = dev(a), dev(b)
+    As = A.t().contiguous() if trans_a else A
+    Bs = B.t().contiguous() if trans_b else B
+    C = gemm_ex(As, Bs, M, N, K, trans_a, trans_b, bias=dev(bias), flags=capi.EPI_BIAS_COL | capi.EPI_RELU)
+    assert_device_ok()
+    got = C.cpu().numpy()
+    assert not np.isnan(got).any()
+    want = np.maximum(oracle.matmul(a, b) + bias[None, :], 0)
+    assert rel_err(got, want) < FP32_TOL
+    exact = np.maximum(a.astype(np.float64) @ b.astype(np.float64) + bias[None, :], 0)
+    assert rel_err(got, exact) < FP32_TOL
+    # operands given as TF32 planes are added back together exactly: same bits as the unsplit call
+    if K % 4 == 0 and M % 4 == 0 and N % 4 == 0:
+        hA, hB = torch.empty((2, *As.shape), device="cuda"), torch.empty((2, *Bs.shape), device="cuda")
+        capi.check(lib.tfb_split_tf32(ptr(As), As.shape[0], As.shape[1], As.shape[1], ptr(hA[0]), ptr(hA[1]), As.shape[1], stream_ptr()))
+        capi.check(lib.tfb_split_tf32(ptr(Bs), Bs.shape[0], Bs.shape[1], Bs.shape[1], ptr(hB[0]), ptr(hB[1]), Bs.shape[1], stream_ptr()))
+        C2 = torch.full((M, N), float("nan"), device="cuda")
+        capi.check(lib.tfb_gemm_presplit(ptr(hA[0]), ptr(hA[1]), ptr(hB[0]), ptr(hB[1]), ptr(C2), M, N, K, As.shape[1],
+                                         Bs.shape[1], N, int(trans_a), int(trans_b), ptr(dev(bias)),
+                                         capi.EPI_BIAS_COL | capi.EPI_RELU, stream_ptr()))
+        assert_device_ok()
+        assert torch.equal(C2, C)

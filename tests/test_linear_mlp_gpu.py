@@ -1,5 +1,7 @@
 """Parity of nn::Linear forward/backward, the loss kernels, SGD and the MLP step with the oracle and
 with the golden outputs of the unmodified reference."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -12,6 +14,21 @@ from gpu_util import assert_device_ok, dev, lib, ptr, rel_err, stream_ptr
 pytestmark = pytest.mark.gpu
 FP32_TOL = 1e-5
 BF16_TOL = 1e-2
+
+
+@pytest.fixture(autouse=True, params=["small_products_on_cuda_cores", "tensor_cores_only"])
+def product_path(request):
+    """FP32 products with few rows and a long contraction run on the one-launch CUDA-core kernel by default;
+    the tests run a second time with that knob off, so that the tensor-core path keeps seeing those shapes.
+    Tests that only hold large products are not repeated."""
+    large_only = ("test_square_sweep", "test_config1", "test_split_k_shapes", "test_matmul_on_host_buffers")
+    if request.param == "tensor_cores_only" and request.node.name.startswith(large_only):
+        pytest.skip("large products take the tensor-core path either way")
+    old = ctypes.c_int(0)
+    capi.check(lib.tfb_get_tuning(capi.TUNE_SMALL_GEMM, ctypes.byref(old)))
+    capi.check(lib.tfb_set_tuning(capi.TUNE_SMALL_GEMM, 1 if request.param == "small_products_on_cuda_cores" else 0))
+    yield request.param
+    capi.check(lib.tfb_set_tuning(capi.TUNE_SMALL_GEMM, old.value))
 
 
 def linear_fwd_bwd(x, w, b, g, relu, dtype=capi.DTYPE_F32):
