@@ -75,6 +75,14 @@ const char* tfb_last_error_string(void);
  *   SMALL_GEMM      1 (default) = FP32 products with at most 128 rows, at most 16384 outputs and a contraction
  *                   of 512..2048 run on the one-launch CUDA-core kernel (exact FP32 FMAs, K split over a
  *                   thread-block cluster), 0 = everything on the tensor-core path
+ *   RAW_HI          1 = a 16-byte aligned FP32 operand whose leading dimension is a multiple of 4 is read by
+ *                   the tensor core as its own hi plane (kind::tf32 drops the low 13 mantissa bits) and
+ *                   the split pass writes only the lo plane = the residual against that truncation, which
+ *                   halves the scratch and a third of the split traffic; 0 (default) = always write
+ *                   round-to-nearest hi and lo planes. Off by default because it was measured slower
+ *                   where it should matter most: an 8192-cubed product at the power cap runs at ~5 % lower
+ *                   clocks when the operand paths carry the 13 mantissa bits that rounded planes hold as
+ *                   zeros (216 against 223-230 TFLOP/s on one GPU, alternating runs)
  *   FUSE_PLANES     which products of the MLP step also write the TF32 hi / lo planes of their result for
  *                   the next layer instead of leaving that to a separate pass: 0 = none, 1 (default) =
  *                   the split-K products (their reduction kernel writes the planes), 2 = all of them
@@ -92,7 +100,8 @@ const char* tfb_last_error_string(void);
 #define TFB_TUNE_FUSE_PLANES 9
 #define TFB_TUNE_GEMM_GROUP_M 10
 #define TFB_TUNE_SMALL_GEMM 11
-#define TFB_TUNE_COUNT 12
+#define TFB_TUNE_RAW_HI 12
+#define TFB_TUNE_COUNT 13
 int tfb_set_tuning(int knob, int value);
 int tfb_get_tuning(int knob, int* value_out);
 

@@ -274,7 +274,7 @@ int conv2d_backward(const float* x, const float* w, const float* dY, float* dX, 
             dW = nullptr, db = nullptr;
             if (dX == nullptr) return TFB_OK;
         }
-        const bool t_dx = dX != nullptr && conv_tma_eligible(s, s.Cout);
+        const bool t_dx = dX != nullptr && conv_tma_eligible(s, s.Cout, true);
         const bool t_w = (dW != nullptr || db != nullptr) && conv_tma_eligible(s, s.Cin);
         if (t_dx || t_w) {
             rc = conv_tma_backward(x, w, dY, t_dx ? dX : nullptr, t_w ? dW : nullptr, t_w ? db : nullptr, s, stream);

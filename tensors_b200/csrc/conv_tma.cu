@@ -1,10 +1,13 @@
-// Stride-1 convolutions on the TMA-fed tcgen05 GEMM kernel.
+// Convolutions on the TMA-fed tcgen05 GEMM kernel.
 //
 // A pre-pass rewrites the activation tensor (NCHW) as NHWC TF32 hi / lo planes. In that layout the
 // slice of the im2col matrix that one K block needs — 32 channels of one filter tap for a rectangle
 // of output positions — is a single 4-D box of the tensor, shifted by the tap's offset, and the
 // padding halo is the box's out-of-range part, which the TMA unit fills with zeros. So the im2col
-// index map costs no instructions and the main loop is the plain GEMM pipeline:
+// index map costs no instructions and the main loop is the plain GEMM pipeline. A convolution stride is the
+// tensor map's traversal stride (the box then spans stride x as many source positions and delivers every
+// stride-th one), so it costs nothing either; the input gradient is stride-1 only (its gather form divides
+// by the stride).
 //
 //   forward          rows = positions, columns = Cout, K = (tap, Cin)       A: x planes   B: W[co][tap][ci]
 //   input gradient   rows = positions, columns = Cin,  K = (tap, Cout)      A: dY planes  B: W[ci][tap][co]
@@ -189,15 +192,17 @@ int to_nhwc_planes(const float* src, int64_t N, int64_t C, int64_t P, int64_t cp
     return TFB_OK;
 }
 
-// 4-D maps (channel, x, y, sample) over NHWC hi / lo planes with a box of 32 channels x bw x bh positions.
+// 4-D maps (channel, x, y, sample) over NHWC hi / lo planes with a box of 32 channels x bw x bh positions,
+// taken every sw-th / sh-th position of the tensor.
 int plane_maps(CUtensorMap out[2], const float* hi, const float* lo, int64_t cp, int64_t W, int64_t H, int64_t N,
-               uint32_t bw, uint32_t bh, bool atom32) {
+               uint32_t bw, uint32_t bh, bool atom32, uint32_t sw = 1, uint32_t sh = 1) {
     const uint64_t dims[4] = {(uint64_t)cp, (uint64_t)W, (uint64_t)H, (uint64_t)N};
     const uint64_t strides[3] = {(uint64_t)cp * 4, (uint64_t)(W * cp) * 4, (uint64_t)(H * W * cp) * 4};
-    const uint32_t box[4] = {32, bw, bh, 1};
-    int rc = make_map_nd(&out[0], hi, 4, dims, strides, box, atom32);
+    const uint32_t box[4] = {32, (bw - 1) * sw + 1, (bh - 1) * sh + 1, 1};
+    const uint32_t estr[4] = {1, sw, sh, 1};
+    int rc = make_map_nd(&out[0], hi, 4, dims, strides, box, atom32, estr);
     if (rc != TFB_OK) return rc;
-    return make_map_nd(&out[1], lo, 4, dims, strides, box, atom32);
+    return make_map_nd(&out[1], lo, 4, dims, strides, box, atom32, estr);
 }
 
 struct SpatialCall {
@@ -207,6 +212,7 @@ struct SpatialCall {
     int64_t J;                                  // output channels of this product
     int64_t out_H, out_W;                       // position grid = extent of the stored tensor
     int ay0, ay_step, ax0, ax_step;
+    int sy = 1, sx = 1;                         // position -> source stride (forward: the convolution's)
     float* dst; const float* bias; bool relu;
 };
 
@@ -242,11 +248,13 @@ int run_spatial(const SpatialCall& c, const ConvShape& s, const DeviceState* st,
     a.cv.out_h = (int)c.out_H; a.cv.out_w = (int)c.out_W;
     a.cv.cblks = cblks; a.cv.kw = (int)s.kW; a.cv.taps = (int)khw;
     a.cv.ay0 = c.ay0; a.cv.ay_step = c.ay_step; a.cv.ax0 = c.ax0; a.cv.ax_step = c.ax_step;
+    a.cv.sx = c.sx; a.cv.sy = c.sy;
     a.cv.n_samples = (int)s.N;
 
     CUtensorMap maps[5];
     memset(maps, 0, sizeof(maps));
-    int rc = plane_maps(&maps[0], c.src_hi, c.src_lo, c.src_cp, c.src_W, c.src_H, s.N, (uint32_t)tw, (uint32_t)th, false);
+    int rc = plane_maps(&maps[0], c.src_hi, c.src_lo, c.src_cp, c.src_W, c.src_H, s.N, (uint32_t)tw, (uint32_t)th, false,
+                        (uint32_t)c.sx, (uint32_t)c.sy);
     if (rc != TFB_OK) return rc;
     const uint64_t fdims[3] = {(uint64_t)c.src_cp, (uint64_t)khw, (uint64_t)c.J};
     const uint64_t fstr[2] = {(uint64_t)c.src_cp * 4, (uint64_t)(khw * c.src_cp) * 4};
@@ -293,15 +301,22 @@ bool conv_tma_forced() {
     return tuning(TFB_TUNE_CONV_TMA) == 2;
 }
 
-bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels) {
+bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels, bool input_gradient) {
     const int mode = tuning(TFB_TUNE_CONV_TMA);   // 0 never, 1 by the rules below, 2 whenever possible
     if (mode == 0) return false;
     // A K block holds 32 channels of one tap: with few channels most of it is zero fill and the
     // gather kernel, which packs taps densely, is faster.
     if (mode == 1 && contraction_channels < 16) return false;
-    // Stride 1 only (a box of positions must be a box of the source); tensor-map extents and
-    // 32-bit tile arithmetic bound the rest.
-    return s.sh == 1 && s.sw == 1 && s.N >= 1 && s.N < 65536 && s.H < (1 << 15) && s.W < (1 << 15) &&
+    // A box of positions must be a box of the source traversed with the stride: at most 256 source
+    // elements per box dimension (tiles are at most 128 positions wide and high); tensor-map extents
+    // and 32-bit tile arithmetic bound the rest.
+    if (input_gradient) {
+        if (s.sh != 1 || s.sw != 1) return false;
+    } else {
+        const int64_t tw = 1ll << pow2_ceil_log2(s.outW < 128 ? s.outW : 128), th = 128 / tw;
+        if (s.sw > 8 || s.sh > 8 || (tw - 1) * s.sw + 1 > 256 || (th - 1) * s.sh + 1 > 256) return false;
+    }
+    return s.N >= 1 && s.N < 65536 && s.H < (1 << 15) && s.W < (1 << 15) &&
            s.Cin < (1 << 15) && s.Cout < (1 << 15) && s.kH * s.kW * ((s.Cin + 31) / 32) < (1 << 20) &&
            s.kH * s.kW * ((s.Cout + 31) / 32) < (1 << 20);
 }
@@ -331,6 +346,7 @@ int conv_tma_forward(const float* x, const float* w, const float* bias, float* o
     c.src_hi = x_hi; c.src_lo = x_lo; c.src_c = s.Cin; c.src_cp = cp; c.src_H = s.H; c.src_W = s.W;
     c.f_hi = f_hi; c.f_lo = f_lo; c.J = s.Cout; c.out_H = s.outH; c.out_W = s.outW;
     c.ay0 = (int)-s.ph; c.ay_step = (int)s.dh; c.ax0 = (int)-s.pw; c.ax_step = (int)s.dw;
+    c.sy = (int)s.sh; c.sx = (int)s.sw;
     c.dst = out; c.bias = bias; c.relu = relu;
     return run_spatial(c, s, st, stream);
 }
@@ -418,6 +434,7 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
         a.bias = nullptr; a.bias_mode = kBiasNone; a.relu = 0; a.c_tma = 1; a.status = st->status;
         a.cv.cblks = cblks; a.cv.kw = (int)s.kW; a.cv.taps = (int)khw;
         a.cv.ay0 = (int)-s.ph; a.cv.ay_step = (int)s.dh; a.cv.ax0 = (int)-s.pw; a.cv.ax_step = (int)s.dw;
+        a.cv.sx = (int)s.sw; a.cv.sy = (int)s.sh;
         a.cv.kblk_w_log2 = kw_log2; a.cv.kblk_h = kbh; a.cv.kblk_x = (int)kblk_x; a.cv.kblk_y = (int)kblk_y;
         a.cv.n_samples = (int)s.N;
 
@@ -425,7 +442,8 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
         memset(maps, 0, sizeof(maps));
         rc = plane_maps(&maps[0], dy_hi, dy_lo, cop, s.outW, s.outH, s.N, (uint32_t)kbw, (uint32_t)kbh, true);
         if (rc != TFB_OK) return rc;
-        rc = plane_maps(&maps[2], x_hi, x_lo, cp, s.W, s.H, s.N, (uint32_t)kbw, (uint32_t)kbh, true);
+        rc = plane_maps(&maps[2], x_hi, x_lo, cp, s.W, s.H, s.N, (uint32_t)kbw, (uint32_t)kbh, true, (uint32_t)s.sw,
+                        (uint32_t)s.sh);
         if (rc != TFB_OK) return rc;
         rc = make_map(&maps[4], TFB_DTYPE_F32, partial, (uint64_t)ncols, (uint64_t)(splits * rows_per_split),
                       (uint64_t)ld_part * 4, 32, 32);

@@ -69,7 +69,7 @@ int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint
 }
 
 int make_map_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                const uint32_t* box, bool atom32) {
+                const uint32_t* box, bool atom32, const uint32_t* elem_strides) {
     int rc0 = resolve_encoder();
     if (rc0 != TFB_OK) return rc0;
     if (rank < 2 || rank > 5) return fail(TFB_ERR_INVALID_ARG, "tensor map rank %d", rank);
@@ -79,7 +79,7 @@ int make_map_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* di
     for (int i = 0; i < rank; ++i) {
         gdim[i] = dims[i];
         bx[i] = box[i];
-        estr[i] = 1;
+        estr[i] = elem_strides != nullptr ? elem_strides[i] : 1;
         if (i > 0) gstride[i - 1] = strides_bytes[i - 1];
     }
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), gdim,
@@ -103,10 +103,14 @@ __device__ __forceinline__ float tf32_round(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return __uint_as_float(r);
 }
+// What the tensor core makes of a raw FP32 operand under kind::tf32: the low 13 mantissa bits dropped.
+__device__ __forceinline__ float tf32_trunc(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
 // hi = x rounded to TF32 (10-bit mantissa), lo = x - hi (exact in FP32).
 // One thread per group of 4 output columns; ld_out is a multiple of 4 so the stores are
 // 16-byte vectors. Columns in [cols, ld_out) are written as zeros.
+// With hi == nullptr only a lo plane is written, for a product that reads the operand itself as its hi
+// plane: lo = x - trunc(x), rounded to TF32 (the tensor core would otherwise truncate it too).
 struct SplitJob {
     const float* src;
     long long rows, cols, ld;
@@ -153,12 +157,17 @@ __device__ __forceinline__ void split_tf32_body(const SplitJob& job, long long b
             }
         }
         float h[4], l[4];
+        if (hi != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            h[j] = tf32_round(x[j]);
-            l[j] = x[j] - h[j];
+            for (int j = 0; j < 4; ++j) {
+                h[j] = tf32_round(x[j]);
+                l[j] = x[j] - h[j];
+            }
+            *reinterpret_cast<float4*>(hi + r * ld_out + c) = make_float4(h[0], h[1], h[2], h[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) l[j] = tf32_round(x[j] - tf32_trunc(x[j]));
         }
-        *reinterpret_cast<float4*>(hi + r * ld_out + c) = make_float4(h[0], h[1], h[2], h[3]);
         *reinterpret_cast<float4*>(lo + r * ld_out + c) = make_float4(l[0], l[1], l[2], l[3]);
     }
 }
@@ -236,6 +245,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
             const float h = tf32_round(v);
             planes_hi[i] = h;
             planes_lo[i] = v - h;
+        } else if (planes_lo != nullptr) {   // the consumer reads C itself as the hi plane
+            planes_lo[i] = tf32_round(v - tf32_trunc(v));
         }
     }
 }
@@ -430,6 +441,10 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
     return p;
 }
 
+bool raw_hi_operand(const void* ptr, int64_t ld, const void* mask) {
+    return tuning(TFB_TUNE_RAW_HI) != 0 && mask == nullptr && aligned16(ptr) && (ld & 3) == 0;
+}
+
 bool gemm_uses_split_k(const GemmCall& c, int sm_count) {
     return !small_gemm_eligible(c) && gemm_plan(c, sm_count).split_k > 1;
 }
@@ -440,8 +455,11 @@ size_t gemm_workspace_bytes(const GemmCall& c, int sm_count) {
     const int64_t a_rows = c.a_kmajor ? c.M : c.K, a_cols = c.a_kmajor ? c.K : c.M;
     const int64_t b_rows = c.b_kmajor ? c.N : c.K, b_cols = c.b_kmajor ? c.K : c.N;
     if (c.in_dtype == TFB_DTYPE_F32) {
-        if (!c.a_presplit) bytes += (size_t)(2 * a_rows * round_up(a_cols, 4) * 4 + 256);
-        if (!c.b_presplit) bytes += (size_t)(2 * b_rows * round_up(b_cols, 4) * 4 + 256);
+        // two planes per operand, or the lo plane alone where the operand itself can serve as the hi plane
+        if (!c.a_presplit)
+            bytes += (size_t)((raw_hi_operand(c.A, c.lda, c.a_mask) ? 1 : 2) * a_rows * round_up(a_cols, 4) * 4 + 256);
+        if (!c.b_presplit)
+            bytes += (size_t)((raw_hi_operand(c.B, c.ldb, nullptr) ? 1 : 2) * b_rows * round_up(b_cols, 4) * 4 + 256);
     } else {
         if (!aligned16(c.A) || (c.lda & 7)) bytes += (size_t)(a_rows * round_up(a_cols, 8) * 2 + 256);
         if (!aligned16(c.B) || (c.ldb & 7)) bytes += (size_t)(b_rows * round_up(b_cols, 8) * 2 + 256);
@@ -486,7 +504,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     // ---- operand preparation into scratch -------------------------------------
     const void* a_ptr[2] = {c.A, nullptr};
     const void* b_ptr[2] = {c.B, nullptr};
-    int64_t lda = c.lda, ldb = c.ldb;
+    int64_t lda[2] = {c.lda, c.lda}, ldb[2] = {c.ldb, c.ldb};   // per plane
     const size_t need = gemm_workspace_bytes(c, st->sm_count);
     uint8_t* ws = nullptr;
     if (need > 0) {
@@ -515,19 +533,31 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
                 a_ptr[1] = static_cast<const float*>(c.A) + c.a_lo_off;
             } else {
                 const int64_t ldp = round_up(a_cols, 4);
-                float* hi = reinterpret_cast<float*>(carve((size_t)(2 * a_rows * ldp * 4)));
-                float* lo = hi + a_rows * ldp;
-                jobs[njobs++] = SplitJob{static_cast<const float*>(c.A), a_rows, a_cols, c.lda, c.a_mask, hi, lo, ldp};
-                a_ptr[0] = hi; a_ptr[1] = lo; lda = ldp;
+                if (raw_hi_operand(c.A, c.lda, c.a_mask)) {
+                    float* lo = reinterpret_cast<float*>(carve((size_t)(a_rows * ldp * 4)));
+                    jobs[njobs++] = SplitJob{static_cast<const float*>(c.A), a_rows, a_cols, c.lda, nullptr, nullptr, lo, ldp};
+                    a_ptr[1] = lo; lda[1] = ldp;
+                } else {
+                    float* hi = reinterpret_cast<float*>(carve((size_t)(2 * a_rows * ldp * 4)));
+                    float* lo = hi + a_rows * ldp;
+                    jobs[njobs++] = SplitJob{static_cast<const float*>(c.A), a_rows, a_cols, c.lda, c.a_mask, hi, lo, ldp};
+                    a_ptr[0] = hi; a_ptr[1] = lo; lda[0] = lda[1] = ldp;
+                }
             }
             if (c.b_presplit) {
                 b_ptr[1] = static_cast<const float*>(c.B) + c.b_lo_off;
             } else {
                 const int64_t ldp = round_up(b_cols, 4);
-                float* hi = reinterpret_cast<float*>(carve((size_t)(2 * b_rows * ldp * 4)));
-                float* lo = hi + b_rows * ldp;
-                jobs[njobs++] = SplitJob{static_cast<const float*>(c.B), b_rows, b_cols, c.ldb, nullptr, hi, lo, ldp};
-                b_ptr[0] = hi; b_ptr[1] = lo; ldb = ldp;
+                if (raw_hi_operand(c.B, c.ldb, nullptr)) {
+                    float* lo = reinterpret_cast<float*>(carve((size_t)(b_rows * ldp * 4)));
+                    jobs[njobs++] = SplitJob{static_cast<const float*>(c.B), b_rows, b_cols, c.ldb, nullptr, nullptr, lo, ldp};
+                    b_ptr[1] = lo; ldb[1] = ldp;
+                } else {
+                    float* hi = reinterpret_cast<float*>(carve((size_t)(2 * b_rows * ldp * 4)));
+                    float* lo = hi + b_rows * ldp;
+                    jobs[njobs++] = SplitJob{static_cast<const float*>(c.B), b_rows, b_cols, c.ldb, nullptr, hi, lo, ldp};
+                    b_ptr[0] = hi; b_ptr[1] = lo; ldb[0] = ldb[1] = ldp;
+                }
             }
             if (njobs == 1) {
                 rc = split_operand_on(st->sm_count, jobs[0].src, jobs[0].rows, jobs[0].cols, jobs[0].ld, jobs[0].mask,
@@ -550,7 +580,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
                                 static_cast<const uint16_t*>(c.A), (long long)a_rows, (long long)a_cols, (long long)c.lda, d,
                                 (long long)ldp);
                 if (rc != TFB_OK) return rc;
-                a_ptr[0] = d; lda = ldp;
+                a_ptr[0] = d; lda[0] = ldp;
             }
             if (!aligned16(c.B) || (c.ldb & 7)) {
                 const int64_t ldp = round_up(b_cols, 8);
@@ -559,7 +589,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
                                 static_cast<const uint16_t*>(c.B), (long long)b_rows, (long long)b_cols, (long long)c.ldb, d,
                                 (long long)ldp);
                 if (rc != TFB_OK) return rc;
-                b_ptr[0] = d; ldb = ldp;
+                b_ptr[0] = d; ldb[0] = ldp;
             }
         }
     }
@@ -593,7 +623,8 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     args.status = st->status;
     args.trace = g_gemm_trace.load(std::memory_order_relaxed);
     if (c.planes_hi != nullptr || c.planes_lo != nullptr) {
-        if (!f32 || c.out_dtype != TFB_DTYPE_F32 || (c.N & 3) || c.planes_hi == nullptr || c.planes_lo == nullptr ||
+        // planes_hi may be null: the consumer then reads C itself as the hi plane and only lo is written
+        if (!f32 || c.out_dtype != TFB_DTYPE_F32 || (c.N & 3) || c.planes_lo == nullptr ||
             !aligned16(c.planes_hi) || !aligned16(c.planes_lo) || c.K <= 0)
             return fail(TFB_ERR_UNSUPPORTED, "gemm: result planes need FP32 in and out, N a multiple of 4 and aligned planes");
         args.planes_hi = c.planes_hi;
@@ -612,15 +643,15 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     const int nplanes = f32 ? 2 : 1;
     for (int p = 0; p < nplanes; ++p) {
         if (c.a_kmajor)
-            rc = make_map(&maps[p], c.in_dtype, a_ptr[p], (uint64_t)c.K, (uint64_t)c.M, (uint64_t)lda * es, bk, kBlockM);
+            rc = make_map(&maps[p], c.in_dtype, a_ptr[p], (uint64_t)c.K, (uint64_t)c.M, (uint64_t)lda[p] * es, bk, kBlockM);
         else
-            rc = make_map(&maps[p], c.in_dtype, a_ptr[p], (uint64_t)c.M, (uint64_t)c.K, (uint64_t)lda * es, t_mn, bk, f32);
+            rc = make_map(&maps[p], c.in_dtype, a_ptr[p], (uint64_t)c.M, (uint64_t)c.K, (uint64_t)lda[p] * es, t_mn, bk, f32);
         if (rc != TFB_OK) return rc;
         if (c.b_kmajor)
-            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.K, (uint64_t)c.N, (uint64_t)ldb * es, bk,
+            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.K, (uint64_t)c.N, (uint64_t)ldb[p] * es, bk,
                           use_pair ? bn / 2 : bn);
         else
-            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.N, (uint64_t)c.K, (uint64_t)ldb * es, t_mn, bk, f32);
+            rc = make_map(&maps[2 + p], c.in_dtype, b_ptr[p], (uint64_t)c.N, (uint64_t)c.K, (uint64_t)ldb[p] * es, t_mn, bk, f32);
         if (rc != TFB_OK) return rc;
     }
     if (!f32) { maps[1] = maps[0]; maps[3] = maps[2]; }
@@ -642,7 +673,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     } else {
         args.split_stride = 0;
         args.c_tma = (c.out_dtype == TFB_DTYPE_F32 && aligned16(c.C) && (c.ldc & 3) == 0) ? 1 : 0;
-        if (args.planes_hi != nullptr && !args.c_tma)
+        if (args.planes_lo != nullptr && !args.c_tma)
             return fail(TFB_ERR_UNSUPPORTED, "gemm: result planes need a 16-byte aligned output with ldc a multiple of 4");
         if (args.c_tma) {
             rc = make_map(&maps[4], TFB_DTYPE_F32, c.C, (uint64_t)c.N, (uint64_t)c.M, (uint64_t)c.ldc * 4, 32, 32);

@@ -75,7 +75,8 @@ struct ConvGeom {
     int out_h, out_w;                 // extent of the position grid (= of the stored tensor)
     int cblks;                        // 32-channel blocks per tap
     int kw, taps;                     // filter width, number of taps (tap = ki * kw + kj)
-    int ay0, ay_step, ax0, ax_step;   // source row = position row + ay0 + ki * ay_step (x alike)
+    int ay0, ay_step, ax0, ax_step;   // source row = position row * sy + ay0 + ki * ay_step (x alike)
+    int sx, sy;                       // convolution stride (the source maps traverse with the same stride)
     int kblk_w_log2, kblk_h;          // kConvWgrad: K block = kblk_h rows of 2^kblk_w_log2 positions
     int kblk_x, kblk_y;               // K blocks per sample along x and y
     int n_samples;
@@ -220,12 +221,15 @@ __device__ __forceinline__ float tf32_hi(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return __uint_as_float(r);
 }
+// what kind::tf32 makes of a raw FP32 operand: the low 13 mantissa bits dropped
+__device__ __forceinline__ float tf32_cut(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
 // One warp's 32 rows x 32 columns (lane = row, v = its 32 values) to a row-major FP32 matrix with whole
 // 128-byte lines per store instruction: the block is transposed through the warp's swizzled staging
 // buffer (16-byte chunk j of row r at chunk j ^ (r & 7): conflict-free both ways), then lane
 // (r & 3, chunk) stores 16 bytes of row 4k + (lane >> 3). PLANE selects what is stored: 1 = the value
-// rounded to TF32 (hi), 2 = the value minus that (lo) — computed on the way into the buffer, so no
+// rounded to TF32 (hi), 2 = the value minus that (lo), 3 = the value minus its truncation to TF32, rounded
+// (the lo plane that goes with the value itself as hi) — computed on the way into the buffer, so no
 // second register array is needed. `m_rows` / `n_cols` clip at the matrix edge (n_cols is a multiple
 // of 4). The caller makes sure nothing else is still reading the buffer.
 template <int PLANE>
@@ -234,9 +238,14 @@ __device__ __forceinline__ void store32x32_via_staging(const float (&v)[32], uin
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         float4 x = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-        const float4 h = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
-        if (PLANE == 1) x = h;
-        else x = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+        if (PLANE == 3) {
+            x = make_float4(tf32_hi(x.x - tf32_cut(x.x)), tf32_hi(x.y - tf32_cut(x.y)), tf32_hi(x.z - tf32_cut(x.z)),
+                            tf32_hi(x.w - tf32_cut(x.w)));
+        } else {
+            const float4 h = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
+            if (PLANE == 1) x = h;
+            else x = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+        }
         *reinterpret_cast<float4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = x;
     }
     __syncwarp();
@@ -257,8 +266,12 @@ __device__ __forceinline__ void epilogue_store_planes32(const float (&v)[32], co
     // the warp's previous TMA store may still be reading the staging buffer
     if (lane == 0) tma_store_wait_read<0>();
     __syncwarp();
-    store32x32_via_staging<1>(v, staging, lane, args.planes_hi, args.ld_planes, row0, col0, args.M, args.N);
-    store32x32_via_staging<2>(v, staging, lane, args.planes_lo, args.ld_planes, row0, col0, args.M, args.N);
+    if (args.planes_hi != nullptr) {
+        store32x32_via_staging<1>(v, staging, lane, args.planes_hi, args.ld_planes, row0, col0, args.M, args.N);
+        store32x32_via_staging<2>(v, staging, lane, args.planes_lo, args.ld_planes, row0, col0, args.M, args.N);
+    } else {
+        store32x32_via_staging<3>(v, staging, lane, args.planes_lo, args.ld_planes, row0, col0, args.M, args.N);
+    }
 }
 
 __device__ __forceinline__ void tile_coords(int t, const GemmArgs& a, int& tm, int& tn) {
@@ -428,7 +441,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     if constexpr (CONV == kConvSpatial) {
                         const int tap = kb / cv.cblks, c0 = (kb - tap * cv.cblks) * 32;
                         const int ki = tap / cv.kw, kj = tap - ki * cv.kw;
-                        const int sy = cs_y0 + cv.ay0 + ki * cv.ay_step, sx = cs_x0 + cv.ax0 + kj * cv.ax_step;
+                        const int sy = cs_y0 * cv.sy + cv.ay0 + ki * cv.ay_step;
+                        const int sx = cs_x0 * cv.sx + cv.ax0 + kj * cv.ax_step;
                         tma_load_4d<PAIR>(a_hi, &tmA, c0, sx, sy, cs_n, fb);
                         tma_load_4d<PAIR>(a_lo, &tmA2, c0, sx, sy, cs_n, fb);
                         tma_load_3d<PAIR>(b_hi, &tmB, c0, tap, n0, fb);
@@ -438,6 +452,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         const int n = kb / per, r = kb - n * per;
                         const int by = r / cv.kblk_x, bx = r - by * cv.kblk_x;
                         const int px = bx << cv.kblk_w_log2, py = by * cv.kblk_h;
+                        const int qx = px * cv.sx, qy = py * cv.sy;   // the same block in the strided source
 #pragma unroll
                         for (int i = 0; i < kBlockM / T_MN; ++i) {
                             tma_load_4d<PAIR>(a_hi + i * (BK * 128), &tmA, m0 + i * T_MN, px, py, n, fb);
@@ -447,8 +462,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         for (int i = 0; i < BN_CTA / T_MN; ++i) {
                             // column boxes past the last tap read a sample index beyond the tensor: zeros
                             const int nn = cw_ok[i] ? n : cv.n_samples;
-                            tma_load_4d<PAIR>(b_hi + i * (BK * 128), &tmB, cw_c[i], px + cw_dx[i], py + cw_dy[i], nn, fb);
-                            tma_load_4d<PAIR>(b_lo + i * (BK * 128), &tmB2, cw_c[i], px + cw_dx[i], py + cw_dy[i], nn, fb);
+                            tma_load_4d<PAIR>(b_hi + i * (BK * 128), &tmB, cw_c[i], qx + cw_dx[i], qy + cw_dy[i], nn, fb);
+                            tma_load_4d<PAIR>(b_lo + i * (BK * 128), &tmB2, cw_c[i], qx + cw_dx[i], qy + cw_dy[i], nn, fb);
                         }
                     } else {
                     if constexpr (!A_MN) {
@@ -661,7 +676,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             epilogue_apply32(v, args, col0, row_bias);
                             // planes first (plain stores, the staging buffer is free again at once), then the
                             // asynchronous TMA store of the values themselves
-                            if (args.planes_hi != nullptr) epilogue_store_planes32(v, args, staging, lane, row0, col0);
+                            if (args.planes_lo != nullptr) epilogue_store_planes32(v, args, staging, lane, row0, col0);
                             if (c_tma) epilogue_store32_tma<S::STAGING_BUFS>(v, &tmC, staging, stage_buf, lane, row0, col0);
                             else epilogue_store32(v, args, row, col0);
                         }

@@ -91,8 +91,12 @@ struct GemmCall {
     // FP32 only: operands already split by gemm_split_operand (hi at ptr, lo at ptr + lo_off).
     bool a_presplit = false, b_presplit = false;
     int64_t a_lo_off = 0, b_lo_off = 0;   // elements
+    // With *_presplit: the hi plane is the operand itself (the tensor core drops its low 13 mantissa bits)
+    // and the lo plane is the residual against that truncation, as split_operand writes it for hi == nullptr.
+    bool a_raw_hi = false, b_raw_hi = false;
     // FP32 output only, N a multiple of 4: also write the TF32 hi / lo planes of the result (after bias
-    // and ReLU) with leading dimension N, for a product that consumes this output next.
+    // and ReLU) with leading dimension N, for a product that consumes this output next. planes_lo alone:
+    // that product reads C itself as its hi plane (raw-hi form, above) and only the residual is written.
     float* planes_hi = nullptr;
     float* planes_lo = nullptr;
     int force_bn = 0;          // 0 = choose; else 64 / 128 / 256
@@ -107,6 +111,9 @@ int small_gemm_run(const GemmCall& call, cudaStream_t stream);
 // True when gemm_run would split this call's contraction between CTAs (its epilogue then runs in the
 // reduction kernel).
 bool gemm_uses_split_k(const GemmCall& call, int sm_count);
+// True when an FP32 operand at `ptr` with leading dimension `ld` (and no element mask) can be its own hi
+// plane: 16-byte aligned, ld a multiple of 4, and the RAW_HI knob on.
+bool raw_hi_operand(const void* ptr, int64_t ld, const void* mask);
 // Same, with the device facts (SM count, status word) supplied by the caller instead of the
 // lazily created per-device state.
 int gemm_run_on(const GemmCall& call, cudaStream_t stream, const DeviceState* st);
@@ -122,8 +129,10 @@ int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t inner, uint
 
 // FP32 tensor map of rank 2..5: dims[0] is the contiguous dimension, strides_bytes[i] is the stride of
 // dims[i + 1] (multiples of 16), box the tile; 128-byte swizzle (with 32-byte atoms if atom32).
+// elem_strides (optional): traversal stride per dimension — a box of extent b then delivers every
+// stride-th element, ceil(b / stride) of them.
 int make_map_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-                const uint32_t* box, bool atom32);
+                const uint32_t* box, bool atom32, const uint32_t* elem_strides = nullptr);
 
 // Splits a row-major FP32 matrix (rows x cols, leading dimension ld) into TF32 hi / lo
 // planes with leading dimension ld_out (multiple of 4, padding zero-filled).
@@ -143,6 +152,7 @@ struct SavedPlanes {
     const float* hi = nullptr;
     const float* lo = nullptr;
     int64_t ld = 0;
+    bool raw_hi = false;   // hi is the operand itself, lo its residual against truncation (GemmCall::a_raw_hi)
 };
 // linear_backward with X and / or W optionally given as saved hi / lo planes (FP32 only; X and W are
 // ignored for the operands whose planes are supplied).
@@ -151,15 +161,18 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
                          cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved);
 
 // ---------------------------------------------------------------------------
-// nn::Conv2d (conv.cu: gather kernel, entry points; conv_tma.cu: stride-1 path on the GEMM kernel)
+// nn::Conv2d (conv.cu: gather kernel, entry points; conv_tma.cu: TMA-fed path on the GEMM kernel)
 // ---------------------------------------------------------------------------
 struct ConvShape {
     int64_t N, Cin, H, W, Cout, kH, kW, sh, sw, ph, pw, dh, dw, outH, outW;
 };
-// True when a product of this convolution should run on the TMA-fed path: stride 1, extents within
-// tensor-map limits, and enough channels in the contraction (forward and weight gradient: Cin; input
-// gradient: Cout) to fill the 32-channel K blocks.
-bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels);
+// True when a product of this convolution should run on the TMA-fed path: extents within tensor-map
+// limits, enough channels in the contraction (forward and weight gradient: Cin; input gradient: Cout) to
+// fill the 32-channel K blocks, and a stride the feed can express — any stride whose tile stays within a
+// 256-element box for the forward product and the weight gradient (the tensor map traverses the source
+// with the convolution's stride), stride 1 for the input gradient (`input_gradient`; its gather form reads
+// rows (y + pad - ki * dilation) / stride, which is not a box).
+bool conv_tma_eligible(const ConvShape& s, int64_t contraction_channels, bool input_gradient = false);
 // True when the debugging override asks for the TMA-fed path wherever it is possible.
 bool conv_tma_forced();
 int conv_tma_forward(const float* x, const float* w, const float* bias, float* out, const ConvShape& s, bool relu,

@@ -191,9 +191,11 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
     gx.A = gw.A = reinterpret_cast<const void*>(static_cast<uintptr_t>(256));
     if (wsaved.hi != nullptr) {
         gx.B = wsaved.hi; gx.ldb = wsaved.ld; gx.b_presplit = true; gx.b_lo_off = wsaved.lo - wsaved.hi;
+        gx.b_raw_hi = wsaved.raw_hi;
     }
     if (xs.hi != nullptr) {
         gw.B = xs.hi; gw.ldb = xs.ld; gw.b_presplit = true; gw.b_lo_off = xs.lo - xs.hi;
+        gw.b_raw_hi = xs.raw_hi;
     }
 
     const size_t dz_bytes = align256((size_t)(batch * ldz) * (f32 ? 8 : 2));

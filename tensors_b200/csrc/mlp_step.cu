@@ -339,8 +339,11 @@ int launch_update(tfb_mlp* m, int world_in_kernel, float lr, float mu, cudaStrea
 int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,
                      cudaStream_t stream) {
     const int L = m->L;
-    int rc = split_operand(m->params, 1, m->numel, m->numel, nullptr, m->pplanes, m->pplanes + m->numel, m->numel,
-                           stream);
+    // Where an operand can be its own hi plane (aligned, width a multiple of 4) only its lo plane is written:
+    // the parameters as one flat vector, the batch, and each hidden activation.
+    const bool raw_params = raw_hi_operand(m->params, m->numel, nullptr);
+    int rc = split_operand(m->params, 1, m->numel, m->numel, nullptr, raw_params ? nullptr : m->pplanes,
+                           m->pplanes + m->numel, m->numel, stream);
     if (rc != TFB_OK) return rc;
     std::vector<SavedPlanes> xs((size_t)L), ws((size_t)L);
     DeviceState* st = nullptr;
@@ -348,6 +351,7 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
     if (rc != TFB_OK) return rc;
     const int fuse = tuning(TFB_TUNE_FUSE_PLANES);
     bool planes_ready = false;   // did the product of the layer below already write this layer's input planes?
+    bool ready_raw = false;      // ... in the raw-hi form (lo plane only)?
     for (int i = 0; i < L; ++i) {
         const int64_t in_f = m->dims[(size_t)i], out_f = m->dims[(size_t)i + 1];
         const float* in = i == 0 ? X : m->act[(size_t)i];
@@ -356,15 +360,18 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         float* xl = xh + rows * ldx;
         // The planes of a hidden layer's input were written by the product that made it (its epilogue);
         // only the batch itself, and inputs whose width is not a multiple of 4, are split here.
+        bool raw_in = planes_ready ? ready_raw : raw_hi_operand(in, in_f, nullptr);
         if (!planes_ready) {
-            rc = split_operand(in, rows, in_f, in_f, nullptr, xh, xl, ldx, stream);
+            rc = split_operand(in, rows, in_f, in_f, nullptr, raw_in ? nullptr : xh, xl, ldx, stream);
             if (rc != TFB_OK) return rc;
         }
-        xs[(size_t)i].hi = xh; xs[(size_t)i].lo = xl; xs[(size_t)i].ld = ldx;
+        xs[(size_t)i].hi = raw_in ? in : xh; xs[(size_t)i].lo = xl; xs[(size_t)i].ld = ldx;   // raw: in_f == ldx
+        xs[(size_t)i].raw_hi = raw_in;
         if (m->wplanes[(size_t)i] == nullptr) {
-            ws[(size_t)i].hi = m->pplanes + m->w_off[(size_t)i];
+            ws[(size_t)i].hi = (raw_params ? m->params : m->pplanes) + m->w_off[(size_t)i];
             ws[(size_t)i].lo = m->pplanes + m->numel + m->w_off[(size_t)i];
             ws[(size_t)i].ld = in_f;
+            ws[(size_t)i].raw_hi = raw_params;
         } else {
             float* wh = m->wplanes[(size_t)i];
             float* wl = wh + out_f * ldx;
@@ -374,7 +381,9 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         }
         GemmCall c;
         c.A = xs[(size_t)i].hi; c.a_presplit = true; c.a_lo_off = xs[(size_t)i].lo - xs[(size_t)i].hi;
+        c.a_raw_hi = xs[(size_t)i].raw_hi;
         c.B = ws[(size_t)i].hi; c.b_presplit = true; c.b_lo_off = ws[(size_t)i].lo - ws[(size_t)i].hi;
+        c.b_raw_hi = ws[(size_t)i].raw_hi;
         c.C = m->act[(size_t)i + 1];
         c.M = rows; c.N = out_f; c.K = in_f;
         c.lda = ldx; c.ldb = ws[(size_t)i].ld; c.ldc = out_f;
@@ -388,8 +397,10 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         planes_ready = false;
         if (i + 1 < L && (out_f & 3) == 0 &&
             (fuse == 2 || (fuse == 1 && (gemm_uses_split_k(c, st->sm_count) || small_gemm_eligible(c))))) {
-            c.planes_hi = m->xplanes[(size_t)i + 1];
-            c.planes_lo = c.planes_hi + rows * out_f;
+            // raw-hi form where the output itself can be the next product's hi plane
+            ready_raw = raw_hi_operand(c.C, out_f, nullptr);
+            c.planes_hi = ready_raw ? nullptr : m->xplanes[(size_t)i + 1];
+            c.planes_lo = m->xplanes[(size_t)i + 1] + rows * out_f;
             planes_ready = true;
         }
         rc = gemm_run(c, stream);

@@ -42,6 +42,12 @@ struct SmallArgs {
     float* planes_lo;
 };
 
+__device__ __forceinline__ float tf32_rn(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
 __device__ __forceinline__ float ld_shared_cluster_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -121,11 +127,11 @@ __global__ void __launch_bounds__(256) small_gemm_kernel(const SmallArgs a) {
     if (a.relu) acc = acc > 0.f ? acc : 0.f;
     a.C[(long long)m * a.ldc + n] = acc;
     if (a.planes_hi != nullptr) {
-        uint32_t r;
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(acc));
-        const float hi = __uint_as_float(r);
+        const float hi = tf32_rn(acc);
         a.planes_hi[(long long)m * a.N + n] = hi;
         a.planes_lo[(long long)m * a.N + n] = acc - hi;
+    } else if (a.planes_lo != nullptr) {   // the consumer reads C itself as the hi plane
+        a.planes_lo[(long long)m * a.N + n] = tf32_rn(acc - __uint_as_float(__float_as_uint(acc) & 0xFFFFE000u));
     }
 }
 
@@ -160,9 +166,9 @@ bool small_gemm_eligible(const GemmCall& c) {
 int small_gemm_run(const GemmCall& c, cudaStream_t stream) {
     SmallArgs a;
     a.A = static_cast<const float*>(c.A);
-    a.A_lo = c.a_presplit ? a.A + c.a_lo_off : nullptr;
+    a.A_lo = c.a_presplit && !c.a_raw_hi ? a.A + c.a_lo_off : nullptr;   // a raw hi plane is the value itself
     a.B = static_cast<const float*>(c.B);
-    a.B_lo = c.b_presplit ? a.B + c.b_lo_off : nullptr;
+    a.B_lo = c.b_presplit && !c.b_raw_hi ? a.B + c.b_lo_off : nullptr;
     a.C = static_cast<float*>(c.C);
     a.M = (int)c.M; a.N = (int)c.N; a.K = (int)c.K;
     // a_kmajor: A stored [M][K] (K contiguous); else stored [K][M]
@@ -174,8 +180,8 @@ int small_gemm_run(const GemmCall& c, cudaStream_t stream) {
     a.ldc = c.ldc;
     a.bias = c.bias; a.bias_mode = c.bias_mode; a.relu = c.relu ? 1 : 0;
     a.planes_hi = c.planes_hi; a.planes_lo = c.planes_lo;
-    if ((a.planes_hi == nullptr) != (a.planes_lo == nullptr))
-        return fail(TFB_ERR_INVALID_ARG, "gemm: both result planes or neither");
+    if (a.planes_hi != nullptr && a.planes_lo == nullptr)
+        return fail(TFB_ERR_INVALID_ARG, "gemm: a hi result plane without its lo plane");
     // one block of the cluster per 128 elements of K, at most eight (the portable cluster size)
     int splits = (int)((c.K + kChunk - 1) / kChunk);
     if (splits > kMaxSplit) splits = kMaxSplit;

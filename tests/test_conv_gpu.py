@@ -48,10 +48,10 @@ def conv_backward(x, w, g, stride=(1, 1), pad=(0, 0), dil=(1, 1)):
 
 @pytest.fixture(params=["default", "tma_feed", "gather_kernel"])
 def feed(request):
-    """By default a stride-1 product with at least 16 contraction channels runs on the TMA-fed GEMM
-    kernel, short contractions (forward with Cin*kH*kW <= 128, input gradient with Cin <= 4, weight
+    """By default a product with at least 16 contraction channels runs on the TMA-fed GEMM kernel (forward
+    and weight gradient at any stride whose tile fits a 256-element box, input gradient at stride 1), short contractions (forward with Cin*kH*kW <= 128, input gradient with Cin <= 4, weight
     gradient with Cin*kH*kW < 32) on the CUDA-core kernels and everything else on the kernel with software gather producers.
-    The CONV_TMA knob at 2 sends every stride-1 product to the first; CONV_TMA = 0 with CONV_DIRECT = 0
+    The CONV_TMA knob at 2 sends every product the feed can express to the first; CONV_TMA = 0 with CONV_DIRECT = 0
     everything to the last, so each kernel gets every case it can take."""
     def get(knob):
         v = ctypes.c_int(0)
@@ -140,6 +140,16 @@ def test_forward_against_reference_golden(golden):
     (1, 40, 9, 7, 150, 2, 3, (1, 1), (0, 2), (1, 1)),
     (3, 70, 16, 16, 70, 3, 3, (1, 1), (1, 1), (1, 1)),
     (2, 4, 6, 6, 5, 3, 3, (1, 1), (0, 0), (1, 1)),
+    # strides with enough channels for the TMA feed by default (forward and weight gradient; the input
+    # gradient of a strided layer stays on the gather kernel): odd extents, dilation, a stride per axis,
+    # an output row wider than one tile, a stride whose box would exceed 256 elements (gather kernel)
+    (2, 32, 33, 31, 48, 3, 3, (2, 2), (1, 1), (1, 1)),
+    (1, 64, 56, 56, 64, 3, 3, (2, 2), (1, 1), (1, 1)),
+    (2, 24, 20, 70, 40, 3, 3, (1, 3), (1, 0), (1, 1)),
+    (2, 16, 19, 19, 24, 3, 3, (2, 2), (2, 2), (2, 2)),
+    (1, 16, 8, 300, 8, 1, 3, (1, 2), (0, 1), (1, 1)),
+    (1, 16, 4, 400, 8, 1, 1, (1, 3), (0, 0), (1, 1)),
+    (2, 20, 30, 30, 36, 4, 4, (4, 4), (0, 0), (1, 1)),
 ])
 def test_forward_backward_against_oracle(oracle, case, feed):
     N, Cin, H, W, Cout, kH, kW, stride, pad, dil = case
@@ -232,6 +242,29 @@ def test_index_map_through_the_production_kernels_bit_exact(oracle, layer):
             nn, pp = np.nonzero(src >= 0)
             want[nn, src[nn, pp] - nn * per] = val[nn, pp]
         assert np.array_equal(gi.reshape(N, per).astype(np.int64), want), (layer, tap)
+
+
+def test_index_map_of_a_strided_layer_on_the_tma_feed_bit_exact(oracle):
+    # The same scheme for a layer whose stride and dilation are expressed by the tensor map itself
+    # (traversal stride of the box, tap offsets added to its start): 32 channels, 3x3, stride 2, dilation 2,
+    # pad 2, odd extents. Forward only: the input gradient of a strided layer runs on the gather kernel, whose
+    # index function is pinned separately.
+    N, Cin, H, W, Cout, k, st, pad, dil = 2, 32, 21, 19, 96, 3, 2, 2, 2
+    oH, oW = out_dim(H, k, st, pad, dil), out_dim(W, k, st, pad, dil)
+    K, P = Cin * k * k, oH * oW
+    per = Cin * H * W
+    x = _own_index_tensor(N, Cin, H, W)
+    want_map = oracle.im2col_index_range(0, N * K * P, Cin, H, W, k, k, st, st, pad, pad, dil, dil).reshape(N, K, P)
+    sample_base = (np.arange(N, dtype=np.int64) * per).reshape(N, 1, 1)
+    want_val = np.where(want_map >= 0, want_map - sample_base + 1, 0)
+    for first in range(0, K, Cout):
+        taps = np.arange(first, min(first + Cout, K))
+        w = np.zeros((Cout, K), np.float32)
+        w[np.arange(len(taps)), taps] = 1.0
+        y = conv_forward(x, w.reshape(Cout, Cin, k, k), None, stride=(st, st), pad=(pad, pad), dil=(dil, dil))
+        y = y.reshape(N, Cout, P)
+        assert np.array_equal(y[:, :len(taps)].astype(np.int64), want_val[:, taps]), first
+        assert not y[:, len(taps):].any()
 
 
 def test_config3_full_size_properties_and_sampled_oracle(oracle):

@@ -441,3 +441,38 @@ def test_few_rows_long_contraction_on_the_cuda_core_kernel(oracle, shape, trans_
                                          capi.EPI_BIAS_COL | capi.EPI_RELU, stream_ptr()))
         assert_device_ok()
         assert torch.equal(C2, C)
+
+
+@pytest.mark.parametrize("raw_hi", [1, 0])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True), (True, True)])
+def test_operand_as_its_own_hi_plane(oracle, raw_hi, trans_a, trans_b, product_path):
+    # kind::tf32 drops the low 13 mantissa bits of what it reads, so an aligned FP32 operand serves as its
+    # own hi plane and only lo = x - trunc(x) is written (knob RAW_HI, default off). Both forms must sit at
+    # the same distance from an FP64 product — a lo plane that does not match the hi plane it is used with
+    # would show as an error near 1e-3 — for aligned operands, operands with padded rows whose padding holds
+    # garbage, rows that are not a multiple of 16 bytes, and a base pointer off the 16-byte grid.
+    if product_path == "tensor_cores_only":
+        pytest.skip("none of these shapes is in the CUDA-core window")
+    old = ctypes.c_int(0)
+    capi.check(lib.tfb_get_tuning(capi.TUNE_RAW_HI, ctypes.byref(old)))
+    capi.check(lib.tfb_set_tuning(capi.TUNE_RAW_HI, raw_hi))
+    try:
+        for (M, N, K, pad_a, pad_b, shift) in ((384, 320, 512, 0, 0, 0), (300, 200, 100, 8, 4, 0), (130, 70, 90, 3, 1, 0),
+                                                 (256, 256, 256, 4, 4, 1), (1024, 1024, 1100, 0, 0, 0)):
+            a, b = refdata.uniform(31, (M, K)), refdata.uniform(32, (K, N))
+            sa, sb = (a.T if trans_a else a), (b.T if trans_b else b)
+            hold_a = np.full((sa.shape[0], sa.shape[1] + pad_a), np.float32(1e30))
+            hold_b = np.full((sb.shape[0], sb.shape[1] + pad_b), np.float32(-1e30))
+            hold_a[:, :sa.shape[1]] = sa
+            hold_b[:, :sb.shape[1]] = sb
+            # `shift` floats in front of the matrix take its base off the 16-byte grid
+            fa = torch.cat([torch.zeros(shift, device="cuda"), dev(hold_a).reshape(-1)])
+            fb = torch.cat([torch.zeros(shift, device="cuda"), dev(hold_b).reshape(-1)])
+            C = gemm_ex(fa[shift:], fb[shift:], M, N, K, trans_a, trans_b, lda=hold_a.shape[1], ldb=hold_b.shape[1])
+            assert_device_ok()
+            got = C.cpu().numpy()
+            exact = a.astype(np.float64) @ b.astype(np.float64)
+            assert rel_err(got, exact) < 4e-6, (M, N, K, pad_a, pad_b, shift)
+            assert rel_err(got, oracle.matmul(a, b)) < FP32_TOL
+    finally:
+        capi.check(lib.tfb_set_tuning(capi.TUNE_RAW_HI, old.value))

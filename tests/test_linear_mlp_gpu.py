@@ -243,6 +243,37 @@ def test_mlp_steps_do_not_depend_on_programmatic_dependent_launch():
     assert out[0][1] == out[1][1]
 
 
+def test_mlp_step_with_operands_as_their_own_hi_planes(oracle):
+    # The step keeps the batch, the parameters and the hidden activations as their own hi planes and
+    # writes lo planes only (knob RAW_HI, default off). With the knob off it writes round-to-nearest
+    # hi / lo pairs. Both must give the oracle's loss and gradients; they need not agree bit for bit.
+    import ctypes
+    from tensors_b200.mlp import MLP
+    dims = (784, 256, 192, 10)
+    ws = [refdata.linear_weight(dims[i], dims[i + 1]) for i in range(3)]
+    x, lab = refdata.mnist_like(17, (1500, 784)), refdata.labels(18, 1500)
+    X, L = dev(x), torch.from_numpy(lab).cuda()
+    ol, odw, odb = oracle.mlp_grads(x, lab, ws, bs=[np.zeros(d, np.float32) for d in dims[1:]])
+    old = ctypes.c_int(0)
+    capi.check(lib.tfb_get_tuning(capi.TUNE_RAW_HI, ctypes.byref(old)))
+    try:
+        for raw in (1, 0):
+            capi.check(lib.tfb_set_tuning(capi.TUNE_RAW_HI, raw))
+            m = MLP(dims, ws, max_rows=1500)
+            m.forward_backward(X, L)
+            assert_device_ok()
+            assert abs(local_loss(m) - ol) < 1e-5, raw
+            # the head: no ReLU mask behind it, so no ties
+            assert rel_err(m.weight(2, m.grads).cpu().numpy(), odw[2]) < 2e-5, raw
+            assert rel_err(m.bias(2, m.grads).cpu().numpy(), odb[2]) < 2e-5, raw
+            for i in (0, 1):   # hidden layers: a unit at a ReLU tie may move one row (see the invariance test)
+                got = m.weight(i, m.grads).cpu().numpy()
+                rows = np.linalg.norm(got - odw[i], axis=1) / (np.linalg.norm(odw[i], axis=1) + 1e-30)
+                assert int((rows > 5e-5).sum()) <= 2, (raw, i, np.sort(rows)[-4:])
+    finally:
+        capi.check(lib.tfb_set_tuning(capi.TUNE_RAW_HI, old.value))
+
+
 def test_mlp_full_batch_data_parallel_invariance(oracle):
     # The named configuration at its full global batch of 8192 rows. The batch is cut into G row shards
     # as G data-parallel ranks would hold them; each shard's gradient is scaled by the GLOBAL batch, so
