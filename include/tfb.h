@@ -83,6 +83,10 @@ const char* tfb_last_error_string(void);
  *                   where it should matter most: an 8192-cubed product at the power cap runs at ~5 % lower
  *                   clocks when the operand paths carry the 13 mantissa bits that rounded planes hold as
  *                   zeros (216 against 223-230 TFLOP/s on one GPU, alternating runs)
+ *   CLUSTER_K       1 (default) = an FP32 product that would run as two K splits of 128 x 128 tiles with at
+ *                   most one tile per SM pair runs each tile on a cluster of two CTAs, which add their
+ *                   halves through distributed shared memory (no partial sums in scratch, no reduction
+ *                   kernel; same bits as the two-kernel form); 0 = partial sums + reduction kernel
  *   FUSE_PLANES     which products of the MLP step also write the TF32 hi / lo planes of their result for
  *                   the next layer instead of leaving that to a separate pass: 0 = none, 1 (default) =
  *                   the split-K products (their reduction kernel writes the planes), 2 = all of them
@@ -101,7 +105,8 @@ const char* tfb_last_error_string(void);
 #define TFB_TUNE_GEMM_GROUP_M 10
 #define TFB_TUNE_SMALL_GEMM 11
 #define TFB_TUNE_RAW_HI 12
-#define TFB_TUNE_COUNT 13
+#define TFB_TUNE_CLUSTER_K 13
+#define TFB_TUNE_COUNT 14
 int tfb_set_tuning(int knob, int value);
 int tfb_get_tuning(int knob, int* value_out);
 

@@ -9,7 +9,7 @@ DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 EPI_NONE, EPI_BIAS_COL, EPI_BIAS_ROW, EPI_RELU = 0, 1, 2, 4
 (TUNE_GEMM_TILE_N, TUNE_GEMM_PAIR, TUNE_GEMM_SPLIT_K, TUNE_GEMM_CHUNK_KB, TUNE_CONV_TMA, TUNE_CONV_DIRECT,
  TUNE_CONV_PAIR, TUNE_HOST_PANEL_ROWS, TUNE_PDL, TUNE_FUSE_PLANES, TUNE_GEMM_GROUP_M, TUNE_SMALL_GEMM,
- TUNE_RAW_HI) = range(13)
+ TUNE_RAW_HI, TUNE_CLUSTER_K) = range(14)
 
 
 class TfbError(RuntimeError):

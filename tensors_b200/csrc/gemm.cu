@@ -262,12 +262,13 @@ int grid_for(long long work_items, int block, int sm_count) {
 // ---------------------------------------------------------------------------
 // Launch
 // ---------------------------------------------------------------------------
-// `workers`: CTAs of the persistent grid, or CTA pairs (clusters of two) when PAIR.
-template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR>
+// `workers`: CTAs of the persistent grid, or clusters of two when PAIR (one 256-row tile per pair) or KCL
+// (one tile per cluster, its contraction shared by the two CTAs).
+template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR, bool KCL = false>
 int launch_variant(const CUtensorMap maps[5], const GemmArgs& args, int workers, cudaStream_t stream) {
     using S = GemmSmem<KIND, BN, STAGES, PAIR>;
     static_assert(S::TOTAL <= 232448, "stage ring + staging exceed the 227 KB shared-memory limit");
-    auto kern = gemm_tcgen05_kernel<KIND, BN, STAGES, A_MN, B_MN, PAIR>;
+    auto kern = gemm_tcgen05_kernel<KIND, BN, STAGES, A_MN, B_MN, PAIR, kConvNone, KCL>;
     // Once per (kernel variant, device); several host threads may get here at the same time.
     static std::atomic<bool> attr_set[64];
     int dev = 0;
@@ -278,13 +279,13 @@ int launch_variant(const CUtensorMap maps[5], const GemmArgs& args, int workers,
         attr_set[dev].store(true, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(PAIR ? 2 * workers : workers));
+    cfg.gridDim = dim3((unsigned)((PAIR || KCL) ? 2 * workers : workers));
     cfg.blockDim = dim3((unsigned)gemm_threads(KIND));
     cfg.dynamicSmemBytes = S::TOTAL;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+    attr[0].val.clusterDim.x = (PAIR || KCL) ? 2 : 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     // The kernel's prologue (barriers, tensor memory, descriptor prefetch) may overlap the tail of the
@@ -297,13 +298,13 @@ int launch_variant(const CUtensorMap maps[5], const GemmArgs& args, int workers,
     return TFB_OK;
 }
 
-template <int KIND, int BN, int STAGES, bool PAIR>
+template <int KIND, int BN, int STAGES, bool PAIR, bool KCL = false>
 int launch_layout(bool a_mn, bool b_mn, const CUtensorMap maps[5], const GemmArgs& args, int workers,
                   cudaStream_t stream) {
-    if (!a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, false, false, PAIR>(maps, args, workers, stream);
-    if (!a_mn && b_mn) return launch_variant<KIND, BN, STAGES, false, true, PAIR>(maps, args, workers, stream);
-    if (a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, true, false, PAIR>(maps, args, workers, stream);
-    return launch_variant<KIND, BN, STAGES, true, true, PAIR>(maps, args, workers, stream);
+    if (!a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, false, false, PAIR, KCL>(maps, args, workers, stream);
+    if (!a_mn && b_mn) return launch_variant<KIND, BN, STAGES, false, true, PAIR, KCL>(maps, args, workers, stream);
+    if (a_mn && !b_mn) return launch_variant<KIND, BN, STAGES, true, false, PAIR, KCL>(maps, args, workers, stream);
+    return launch_variant<KIND, BN, STAGES, true, true, PAIR, KCL>(maps, args, workers, stream);
 }
 
 int choose_bn(int64_t M, int64_t N, int sm_count) {
@@ -360,6 +361,9 @@ struct GemmPlan {
     int64_t rows_per_split = 0;   // rows of one split's partial output (whole tiles)
     int64_t ld_partial = 0;       // its leading dimension (multiple of 4)
     size_t partial_bytes = 0;
+    // The two halves of every tile's contraction run in the two CTAs of a cluster and are added on chip
+    // (KCL kernels): no partial sums in scratch, no reduction kernel.
+    bool cluster_k = false;
 };
 
 GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
@@ -437,8 +441,19 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
         } else if (sp_one.ok) {
             apply(sp_one, false, bn1);
         }
+        // Two splits of FP32 128 x 128 tiles, at most one tile per SM pair: the halves meet on chip.
+        const long long tiles_now = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + p.bn - 1) / p.bn);
+        if (f32 && !p.pair && p.bn == 128 && p.split_k == 2 && tiles_now * 2 <= sm_count &&
+            tuning(TFB_TUNE_CLUSTER_K) != 0) {
+            p.cluster_k = true;
+            p.partial_bytes = 0;
+        }
     }
     return p;
+}
+
+bool gemm_uses_cluster_k(const GemmCall& c, int sm_count) {
+    return !small_gemm_eligible(c) && gemm_plan(c, sm_count).cluster_k;
 }
 
 bool raw_hi_operand(const void* ptr, int64_t ld, const void* mask) {
@@ -446,7 +461,9 @@ bool raw_hi_operand(const void* ptr, int64_t ld, const void* mask) {
 }
 
 bool gemm_uses_split_k(const GemmCall& c, int sm_count) {
-    return !small_gemm_eligible(c) && gemm_plan(c, sm_count).split_k > 1;
+    if (small_gemm_eligible(c)) return false;
+    const GemmPlan p = gemm_plan(c, sm_count);
+    return p.split_k > 1 && !p.cluster_k;
 }
 
 size_t gemm_workspace_bytes(const GemmCall& c, int sm_count) {
@@ -657,7 +674,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
     if (!f32) { maps[1] = maps[0]; maps[3] = maps[2]; }
     // FP32 output with 16-byte aligned rows leaves through TMA stores of 32 x 32 blocks.
     float* partial = nullptr;
-    if (plan.split_k > 1) {
+    if (plan.split_k > 1 && !plan.cluster_k) {
         // Units write raw FP32 partial sums; the epilogue proper runs in the reduction kernel.
         partial = reinterpret_cast<float*>(carve(plan.partial_bytes));
         args.C = partial;
@@ -693,6 +710,9 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
         const int pairs = units < max_pairs ? (int)units : max_pairs;
         if (f32) rc = launch_layout<kKindTF32x3, 256, 3, true>(a_mn, b_mn, maps, args, pairs, stream);
         else rc = launch_layout<kKind16, 256, 6, true>(a_mn, b_mn, maps, args, pairs, stream);
+    } else if (plan.cluster_k) {
+        args.cluster_k = 1;
+        rc = launch_layout<kKindTF32x3, 128, 3, false, true>(a_mn, b_mn, maps, args, args.num_tiles, stream);
     } else if (f32) {
         if (bn == 256) rc = launch_layout<kKindTF32x3, 256, 2, false>(a_mn, b_mn, maps, args, grid, stream);
         else if (bn == 128) rc = launch_layout<kKindTF32x3, 128, 3, false>(a_mn, b_mn, maps, args, grid, stream);
@@ -702,7 +722,7 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
         else if (bn == 128) rc = launch_layout<kKind16, 128, 6, false>(a_mn, b_mn, maps, args, grid, stream);
         else rc = launch_layout<kKind16, 64, 8, false>(a_mn, b_mn, maps, args, grid, stream);
     }
-    if (rc != TFB_OK || plan.split_k == 1) return rc;
+    if (rc != TFB_OK || plan.split_k == 1 || plan.cluster_k) return rc;
     const long long total = (long long)c.M * c.N;
     return launch_pdl(splitk_reduce_kernel, dim3((unsigned)grid_for(total, 256, st->sm_count)), dim3(256), 0, stream,
                       (const float*)partial, plan.split_k, (long long)c.M, (long long)c.N, (long long)plan.ld_partial,

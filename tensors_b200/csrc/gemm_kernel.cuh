@@ -86,6 +86,7 @@ struct GemmArgs {
     int M, N, K;
     int tiles_m, tiles_n, num_tiles, k_blocks;
     int chunk_kb;         // K blocks accumulated in TMEM before the epilogue drains them
+    int cluster_k;        // KCL kernels: 1 (documentation of the mode; the kernel variant decides)
     int split_k;          // work units per output tile; unit u = split * num_tiles + tile
     int kb_per_split;     // K blocks per unit (the last split may hold fewer)
     long long split_stride;   // elements between the partial outputs of consecutive splits
@@ -300,7 +301,14 @@ __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t cta
         ::"r"(bar), "h"(cta_mask) : "memory");
 }
 
-template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR, int CONV = kConvNone>
+// KCL ("K split over a cluster"): the two CTAs of a cluster each accumulate half of ONE output tile's
+// contraction (split_k = 2, at most one tile per cluster: no tile loop) and then exchange halves of their
+// partial tiles through distributed shared memory: CTA k finishes columns [k * BN / 2, (k + 1) * BN / 2) —
+// the epilogue warps that hold the other half send it into the peer's epilogue staging buffers (idle until
+// the stores begin), the warps that hold its own half add what the peer sent (a sum of two terms: the same
+// bits as the split-K reduction kernel's) and run the epilogue. No partial sums in global memory, no
+// second kernel, and both CTAs store. FP32 path, single-CTA MMAs.
+template <int KIND, int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR, int CONV = kConvNone, bool KCL = false>
 __global__ void __launch_bounds__(gemm_threads(KIND), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
@@ -326,6 +334,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     static_assert(CONV == kConvNone || TF32, "the convolution feeds exist for FP32 operands only");
     static_assert(CONV != kConvSpatial || (!A_MN && !B_MN), "spatial feed: both operands K-major");
     static_assert(CONV != kConvWgrad || (A_MN && B_MN), "weight-gradient feed: both operands MN-major");
+    static_assert(!KCL || (TF32 && !PAIR && CONV == kConvNone), "cluster split-K: FP32 path, single-CTA MMAs");
+    static_assert(!KCL || (EPI_WARPS == 8 && COLS * 32 * 4 == 2 * S::STAGING_BUFS * 4096),
+                  "cluster split-K: a warp's 32 x COLS partial block must fill two staging buffers");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -340,14 +351,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint8_t* after_bars = smem_gen + STAGES * S::STAGE_BYTES + S::STAGING_BYTES + 8 * (2 * STAGES + 4);
     volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(after_bars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(after_bars + 4);
+    // KCL: the peer's half of my columns has landed in my staging buffers
+    const uint32_t xdata_bar = bars + 8u * (2 * STAGES + 4) + 8u;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const bool tracing = args.trace != nullptr && blockIdx.x == 0;
     if (tracing && threadIdx.x == 0) args.trace[0] = global_timer_ns();
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;   // 0 = leader of the pair
-    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-    const int num_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const uint32_t krank = KCL ? cluster_ctarank() : 0u;   // which half of the contraction (KCL)
+    const int worker = (PAIR || KCL) ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int num_workers = (PAIR || KCL) ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -358,6 +372,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             mbar_init(tfull_bar(b), 1);
             mbar_init(tempty_bar(b), CG * 32 * EPI_WARPS);
         }
+        if constexpr (KCL) mbar_init(xdata_bar, 32 * EPI_WARPS / 2);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmA);
@@ -378,6 +393,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         cluster_arrive();
         cluster_wait();
     }
+    // KCL: the peer's barrier must be initialised before anything arrives on it, which happens only in the
+    // epilogue. Arrive now (release) and wait there — nobody stalls here for the cluster to assemble.
+    if constexpr (KCL) cluster_arrive();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
     // Everything above touched only shared and tensor memory; operands and outputs of the kernels
@@ -387,6 +405,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (tracing && threadIdx.x == 0) args.trace[1] = global_timer_ns();
 
     const int num_units = args.num_tiles * args.split_k;
+    [[maybe_unused]] bool kcl_waited = false;   // has this thread waited for the prologue's cluster barrier yet?
+    // KCL: this CTA's one unit is (tile = cluster index, split = rank in the cluster); no further units.
+    const int unit_first = KCL ? (int)krank * args.num_tiles + worker : worker;
+    const int unit_step = KCL ? num_units : num_workers;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -394,7 +416,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int u = worker; u < num_units && ok; u += num_workers) {
+            for (int u = unit_first; u < num_units && ok; u += unit_step) {
                 int t, split, ub0, ub1, tm, tn;
                 unit_decode(u, args, t, split, ub0, ub1);
                 tile_coords(t, args, tm, tn);
@@ -534,7 +556,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint32_t ph = 0;
             uint32_t cit = 0;   // accumulator hand-offs so far (chunks, over all tiles)
             bool ok = true;
-            for (int u = worker; u < num_units && ok; u += num_workers) {
+            for (int u = unit_first; u < num_units && ok; u += unit_step) {
                 int t, split, ub0, ub1;
                 unit_decode(u, args, t, split, ub0, ub1);
                 for (int kb0 = ub0; kb0 < ub1 && ok; kb0 += args.chunk_kb, ++cit) {
@@ -550,7 +572,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         ok = mbar_wait(full_bar(s), ph, abort_flag, args.status, kDevTimeoutFull);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        if (tracing && u == worker && kb == ub0) args.trace[2] = global_timer_ns();
+                        if (tracing && u == unit_first && kb == ub0) args.trace[2] = global_timer_ns();
                         const uint32_t st = smem_base + s * S::STAGE_BYTES;
                         const uint32_t a_hi = st;
                         const uint32_t a_lo = st + S::A_TILE;
@@ -595,7 +617,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         };
         uint32_t cit = 0;
         bool ok = true;
-        for (int u = worker; u < num_units && ok; u += num_workers) {
+        for (int u = unit_first; u < num_units && ok; u += unit_step) {
             int t, split, ub0, ub1, tm, tn;
             unit_decode(u, args, t, split, ub0, ub1);
             tile_coords(t, args, tm, tn);
@@ -636,6 +658,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     release(buf);
                 }
                 if (!ok) break;
+                if constexpr (KCL) {
+                    // Warp ew holds column half ew >> 2 of this CTA's partial tile; half k is finished by CTA k.
+                    // The same warp index sends in one CTA and receives in the other. A receiving warp's 8 KB
+                    // arrive in its own staging buffer (float4 slots 0..7 of each lane) and in that of the
+                    // sending warp beside it (slots 8..15), lane-interleaved: conflict-free both ways, and no
+                    // other warp's stores can touch them.
+                    constexpr int HALF = COLS / 8;   // float4 slots per staging buffer
+                    const uint32_t own_off = (uint32_t)(STAGES * S::STAGE_BYTES + ew * 4096 + lane * 16);
+                    const uint32_t side_off = (uint32_t)(STAGES * S::STAGE_BYTES + (ew ^ 4) * 4096 + lane * 16);
+                    cluster_wait();   // long since complete: the peer arrived in its prologue
+                    kcl_waited = true;
+                    if ((uint32_t)(ew >> 2) == krank) {
+                        ok = mbar_wait(xdata_bar, 0, abort_flag, args.status, kDevTimeoutPeer);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        fence_acq_rel_cluster();
+#pragma unroll
+                        for (int i = 0; i < 2 * HALF; ++i) {
+                            const float4 p = *reinterpret_cast<const float4*>(
+                                smem_gen + (i < HALF ? own_off + i * 512 : side_off + (i - HALF) * 512));
+                            acc[4 * i] += p.x; acc[4 * i + 1] += p.y; acc[4 * i + 2] += p.z; acc[4 * i + 3] += p.w;
+                        }
+                        __syncwarp();   // the staging buffer is about to be reused for the stores
+                    } else {
+                        const uint32_t peer = mapa_shared(smem_base, krank ^ 1u);
+#pragma unroll
+                        for (int i = 0; i < 2 * HALF; ++i)
+                            st_shared_cluster_v4(peer + (i < HALF ? own_off + i * 512 : side_off + (i - HALF) * 512),
+                                                 acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+                        fence_acq_rel_cluster();
+                        mbar_arrive_cluster(mapa_shared(xdata_bar, krank ^ 1u));
+                        break;   // the peer finishes these columns
+                    }
+                }
                 if constexpr (CONV == kConvSpatial) {
                     // Row r of the CTA's 128 is position (y0 + r / tw, x0 + r % tw) of sample n; column j
                     // goes to dst[n][j][y][x] (NCHW): lanes are consecutive x, so each store
@@ -714,6 +770,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (tracing && ew == 0 && lane == 0) args.trace[5] = global_timer_ns();
     }
 
+    // KCL: every thread pairs its prologue arrive with one wait. No second cluster barrier: each CTA has
+    // received everything the peer will ever write into it before it gets here.
+    if constexpr (KCL) {
+        __syncwarp();
+        if (!kcl_waited) cluster_wait();
+    }
     tc_fence_before_sync();
     __syncthreads();
     if constexpr (PAIR) {

@@ -111,6 +111,9 @@ int small_gemm_run(const GemmCall& call, cudaStream_t stream);
 // True when gemm_run would split this call's contraction between CTAs (its epilogue then runs in the
 // reduction kernel).
 bool gemm_uses_split_k(const GemmCall& call, int sm_count);
+// True when gemm_run would run this call with each tile's contraction shared by a cluster of two CTAs
+// (one tile per cluster, so its epilogue is short and off the critical path of any other tile).
+bool gemm_uses_cluster_k(const GemmCall& call, int sm_count);
 // True when an FP32 operand at `ptr` with leading dimension `ld` (and no element mask) can be its own hi
 // plane: 16-byte aligned, ld a multiple of 4, and the RAW_HI knob on.
 bool raw_hi_operand(const void* ptr, int64_t ld, const void* mask);

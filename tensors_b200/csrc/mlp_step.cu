@@ -396,7 +396,8 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         // longer epilogue costs the large-batch products more than the separate pass it saves).
         planes_ready = false;
         if (i + 1 < L && (out_f & 3) == 0 &&
-            (fuse == 2 || (fuse == 1 && (gemm_uses_split_k(c, st->sm_count) || small_gemm_eligible(c))))) {
+            (fuse == 2 || (fuse == 1 && (gemm_uses_split_k(c, st->sm_count) || gemm_uses_cluster_k(c, st->sm_count) ||
+                                         small_gemm_eligible(c))))) {
             // raw-hi form where the output itself can be the next product's hi plane
             ready_raw = raw_hi_operand(c.C, out_f, nullptr);
             c.planes_hi = ready_raw ? nullptr : m->xplanes[(size_t)i + 1];

@@ -34,7 +34,7 @@ constexpr Knob kKnobs[TFB_TUNE_COUNT] = {
     {"TFB_GEMM_BN", 0}, {"TFB_GEMM_PAIR", -1}, {"TFB_GEMM_SPLITK", 0}, {"TFB_GEMM_CHUNK_KB", 0},
     {"TFB_CONV_TMA", 1}, {"TFB_CONV_DIRECT", 1}, {"TFB_CONV_PAIR", -1}, {"TFB_HOST_PANEL", 512},
     {"TFB_PDL", 1}, {"TFB_FUSE_PLANES", 1}, {"TFB_GEMM_GROUP_M", 0}, {"TFB_SMALL_GEMM", 1},
-    {"TFB_RAW_HI", 0},
+    {"TFB_RAW_HI", 0}, {"TFB_CLUSTER_K", 1},
 };
 std::atomic<int> g_knob[TFB_TUNE_COUNT];
 std::once_flag g_knob_once;

@@ -476,3 +476,41 @@ def test_operand_as_its_own_hi_plane(oracle, raw_hi, trans_a, trans_b, product_p
             assert rel_err(got, oracle.matmul(a, b)) < FP32_TOL
     finally:
         capi.check(lib.tfb_set_tuning(capi.TUNE_RAW_HI, old.value))
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1024, 784, 1024), (1000, 900, 1100), (130, 128, 4096), (512, 640, 520)])
+def test_cluster_split_k_is_the_two_kernel_form_bit_for_bit(oracle, shape, trans_a, trans_b, product_path):
+    # FP32 products of a few 128 x 128 tiles with two K splits: by default (knob CLUSTER_K) the two halves of
+    # a tile run in the two CTAs of a cluster and meet in distributed shared memory; with the knob off they go
+    # through partial sums in scratch and the reduction kernel. Both add own + peer and then apply bias and
+    # ReLU, so the results must agree bit for bit; and both must match the oracle.
+    if product_path == "tensor_cores_only":
+        pytest.skip("none of these shapes is in the CUDA-core window")
+    M, N, K = shape
+    a, b = refdata.uniform(41, (M, K)), refdata.uniform(42, (K, N))
+    bias = refdata.normal(43, (N,))
+    A, B = dev(np.ascontiguousarray(a.T) if trans_a else a), dev(np.ascontiguousarray(b.T) if trans_b else b)
+    knobs = (capi.TUNE_GEMM_TILE_N, capi.TUNE_GEMM_PAIR, capi.TUNE_GEMM_SPLIT_K, capi.TUNE_CLUSTER_K)
+    old = []
+    for k in knobs:
+        v = ctypes.c_int(0)
+        capi.check(lib.tfb_get_tuning(k, ctypes.byref(v)))
+        old.append(v.value)
+    out = {}
+    try:
+        capi.check(lib.tfb_set_tuning(capi.TUNE_GEMM_TILE_N, 128))
+        capi.check(lib.tfb_set_tuning(capi.TUNE_GEMM_PAIR, 0))
+        capi.check(lib.tfb_set_tuning(capi.TUNE_GEMM_SPLIT_K, 2))
+        for cluster in (1, 0):
+            capi.check(lib.tfb_set_tuning(capi.TUNE_CLUSTER_K, cluster))
+            C = gemm_ex(A, B, M, N, K, trans_a, trans_b, bias=dev(bias), flags=capi.EPI_BIAS_COL | capi.EPI_RELU)
+            assert_device_ok()
+            out[cluster] = C.cpu().numpy()
+    finally:
+        for k, v in zip(knobs, old):
+            capi.check(lib.tfb_set_tuning(k, v))
+    assert not np.isnan(out[1]).any()
+    assert np.array_equal(out[1], out[0])
+    want = np.maximum(oracle.matmul(a, b) + bias[None, :], 0)
+    assert rel_err(out[1], want) < FP32_TOL
