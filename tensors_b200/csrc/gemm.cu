@@ -348,6 +348,20 @@ int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, cons
     return split_operand_on(st->sm_count, src, rows, cols, ld, mask, hi, lo, ld_out, stream);
 }
 
+int split_operands2(const float* src0, int64_t rows0, int64_t cols0, int64_t ld0, float* hi0, float* lo0, int64_t ld_out0,
+                    const float* src1, int64_t rows1, int64_t cols1, int64_t ld1, float* hi1, float* lo1, int64_t ld_out1,
+                    cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    if (rows0 <= 0 || cols0 <= 0) return split_operand_on(st->sm_count, src1, rows1, cols1, ld1, nullptr, hi1, lo1, ld_out1, stream);
+    if (rows1 <= 0 || cols1 <= 0) return split_operand_on(st->sm_count, src0, rows0, cols0, ld0, nullptr, hi0, lo0, ld_out0, stream);
+    const SplitJob a{src0, rows0, cols0, ld0, nullptr, hi0, lo0, ld_out0}, b{src1, rows1, cols1, ld1, nullptr, hi1, lo1, ld_out1};
+    // blocks shared out in proportion to the two sizes
+    const int ga = grid_for(rows0 * (ld_out0 >> 2), 256, st->sm_count), gb = grid_for(rows1 * (ld_out1 >> 2), 256, st->sm_count);
+    return launch_pdl(split_tf32_pair_kernel, dim3((unsigned)(ga + gb)), dim3(256), 0, stream, a, b, ga);
+}
+
 // Diagnostics: device buffer that CTA 0 of every GEMM launch stamps its phase times into (null = off).
 std::atomic<unsigned long long*> g_gemm_trace{nullptr};
 

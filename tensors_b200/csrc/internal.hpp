@@ -139,6 +139,10 @@ int make_map_nd(CUtensorMap* map, const void* base, int rank, const uint64_t* di
 
 // Splits a row-major FP32 matrix (rows x cols, leading dimension ld) into TF32 hi / lo
 // planes with leading dimension ld_out (multiple of 4, padding zero-filled).
+// Two matrices in one launch (no masks).
+int split_operands2(const float* src0, int64_t rows0, int64_t cols0, int64_t ld0, float* hi0, float* lo0, int64_t ld_out0,
+                    const float* src1, int64_t rows1, int64_t cols1, int64_t ld1, float* hi1, float* lo1, int64_t ld_out1,
+                    cudaStream_t stream);
 int split_operand(const float* src, int64_t rows, int64_t cols, int64_t ld, const float* mask,
                   float* hi, float* lo, int64_t ld_out, cudaStream_t stream);
 

@@ -342,16 +342,20 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
     // Where an operand can be its own hi plane (aligned, width a multiple of 4) only its lo plane is written:
     // the parameters as one flat vector, the batch, and each hidden activation.
     const bool raw_params = raw_hi_operand(m->params, m->numel, nullptr);
-    int rc = split_operand(m->params, 1, m->numel, m->numel, nullptr, raw_params ? nullptr : m->pplanes,
-                           m->pplanes + m->numel, m->numel, stream);
+    // ... in one launch with the batch, whose planes the first product needs
+    const int64_t in0 = m->dims[0], ld0 = round_up(in0, 4);
+    const bool raw_x = raw_hi_operand(X, in0, nullptr);
+    int rc = split_operands2(m->params, 1, m->numel, m->numel, raw_params ? nullptr : m->pplanes, m->pplanes + m->numel,
+                             m->numel, X, rows, in0, in0, raw_x ? nullptr : m->xplanes[0], m->xplanes[0] + rows * ld0, ld0,
+                             stream);
     if (rc != TFB_OK) return rc;
     std::vector<SavedPlanes> xs((size_t)L), ws((size_t)L);
     DeviceState* st = nullptr;
     rc = device_state(&st);
     if (rc != TFB_OK) return rc;
     const int fuse = tuning(TFB_TUNE_FUSE_PLANES);
-    bool planes_ready = false;   // did the product of the layer below already write this layer's input planes?
-    bool ready_raw = false;      // ... in the raw-hi form (lo plane only)?
+    bool planes_ready = true;    // are this layer's input planes written already (layer 0: above; else by the product below)?
+    bool ready_raw = raw_x;      // ... in the raw-hi form (lo plane only)?
     for (int i = 0; i < L; ++i) {
         const int64_t in_f = m->dims[(size_t)i], out_f = m->dims[(size_t)i + 1];
         const float* in = i == 0 ? X : m->act[(size_t)i];

@@ -15,6 +15,8 @@
 // whatever their layout in global memory, so the inner loop is two 16-byte shared-memory reads per four
 // FMAs; the read of the A row is a broadcast within a half-warp. Operands given as TF32 hi / lo planes are
 // added back together on the way in (hi + lo is exactly the original value).
+#include <utility>
+
 #include "internal.hpp"
 #include "ptx.cuh"
 
@@ -35,7 +37,9 @@ struct SmallArgs {
     float* C;
     int M, N, K;
     int k_per_split;      // K elements per block of the cluster (a multiple of 4)
-    long long sa_m, sa_k, sb_k, sb_n, ldc;
+    long long sa_m, sa_k, sb_k, sb_n;
+    long long sc_m, sc_n;  // C[m][n] at C[m * sc_m + n * sc_n]: (ldc, 1), or (1, ldc) when the product runs transposed
+    long long sp_m, sp_n;  // the same for the result planes
     const float* bias;
     int bias_mode, relu;
     float* planes_hi;     // optional TF32 planes of the result, leading dimension N
@@ -125,13 +129,14 @@ __global__ void __launch_bounds__(256) small_gemm_kernel(const SmallArgs a) {
     if (a.bias_mode == 1) acc += __ldg(a.bias + n);
     if (a.bias_mode == 2) acc += __ldg(a.bias + m);
     if (a.relu) acc = acc > 0.f ? acc : 0.f;
-    a.C[(long long)m * a.ldc + n] = acc;
+    a.C[(long long)m * a.sc_m + (long long)n * a.sc_n] = acc;
+    const long long po = (long long)m * a.sp_m + (long long)n * a.sp_n;
     if (a.planes_hi != nullptr) {
         const float hi = tf32_rn(acc);
-        a.planes_hi[(long long)m * a.N + n] = hi;
-        a.planes_lo[(long long)m * a.N + n] = acc - hi;
+        a.planes_hi[po] = hi;
+        a.planes_lo[po] = acc - hi;
     } else if (a.planes_lo != nullptr) {   // the consumer reads C itself as the hi plane
-        a.planes_lo[(long long)m * a.N + n] = tf32_rn(acc - __uint_as_float(__float_as_uint(acc) & 0xFFFFE000u));
+        a.planes_lo[po] = tf32_rn(acc - __uint_as_float(__float_as_uint(acc) & 0xFFFFE000u));
     }
 }
 
@@ -157,10 +162,11 @@ int launch_small(const SmallArgs& a, dim3 grid, cudaStream_t stream) {
 
 }  // namespace
 
+// Few rows, or — the same product read as C^T = B^T A^T — few columns (the 10-class head of an MLP).
 bool small_gemm_eligible(const GemmCall& c) {
     return tuning(TFB_TUNE_SMALL_GEMM) != 0 && c.in_dtype == TFB_DTYPE_F32 && c.out_dtype == TFB_DTYPE_F32 &&
-           c.a_mask == nullptr && c.force_bn == 0 && c.M <= kMaxRows && c.M * c.N <= kMaxOutputs && c.K >= kMinK &&
-           c.K <= kMaxK;
+           c.a_mask == nullptr && c.force_bn == 0 && (c.M <= kMaxRows || c.N <= kMaxRows) && c.M * c.N <= kMaxOutputs &&
+           c.K >= kMinK && c.K <= kMaxK;
 }
 
 int small_gemm_run(const GemmCall& c, cudaStream_t stream) {
@@ -177,9 +183,24 @@ int small_gemm_run(const GemmCall& c, cudaStream_t stream) {
     // b_kmajor: B stored [N][K] (K contiguous); else stored [K][N]
     a.sb_k = c.b_kmajor ? 1 : c.ldb;
     a.sb_n = c.b_kmajor ? c.ldb : 1;
-    a.ldc = c.ldc;
+    a.sc_m = c.ldc; a.sc_n = 1;
+    a.sp_m = c.N; a.sp_n = 1;
     a.bias = c.bias; a.bias_mode = c.bias_mode; a.relu = c.relu ? 1 : 0;
     a.planes_hi = c.planes_hi; a.planes_lo = c.planes_lo;
+    bool a_kfast = c.a_kmajor, b_kfast = c.b_kmajor;
+    if (c.M > kMaxRows) {
+        // Many rows, few columns: run C^T = B^T A^T, i.e. swap the operands' roles and store transposed.
+        std::swap(a.A, a.B);
+        std::swap(a.A_lo, a.B_lo);
+        const long long am = a.sa_m, ak = a.sa_k;
+        a.sa_m = a.sb_n; a.sa_k = a.sb_k;
+        a.sb_n = am; a.sb_k = ak;
+        std::swap(a.M, a.N);
+        std::swap(a.sc_m, a.sc_n);
+        std::swap(a.sp_m, a.sp_n);
+        if (a.bias_mode != 0) a.bias_mode = 3 - a.bias_mode;   // per column <-> per row
+        std::swap(a_kfast, b_kfast);
+    }
     if (a.planes_hi != nullptr && a.planes_lo == nullptr)
         return fail(TFB_ERR_INVALID_ARG, "gemm: a hi result plane without its lo plane");
     // one block of the cluster per 128 elements of K, at most eight (the portable cluster size)
@@ -187,10 +208,10 @@ int small_gemm_run(const GemmCall& c, cudaStream_t stream) {
     if (splits > kMaxSplit) splits = kMaxSplit;
     a.k_per_split = (int)(((c.K + splits - 1) / splits + 3) / 4 * 4);
     splits = (int)((c.K + a.k_per_split - 1) / a.k_per_split);
-    const dim3 grid((unsigned)((c.N + kTile - 1) / kTile), (unsigned)((c.M + kTile - 1) / kTile), (unsigned)splits);
-    if (c.a_kmajor && c.b_kmajor) return launch_small<true, true>(a, grid, stream);
-    if (c.a_kmajor && !c.b_kmajor) return launch_small<true, false>(a, grid, stream);
-    if (!c.a_kmajor && c.b_kmajor) return launch_small<false, true>(a, grid, stream);
+    const dim3 grid((unsigned)((a.N + kTile - 1) / kTile), (unsigned)((a.M + kTile - 1) / kTile), (unsigned)splits);
+    if (a_kfast && b_kfast) return launch_small<true, true>(a, grid, stream);
+    if (a_kfast && !b_kfast) return launch_small<true, false>(a, grid, stream);
+    if (!a_kfast && b_kfast) return launch_small<false, true>(a, grid, stream);
     return launch_small<false, false>(a, grid, stream);
 }
 

@@ -411,9 +411,10 @@ def test_batched_matmul_against_oracle(oracle, in_dtype):
 
 @pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True), (True, True)])
 @pytest.mark.parametrize("shape", [(64, 256, 784), (10, 1024, 1024), (1, 7, 513), (128, 128, 600), (33, 100, 1999),
-                                   (16, 1000, 2048)])
+                                   (16, 1000, 2048), (1024, 10, 1024), (700, 16, 784), (1000, 7, 513)])
 def test_few_rows_long_contraction_on_the_cuda_core_kernel(oracle, shape, trans_a, trans_b):
-    # the window of the one-launch CUDA-core kernel (at most 128 rows and 16384 outputs, K in 512..2048): every
+    # the window of the one-launch CUDA-core kernel (at most 128 rows — or, run transposed, at most 128 columns —
+    # and 16384 outputs, K in 512..2048): every
     # operand layout, ragged tiles, K slices that do not divide evenly between the blocks of a cluster,
     # bias and ReLU; plain FP32 FMAs, so the distance to an FP64 product is checked as well
     M, N, K = shape
