@@ -43,6 +43,8 @@ __device__ __forceinline__ float tf32_rna_c(float x) {
 __global__ void nhwc_split_kernel(const float* __restrict__ src, int C, int P, int cp, float* __restrict__ hi,
                                   float* __restrict__ lo, float* __restrict__ colsum) {
     __shared__ float tile[32][33];
+    pdl_wait();
+    pdl_launch_dependents();
     const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
     const int tx = threadIdx.x, ty = threadIdx.y;
     const float* s = src + (long long)n * C * P;
@@ -80,6 +82,8 @@ __global__ void nhwc_split_kernel(const float* __restrict__ src, int C, int P, i
 // both reading W[co][ci][tap].
 __global__ void filter_planes_kernel(const float* __restrict__ W, int Cout, int Cin, int khw, int cp, int by_cin,
                                      float* __restrict__ hi, float* __restrict__ lo) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int J = by_cin ? Cin : Cout, Cc = by_cin ? Cout : Cin;
     const long long total = (long long)J * khw * cp;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -102,6 +106,8 @@ __global__ void filter_planes_kernel(const float* __restrict__ W, int Cout, int 
 __global__ void wgrad_planes_reduce_kernel(const float* __restrict__ partial, int splits, long long split_stride,
                                            long long ld, int Cout, int Cin, int khw, int cp32,
                                            float* __restrict__ dW) {
+    pdl_wait();
+    pdl_launch_dependents();
     const long long total = (long long)Cout * Cin * khw;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -122,6 +128,8 @@ __global__ void wgrad_planes_reduce_kernel(const float* __restrict__ partial, in
 __global__ void colsum_kernel(const float* __restrict__ partial, long long rows, int cols, long long ld,
                               long long rows_per_block, float* __restrict__ out, int out_ld) {
     __shared__ float sm[8][33];
+    pdl_wait();
+    pdl_launch_dependents();
     const int c = blockIdx.x * 32 + threadIdx.x;
     const long long r0 = (long long)blockIdx.y * rows_per_block;
     const long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
@@ -162,13 +170,17 @@ int launch_feed(const CUtensorMap maps[5], const GemmArgs& args, int workers, cu
     cfg.blockDim = dim3((unsigned)gemm_threads(kKindTF32x3));
     cfg.dynamicSmemBytes = S::TOTAL;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = PAIR ? 2 : 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // every kernel of a convolution call waits in-kernel for the one before it (pdl_wait), so prologues
+    // and launch latencies overlap the predecessor's tail
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tuning(TFB_TUNE_PDL) != 0 ? 2 : 1;
     TFB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], args));
     return TFB_OK;
 }
@@ -187,9 +199,7 @@ int pow2_ceil_log2(int64_t v) {
 int to_nhwc_planes(const float* src, int64_t N, int64_t C, int64_t P, int64_t cp, float* hi, float* lo,
                    float* colsum, cudaStream_t stream) {
     dim3 grid((unsigned)((P + 31) / 32), (unsigned)((cp + 31) / 32), (unsigned)N), block(32, 8);
-    nhwc_split_kernel<<<grid, block, 0, stream>>>(src, (int)C, (int)P, (int)cp, hi, lo, colsum);
-    TFB_CUDA_OK(cudaGetLastError());
-    return TFB_OK;
+    return launch_pdl(nhwc_split_kernel, grid, block, 0, stream, src, (int)C, (int)P, (int)cp, hi, lo, colsum);
 }
 
 // 4-D maps (channel, x, y, sample) over NHWC hi / lo planes with a box of 32 channels x bw x bh positions,
@@ -287,14 +297,12 @@ int column_sums(const float* partial, int64_t rows, int64_t cols, int64_t ld, fl
     const int64_t stage_ld = (cols + 3) / 4 * 4;
     const long long per_block = (rows + kColsumStageBlocks - 1) / kColsumStageBlocks;
     const unsigned col_blocks = (unsigned)((cols + 31) / 32);
-    colsum_kernel<<<dim3(col_blocks, kColsumStageBlocks), dim3(32, 8), 0, stream>>>(partial, rows, (int)cols, ld,
-                                                                                    per_block > 0 ? per_block : 1, stage,
-                                                                                    (int)stage_ld);
-    TFB_CUDA_OK(cudaGetLastError());
-    colsum_kernel<<<dim3(col_blocks, 1), dim3(32, 8), 0, stream>>>(stage, kColsumStageBlocks, (int)cols, stage_ld,
-                                                                   kColsumStageBlocks, out, 0);
-    TFB_CUDA_OK(cudaGetLastError());
-    return TFB_OK;
+    int rc = launch_pdl(colsum_kernel, dim3(col_blocks, kColsumStageBlocks), dim3(32, 8), 0, stream, partial,
+                        (long long)rows, (int)cols, (long long)ld, (long long)(per_block > 0 ? per_block : 1), stage,
+                        (int)stage_ld);
+    if (rc != TFB_OK) return rc;
+    return launch_pdl(colsum_kernel, dim3(col_blocks, 1), dim3(32, 8), 0, stream, (const float*)stage,
+                      (long long)kColsumStageBlocks, (int)cols, (long long)stage_ld, (long long)kColsumStageBlocks, out, 0);
 }
 
 bool conv_tma_forced() {
@@ -339,9 +347,9 @@ int conv_tma_forward(const float* x, const float* w, const float* bias, float* o
     rc = to_nhwc_planes(x, s.N, s.Cin, P, cp, x_hi, x_lo, nullptr, stream);
     if (rc != TFB_OK) return rc;
     const long long ftotal = (long long)s.Cout * khw * cp;
-    filter_planes_kernel<<<grid_1d(ftotal), 256, 0, stream>>>(
-        w, (int)s.Cout, (int)s.Cin, (int)khw, (int)cp, 0, f_hi, f_lo);
-    TFB_CUDA_OK(cudaGetLastError());
+    rc = launch_pdl(filter_planes_kernel, dim3(grid_1d(ftotal)), dim3(256), 0, stream, w, (int)s.Cout, (int)s.Cin, (int)khw,
+                    (int)cp, 0, f_hi, f_lo);
+    if (rc != TFB_OK) return rc;
     SpatialCall c;
     c.src_hi = x_hi; c.src_lo = x_lo; c.src_c = s.Cin; c.src_cp = cp; c.src_H = s.H; c.src_W = s.W;
     c.f_hi = f_hi; c.f_lo = f_lo; c.J = s.Cout; c.out_H = s.outH; c.out_W = s.outW;
@@ -404,9 +412,9 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
         float* f_hi = reinterpret_cast<float*>(ws + o_fd);
         float* f_lo = f_hi + s.Cin * khw * cop;
         const long long ftotal = (long long)s.Cin * khw * cop;
-        filter_planes_kernel<<<grid_1d(ftotal), 256, 0, stream>>>(
-            w, (int)s.Cout, (int)s.Cin, (int)khw, (int)cop, 1, f_hi, f_lo);
-        TFB_CUDA_OK(cudaGetLastError());
+        rc = launch_pdl(filter_planes_kernel, dim3(grid_1d(ftotal)), dim3(256), 0, stream, w, (int)s.Cout, (int)s.Cin,
+                        (int)khw, (int)cop, 1, f_hi, f_lo);
+        if (rc != TFB_OK) return rc;
         SpatialCall c;
         c.src_hi = dy_hi; c.src_lo = dy_lo; c.src_c = s.Cout; c.src_cp = cop; c.src_H = s.outH; c.src_W = s.outW;
         c.f_hi = f_hi; c.f_lo = f_lo; c.J = s.Cin; c.out_H = s.H; c.out_W = s.W;
@@ -453,9 +461,10 @@ int conv_tma_backward(const float* x, const float* w, const float* dY, float* dX
         rc = launch_feed<128, 3, false, kConvWgrad>(maps, a, grid, stream);
         if (rc != TFB_OK) return rc;
         const long long total = (long long)s.Cout * s.Cin * khw;
-        wgrad_planes_reduce_kernel<<<grid_1d(total), 256, 0, stream>>>(
-            partial, (int)splits, rows_per_split * ld_part, ld_part, (int)s.Cout, (int)s.Cin, (int)khw, cp32, dW);
-        TFB_CUDA_OK(cudaGetLastError());
+        rc = launch_pdl(wgrad_planes_reduce_kernel, dim3(grid_1d(total)), dim3(256), 0, stream, (const float*)partial,
+                        (int)splits, (long long)(rows_per_split * ld_part), (long long)ld_part, (int)s.Cout, (int)s.Cin,
+                        (int)khw, (int)cp32, dW);
+        if (rc != TFB_OK) return rc;
     }
     return TFB_OK;
 }
