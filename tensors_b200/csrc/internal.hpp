@@ -163,9 +163,28 @@ struct SavedPlanes {
 };
 // linear_backward with X and / or W optionally given as saved hi / lo planes (FP32 only; X and W are
 // ignored for the operands whose planes are supplied).
+// A bias gradient whose final addition the caller batches with others: linear_backward_impl writes the
+// per-row-block partial column sums into `partial` (the caller's buffer, `capacity_floats` long; it must stay
+// untouched until the finish) and fills in the rest; colsum_finish_many adds them in the usual fixed order.
+struct DeferredColsum {
+    float* partial = nullptr;
+    size_t capacity_floats = 0;
+    long long blocks = 0, cols = 0, ld = 0;
+    float* out = nullptr;
+};
+constexpr int kMaxFinishJobs = 8;   // per launch; longer lists take several launches
+// Floats of partial sums a deferred bias gradient of `batch` x `out_f` needs.
+size_t deferred_colsum_floats(int64_t batch, int64_t out_f);
+// One launch (per kMaxFinishJobs jobs) that finishes the bias gradients and, if row_loss != nullptr, the loss
+// = -(1 / global_rows) * sum of row_loss[0, rows) — the same bits as the separate finish kernels give.
+int colsum_finish_many(const DeferredColsum* jobs, int n, const float* row_loss, int64_t rows, int64_t global_rows,
+                       float* loss_out, cudaStream_t stream);
 int linear_backward_impl(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
                          float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
-                         cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved);
+                         cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved, DeferredColsum* defer = nullptr);
+// log_softmax + NLL with the per-row losses left in row_loss (rows floats) for a later finish.
+int log_softmax_nll_rows(const float* logits, const int64_t* labels, float* dlogits, float* row_loss, int64_t rows,
+                         int64_t cols, int64_t global_rows, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------
 // nn::Conv2d (conv.cu: gather kernel, entry points; conv_tma.cu: TMA-fed path on the GEMM kernel)

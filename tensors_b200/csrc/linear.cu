@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "finish.cuh"
 #include "internal.hpp"
 #include "ptx.cuh"
 
@@ -112,34 +113,36 @@ __global__ void mask_colsum16_kernel(const T* __restrict__ dY, const T* __restri
     if (partial != nullptr) partial[(long long)blockIdx.y * ld_out + c] = s;
 }
 
-// db[c] = sum over row blocks of partial[b][c], in a fixed order: a block of 32 columns x 32 row
-// groups; group g adds blocks g, g+32, ... in ascending order (four loads in flight), then the 32 group
-// sums are added in ascending order.
-constexpr int kFinishGroups = 32;
+// db[c] = sum over row blocks of partial[b][c], in the fixed order of colsum_finish_block.
 __global__ void colsum_finish_kernel(const float* __restrict__ partial, long long blocks, long long cols,
                                      long long ld, float* __restrict__ out) {
     __shared__ float sm[kFinishGroups][33];
     pdl_wait();
     pdl_launch_dependents();
+    colsum_finish_block(partial, blocks, cols, ld, out, blockIdx.x, sm);
+}
 
-    const long long c = (long long)blockIdx.x * 32 + threadIdx.x;
-    float s = 0.f;
-    if (c < cols) {
-        long long b = threadIdx.y;
-        for (; b + 3 * kFinishGroups < blocks; b += 4 * kFinishGroups) {
-            const float p0 = partial[b * ld + c], p1 = partial[(b + kFinishGroups) * ld + c];
-            const float p2 = partial[(b + 2 * kFinishGroups) * ld + c], p3 = partial[(b + 3 * kFinishGroups) * ld + c];
-            s += p0; s += p1; s += p2; s += p3;
-        }
-        for (; b < blocks; b += kFinishGroups) s += partial[b * ld + c];
-    }
-    sm[threadIdx.y][threadIdx.x] = s;
-    __syncthreads();
-    if (threadIdx.y == 0 && c < cols) {
-        float t = 0.f;
-#pragma unroll
-        for (int g = 0; g < kFinishGroups; ++g) t += sm[g][threadIdx.x];
-        out[c] = t;
+// Several such reductions, and optionally a loss, in one launch: blockIdx.y selects the job (the loss is
+// the job after the last bias gradient), blockIdx.x the column block.
+struct FinishJobs {
+    DeferredColsum job[kMaxFinishJobs];
+    int n;
+    const float* row_loss;   // null: no loss job
+    long long rows;
+    float n_inv;
+    float* loss_out;
+};
+__global__ void finish_many_kernel(const FinishJobs J) {
+    __shared__ float sm[kFinishGroups][33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int j = (int)blockIdx.y;
+    if (j < J.n) {
+        const DeferredColsum& d = J.job[j];
+        if ((long long)blockIdx.x * 32 >= d.cols) return;
+        colsum_finish_block(d.partial, d.blocks, d.cols, d.ld, d.out, blockIdx.x, sm);
+    } else if (blockIdx.x == 0) {
+        loss_finish_block(J.row_loss, J.rows, J.n_inv, J.loss_out, (int)(threadIdx.y * 32 + threadIdx.x), &sm[0][0]);
     }
 }
 
@@ -161,9 +164,44 @@ int linear_forward(const void* X, const void* W, const float* bias, void* Y, int
     return gemm_run(c, stream);
 }
 
+size_t deferred_colsum_floats(int64_t batch, int64_t out_f) {
+    if (batch <= 0 || out_f <= 0) return 0;
+    const int64_t ldz = round_up(out_f, 4);
+    // colsum_rows_per_block shrinks the row blocks only while there are at most 512 of them (513 with a
+    // ragged last one); otherwise there is one per kColsumMaxRowsPerBlock rows. Any batch up to `batch` fits.
+    const int64_t full = (batch + kColsumMaxRowsPerBlock - 1) / kColsumMaxRowsPerBlock;
+    const int64_t most = full > 513 ? full : 513;
+    return (size_t)(most * ldz);
+}
+
+int colsum_finish_many(const DeferredColsum* jobs, int n, const float* row_loss, int64_t rows, int64_t global_rows,
+                       float* loss_out, cudaStream_t stream) {
+    for (int first = 0; first < n || (first == 0 && row_loss != nullptr); first += kMaxFinishJobs) {
+        FinishJobs J = {};
+        J.n = n - first < kMaxFinishJobs ? n - first : kMaxFinishJobs;
+        long long col_blocks = 1;
+        for (int i = 0; i < J.n; ++i) {
+            J.job[i] = jobs[first + i];
+            const long long cb = (J.job[i].cols + 31) / 32;
+            if (cb > col_blocks) col_blocks = cb;
+        }
+        const bool with_loss = first == 0 && row_loss != nullptr;
+        if (with_loss) {
+            J.row_loss = row_loss;
+            J.rows = rows;
+            J.n_inv = (float)(1.0 / (double)global_rows);
+            J.loss_out = loss_out;
+        }
+        const int rc = launch_pdl(finish_many_kernel, dim3((unsigned)col_blocks, (unsigned)(J.n + (with_loss ? 1 : 0))),
+                                  dim3(32, kFinishGroups), 0, stream, J);
+        if (rc != TFB_OK) return rc;
+    }
+    return TFB_OK;
+}
+
 int linear_backward_impl(const void* X, const void* W, const void* Y, const void* dY, void* dX, void* dW,
                                 float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
-                                cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved) {
+                                cudaStream_t stream, SavedPlanes xs, SavedPlanes wsaved, DeferredColsum* defer) {
     DeviceState* st = nullptr;
     int rc = device_state(&st);
     if (rc != TFB_OK) return rc;
@@ -199,7 +237,10 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
     }
 
     const size_t dz_bytes = align256((size_t)(batch * ldz) * (f32 ? 8 : 2));
-    const size_t partial_bytes = db != nullptr ? align256((size_t)(row_blocks * ldz) * 4) : 0;
+    const bool deferred = defer != nullptr && db != nullptr;
+    if (deferred && (defer->partial == nullptr || defer->capacity_floats < (size_t)(row_blocks * ldz)))
+        return fail(TFB_ERR_INVALID_ARG, "linear_backward: deferred bias-gradient buffer too small");
+    const size_t partial_bytes = db != nullptr && !deferred ? align256((size_t)(row_blocks * ldz) * 4) : 0;
     const size_t gx_bytes = dX != nullptr ? gemm_workspace_bytes(gx, st->sm_count) : 0;
     const size_t gw_bytes = dW != nullptr ? gemm_workspace_bytes(gw, st->sm_count) : 0;
     const size_t gemm_bytes = align256(gx_bytes > gw_bytes ? gx_bytes : gw_bytes);
@@ -208,7 +249,7 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
     if (rc != TFB_OK) return rc;
     uint8_t* ws = static_cast<uint8_t*>(ws_v);
     void* dz = ws;
-    float* partial = db != nullptr ? reinterpret_cast<float*>(ws + dz_bytes) : nullptr;
+    float* partial = db == nullptr ? nullptr : (deferred ? defer->partial : reinterpret_cast<float*>(ws + dz_bytes));
     void* gemm_ws = ws + dz_bytes + partial_bytes;
 
     const void* mask = relu ? Y : nullptr;
@@ -234,7 +275,10 @@ int linear_backward_impl(const void* X, const void* W, const void* Y, const void
                             static_cast<__half*>(dz), (long long)ldz, partial, rpb);
         if (rc != TFB_OK) return rc;
     }
-    if (db != nullptr) {
+    if (deferred) {
+        // the caller adds the partial sums later, batched with others (colsum_finish_many)
+        defer->blocks = row_blocks; defer->cols = out_f; defer->ld = ldz; defer->out = db;
+    } else if (db != nullptr) {
         rc = launch_pdl(colsum_finish_kernel, dim3((unsigned)((out_f + 31) / 32)), dim3(32, kFinishGroups), 0, stream,
                         (const float*)partial, (long long)row_blocks, (long long)out_f, (long long)ldz, db);
         if (rc != TFB_OK) return rc;
@@ -257,7 +301,7 @@ int linear_backward(const void* X, const void* W, const void* Y, const void* dY,
                     float* db, int64_t batch, int64_t in_f, int64_t out_f, bool relu, int dtype,
                     cudaStream_t stream) {
     return linear_backward_impl(X, W, Y, dY, dX, dW, db, batch, in_f, out_f, relu, dtype, stream, SavedPlanes(),
-                                SavedPlanes());
+                                SavedPlanes(), nullptr);
 }
 
 }  // namespace tfb

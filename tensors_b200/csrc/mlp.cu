@@ -1,6 +1,7 @@
 // The small HBM-bound kernels that keep an MLP training step on the device between its GEMMs:
 // log_softmax + mean negative log-likelihood (loss and gradient with respect to the logits) and
 // SGD with momentum. Both are one pass over their data; neither is a contraction.
+#include "finish.cuh"
 #include "internal.hpp"
 #include "ptx.cuh"
 
@@ -48,16 +49,7 @@ __global__ void loss_finish_kernel(const float* __restrict__ row_loss, long long
     __shared__ float sm[1024];
     pdl_wait();
     pdl_launch_dependents();
-
-    float s = 0.f;
-    for (long long r = threadIdx.x; r < rows; r += blockDim.x) s += row_loss[r];
-    sm[threadIdx.x] = s;
-    __syncthreads();
-    for (int o = blockDim.x / 2; o > 0; o >>= 1) {
-        if ((int)threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) *loss_out = (-1.0f * sm[0]) * n_inv;
+    loss_finish_block(row_loss, rows, n_inv, loss_out, (int)threadIdx.x, sm);   // launched with 1024 threads
 }
 
 // v <- mu * v + g; p <- p - lr * v   (separate multiply and add, like the host formula).
@@ -75,6 +67,17 @@ __global__ void sgd_momentum_kernel(float* __restrict__ p, float* __restrict__ v
 }
 
 }  // namespace
+
+int log_softmax_nll_rows(const float* logits, const int64_t* labels, float* dlogits, float* row_loss, int64_t rows,
+                         int64_t cols, int64_t global_rows, cudaStream_t stream) {
+    if (rows <= 0) return TFB_OK;
+    const float n_inv = (float)(1.0 / (double)global_rows);
+    const int block = 256;
+    const long long grid = (rows * 32 + block - 1) / block;
+    return launch_pdl(log_softmax_nll_kernel, dim3((unsigned)grid), dim3(block), 0, stream, logits,
+                      reinterpret_cast<const long long*>(labels), dlogits, row_loss, (long long)rows, (int)cols, n_inv);
+}
+
 }  // namespace tfb
 
 extern "C" {

@@ -239,6 +239,9 @@ struct tfb_mlp {
     std::vector<float*> xplanes;          // hi / lo planes of the input of layer i
     std::vector<float*> dx;               // gradient with respect to the input of layer i (i > 0)
     float* dz = nullptr;                  // gradient with respect to the logits
+    float* row_loss = nullptr;            // per-row losses of the last step (max_rows floats)
+    std::vector<float*> colsum;           // per layer: partial column sums of its bias gradient
+    std::vector<size_t> colsum_floats;
     // data-parallel group
     int rank = 0, world = 1;
     uint8_t* peer_region[tfb::kMaxWorld] = {nullptr};
@@ -411,21 +414,28 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
         rc = gemm_run(c, stream);
         if (rc != TFB_OK) return rc;
     }
-    // the loss contribution goes to the slot behind the gradients, so that the exchange sums it too
-    rc = tfb_log_softmax_nll(m->act[(size_t)L], labels, m->dz, m->grads + m->numel, rows, m->dims[(size_t)L],
-                             global_rows, stream);
+    // The final additions of the loss and of every layer's bias gradient are short single-block-column
+    // reductions that nothing in the backward pass waits for: they run as ONE launch at the end instead of one
+    // launch each between the products. The loss goes to the slot behind the gradients, so that the exchange
+    // sums it too.
+    rc = log_softmax_nll_rows(m->act[(size_t)L], labels, m->dz, m->row_loss, rows, m->dims[(size_t)L], global_rows,
+                              stream);
     if (rc != TFB_OK) return rc;
+    std::vector<DeferredColsum> finish((size_t)L);
     const float* upstream = m->dz;
     for (int i = L - 1; i >= 0; --i) {
         float* dX = i > 0 ? m->dx[(size_t)i] : nullptr;
         SavedPlanes wsv = dX != nullptr ? ws[(size_t)i] : SavedPlanes();
+        DeferredColsum& d = finish[(size_t)(L - 1 - i)];
+        d.partial = m->colsum[(size_t)i];
+        d.capacity_floats = m->colsum_floats[(size_t)i];
         rc = linear_backward_impl(nullptr, nullptr, m->act[(size_t)i + 1], upstream, dX, m->grads + m->w_off[(size_t)i],
                                   m->grads + m->b_off[(size_t)i], rows, m->dims[(size_t)i], m->dims[(size_t)i + 1],
-                                  i < L - 1, TFB_DTYPE_F32, stream, xs[(size_t)i], wsv);
+                                  i < L - 1, TFB_DTYPE_F32, stream, xs[(size_t)i], wsv, &d);
         if (rc != TFB_OK) return rc;
         upstream = dX;
     }
-    return TFB_OK;
+    return colsum_finish_many(finish.data(), L, m->row_loss, rows, global_rows, m->grads + m->numel, stream);
 }
 
 int check_batch(const tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,
@@ -501,6 +511,13 @@ int tfb_mlp_create(int n_layers, const int64_t* dims, int64_t max_rows, tfb_mlp*
         if (i > 0) o_dx[(size_t)i] = reserve((size_t)(max_rows * dims[i]) * 4);
     }
     const size_t o_dz = reserve((size_t)(max_rows * dims[n_layers]) * 4);
+    const size_t o_rl = reserve((size_t)max_rows * 4);
+    std::vector<size_t> o_cs((size_t)n_layers, 0);
+    m->colsum_floats.assign((size_t)n_layers, 0);
+    for (int i = 0; i < n_layers; ++i) {
+        m->colsum_floats[(size_t)i] = deferred_colsum_floats(max_rows, dims[i + 1]);
+        o_cs[(size_t)i] = reserve(m->colsum_floats[(size_t)i] * 4);
+    }
     e = cudaMalloc(reinterpret_cast<void**>(&m->arena), need);
     if (e != cudaSuccess) {
         (void)cudaGetLastError();
@@ -525,6 +542,9 @@ int tfb_mlp_create(int n_layers, const int64_t* dims, int64_t max_rows, tfb_mlp*
         if (i > 0) m->dx[(size_t)i] = reinterpret_cast<float*>(m->arena + o_dx[(size_t)i]);
     }
     m->dz = reinterpret_cast<float*>(m->arena + o_dz);
+    m->row_loss = reinterpret_cast<float*>(m->arena + o_rl);
+    m->colsum.assign((size_t)n_layers, nullptr);
+    for (int i = 0; i < n_layers; ++i) m->colsum[(size_t)i] = reinterpret_cast<float*>(m->arena + o_cs[(size_t)i]);
     // parameters, gradients, flags, velocity and loss start at zero
     if (cudaMemset(m->region, 0, m->region_bytes) != cudaSuccess ||
         cudaMemset(m->arena, 0, o_pp) != cudaSuccess) {
