@@ -274,6 +274,37 @@ def test_mlp_step_with_operands_as_their_own_hi_planes(oracle):
         capi.check(lib.tfb_set_tuning(capi.TUNE_RAW_HI, old.value))
 
 
+def test_deep_mlp_finishes_every_bias_gradient_in_batches():
+    # Eleven layers: the final additions of the loss and of the bias gradients run as batched launches of at
+    # most eight reductions each, so this step needs two of them. Checked against a float64 autograd walk of
+    # the same network (no reference counterpart has this depth); widths are small, so a ReLU tie is
+    # improbable, and the tolerance would still tell a missing layer (its bias gradient would be zero or stale).
+    from tensors_b200.mlp import MLP
+    dims = (40, 36, 36, 32, 32, 28, 28, 24, 24, 20, 16, 10)
+    L = len(dims) - 1
+    rng = np.random.default_rng(5)
+    ws = [(rng.standard_normal((dims[i + 1], dims[i])) * np.sqrt(2.0 / dims[i])).astype(np.float32) for i in range(L)]
+    bs = [(rng.standard_normal(dims[i + 1]) * 0.1).astype(np.float32) for i in range(L)]
+    x = rng.standard_normal((96, dims[0])).astype(np.float32)
+    lab = rng.integers(0, dims[-1], 96).astype(np.int64)
+    m = MLP(dims, ws, biases=bs, max_rows=96)
+    m.forward_backward(dev(x), torch.from_numpy(lab).cuda())
+    assert_device_ok()
+    tw = [torch.tensor(w, dtype=torch.float64, requires_grad=True) for w in ws]
+    tb = [torch.tensor(b, dtype=torch.float64, requires_grad=True) for b in bs]
+    h = torch.tensor(x, dtype=torch.float64)
+    for i in range(L):
+        h = h @ tw[i].T + tb[i]
+        if i < L - 1:
+            h = torch.relu(h)
+    loss = torch.nn.functional.cross_entropy(h, torch.from_numpy(lab))
+    loss.backward()
+    assert abs(local_loss(m) - float(loss)) < 1e-5
+    for i in range(L):
+        assert rel_err(m.bias(i, m.grads).cpu().numpy(), tb[i].grad.numpy()) < 1e-4, i
+        assert rel_err(m.weight(i, m.grads).cpu().numpy(), tw[i].grad.numpy()) < 1e-4, i
+
+
 def test_mlp_full_batch_data_parallel_invariance(oracle):
     # The named configuration at its full global batch of 8192 rows. The batch is cut into G row shards
     # as G data-parallel ranks would hold them; each shard's gradient is scaled by the GLOBAL batch, so
