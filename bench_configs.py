@@ -107,7 +107,7 @@ def config2(iters):
 
 EXCHANGE = "peer"
 MLP_ROWS = 0
-CONV_N, CONV_LAYERS, CONV_PASSES = 128, ("1", "2"), ("forward", "dgrad", "wgrad+dbias")
+CONV_N, CONV_LAYERS, CONV_PASSES = 128, ("1", "2"), ("forward", "dgrad", "wgrad+dbias", "backward")
 
 
 def config3(iters):
@@ -128,13 +128,16 @@ def config3(iters):
         fwd = lambda: capi.check(lib.tfb_conv2d_forward(p(xin), p(w), p(bias), p(y), *args, 0, 0, stream()))
         dgr = lambda: capi.check(lib.tfb_conv2d_backward(p(xin), p(w), p(g), p(gi), None, None, *args, 0, stream()))
         wgr = lambda: capi.check(lib.tfb_conv2d_backward(p(xin), p(w), p(g), None, p(gw), p(gb), *args, 0, stream()))
-        for what, fn in (("forward", fwd), ("dgrad", dgr), ("wgrad+dbias", wgr)):
+        # "backward": all three gradients in one call, as nn::Conv2d::backward computes them (the upstream
+        # gradient's planes are made once for both products); two passes' worth of FLOPs
+        bwd = lambda: capi.check(lib.tfb_conv2d_backward(p(xin), p(w), p(g), p(gi), p(gw), p(gb), *args, 0, stream()))
+        for what, fn, passes in (("forward", fwd, 1), ("dgrad", dgr, 1), ("wgrad+dbias", wgr, 1), ("backward", bwd, 2)):
             if what not in CONV_PASSES:
                 continue
             us = time_us(fn, iters)
             gus = graph_us(fn, iters)
             emit(config=3, what=f"Conv2d {name} {what}, N={N} 32x32 3x3 p1", us=us, graph_us=gus,
-                 tflops=gflop / gus * 1e3, gbs=alg_bytes / gus / 1e3)
+                 tflops=passes * gflop / gus * 1e3, gbs=passes * alg_bytes / gus / 1e3)
 
 
 def config4(iters):
@@ -293,7 +296,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--conv-n", type=int, default=128, help="config 3: batch size")
     ap.add_argument("--conv-layers", default="1,2", help="config 3: which layers")
-    ap.add_argument("--conv-passes", default="forward,dgrad,wgrad+dbias", help="config 3: which passes")
+    ap.add_argument("--conv-passes", default="forward,dgrad,wgrad+dbias,backward", help="config 3: which passes (backward = all three gradients in one call)")
     ap.add_argument("--mlp-rows", type=int, default=0,
                     help="config 5 on one GPU: run only this many rows of the global batch of 8192 (the shard of one "
                          "rank of a larger group)")
