@@ -436,6 +436,8 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
             return mma + partials;
         };
         const bool f32 = c.in_dtype == TFB_DTYPE_F32;
+        const bool pair0 = p.pair;
+        const int bn0 = p.bn;   // the plan without a split, to fall back to
         const bool pair_ok = !c.force_bn && !env_bn && env_pair != 0 && c.M >= 256 && c.N >= 256;
         int bn1 = p.bn;
         if (!c.force_bn && !env_bn && c.N >= 128) bn1 = c.N >= 256 ? 256 : 128;   // wide tiles feed the MMA better
@@ -461,6 +463,35 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
             tuning(TFB_TUNE_CLUSTER_K) != 0) {
             p.cluster_k = true;
             p.partial_bytes = 0;
+        }
+        // A split that goes through scratch also pays for a second launch (~8000 clocks with its gap): keep
+        // the unsplit plan where that is cheaper (measured: a 1024-cubed BF16 product takes 7.5 us unsplit,
+        // 12.9 us as two splits + reduction; with a 4096-long contraction on 512 x 512 outputs the split wins
+        // 10.9 to 18.9 us).
+        if (p.split_k > 1 && !p.cluster_k && env_split <= 0) {
+            auto clk_kb = [&](int bn, bool pair) {
+                if (f32) return pair ? 1536 : (bn == 256 ? 1800 : (bn == 128 ? 1000 : 700));
+                // 16-bit tiles of one CTA are bound by the latency of a K block, not by the tensor pipe
+                // (measured: ~500 clocks per K block for 64- and 128-column tiles)
+                return pair ? 512 : (bn == 256 ? 600 : 500);
+            };
+            Split cur;
+            cur.split_k = p.split_k;
+            cur.kb_per_split = p.kb_per_split;
+            const long long workers_now = p.pair ? sm_count / 2 : sm_count;
+            const long long tiles_cur = p.pair ? pair_tiles : tiles_now;
+            const double split_cost = cost(cur, tiles_cur, workers_now, clk_kb(p.bn, p.pair)) + 8000.0;
+            const long long tiles0 = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + bn0 - 1) / bn0);
+            const double plain_cost = (double)((tiles0 + sm_count - 1) / sm_count) * p.k_blocks * clk_kb(bn0, false);
+            if (plain_cost <= split_cost) {
+                p.pair = pair0;
+                p.bn = bn0;
+                p.split_k = 1;
+                p.kb_per_split = p.k_blocks;
+                p.rows_per_split = 0;
+                p.ld_partial = 0;
+                p.partial_bytes = 0;
+            }
         }
     }
     return p;
