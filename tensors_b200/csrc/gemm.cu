@@ -447,8 +447,14 @@ GemmPlan gemm_plan(const GemmCall& c, int sm_count) {
         // third candidate: single-CTA tiles of 128 columns, twice as many tiles and half as many splits
         const long long tiles128 = ((c.M + kBlockM - 1) / kBlockM) * ((c.N + 127) / 128);
         const Split sp_128 = (pair_ok && env_pair < 0) ? split_plan(sm_count, tiles128, kBlockM) : Split();
-        if (sp_pair.ok && sp_128.ok &&
-            cost(sp_128, tiles128, sm_count, f32 ? 1000 : 340) < cost(sp_pair, pair_tiles, sm_count / 2, f32 ? 1536 : 512)) {
+        // two splits of 128 x 128 FP32 tiles with a tile per SM pair at most add their halves on chip (below):
+        // no partial traffic, no second launch; every other split pays for the reduction launch (~8000 clocks)
+        const bool kcl_128 = f32 && sp_128.ok && sp_128.split_k == 2 && tiles128 * 2 <= sm_count &&
+                             tuning(TFB_TUNE_CLUSTER_K) != 0;
+        const double cost_128 = !sp_128.ok ? 0.0
+                                : kcl_128  ? ((double)sp_128.kb_per_split * 1000.0 + 5000.0) / 0.9   // measured: a tie at K = 4096
+                                           : cost(sp_128, tiles128, sm_count, f32 ? 1000 : 340) + 8000.0;
+        if (sp_pair.ok && sp_128.ok && cost_128 < cost(sp_pair, pair_tiles, sm_count / 2, f32 ? 1536 : 512) + 8000.0) {
             apply(sp_128, false, 128);
         } else if (sp_pair.ok) {
             // CTA pairs keep the tensor pipe fuller than single CTAs (deeper ring per MMA), so prefer them
