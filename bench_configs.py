@@ -107,6 +107,7 @@ def config2(iters):
 
 EXCHANGE = "peer"
 MLP_ROWS = 0
+BUCKETS = 0
 CONV_N, CONV_LAYERS, CONV_PASSES = 128, ("1", "2"), ("forward", "dgrad", "wgrad+dbias", "backward")
 
 
@@ -169,6 +170,8 @@ def config5(iters):
     X = dev(refdata.mnist_like(7, (batch, 784))[b:e])
     labels = torch.from_numpy(refdata.labels(8, batch)[b:e]).cuda()
     m = MLP(dims, ws, max_rows=e - b, exchange=EXCHANGE)
+    if BUCKETS:
+        m.set_option(MLP.OPT_BUCKETS, BUCKETS)
     step = lambda: m.train_step(X, labels, lr=0.1, momentum=0.9, global_rows=batch)
     us_eager = time_us(step, iters)
     fb = time_us(lambda: m.forward_backward(X, labels, batch), iters)
@@ -297,13 +300,14 @@ def main():
     ap.add_argument("--conv-n", type=int, default=128, help="config 3: batch size")
     ap.add_argument("--conv-layers", default="1,2", help="config 3: which layers")
     ap.add_argument("--conv-passes", default="forward,dgrad,wgrad+dbias,backward", help="config 3: which passes (backward = all three gradients in one call)")
+    ap.add_argument("--buckets", type=int, default=0, help="config 5: exchange buckets (1 or 2; 0 = the handle's default)")
     ap.add_argument("--mlp-rows", type=int, default=0,
                     help="config 5 on one GPU: run only this many rows of the global batch of 8192 (the shard of one "
                          "rank of a larger group)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="config 5 with more than one rank")
     a = ap.parse_args()
-    global CONV_N, CONV_LAYERS, CONV_PASSES, EXCHANGE, MLP_ROWS
-    EXCHANGE, MLP_ROWS = a.exchange, a.mlp_rows
+    global CONV_N, CONV_LAYERS, CONV_PASSES, EXCHANGE, MLP_ROWS, BUCKETS
+    EXCHANGE, MLP_ROWS, BUCKETS = a.exchange, a.mlp_rows, a.buckets
     CONV_N, CONV_LAYERS, CONV_PASSES = a.conv_n, tuple(a.conv_layers.split(",")), tuple(a.conv_passes.split(","))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     capi.check(lib.tfb_init())

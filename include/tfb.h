@@ -395,11 +395,16 @@ int tfb_mlp_replay(tfb_mlp* m, void* stream);
  * exchange also store the summed gradient of this rank's slice into REDUCED_GRADS. TRACE_EXCHANGE: non-zero
  * makes CTA 0 of the exchange kernel record nanosecond timestamps at its phase boundaries (start, after the
  * first flag barrier, after the slice has been summed / updated / stored, after the system-scope fence,
- * after the second barrier) into EXCHANGE_TRACE. */
+ * after the second barrier) into EXCHANGE_TRACE. EXCHANGE_BUCKETS: 1 = one exchange launch behind the backward
+ * pass; 2 = a whole step (tfb_mlp_step, or a captured TFB_MLP_CAPTURE_STEP) exchanges the gradients of every
+ * layer but the first on a side stream of the handle as soon as they are complete — concurrently with the
+ * first layer's weight gradient, on at most 32 SMs — and the first layer's behind it; same sums in the same
+ * order, so the same bits (every rank of a group must use the same value). */
 #define TFB_MLP_OPT_WAIT_LIMIT_NS 0
 #define TFB_MLP_OPT_EXCHANGE_CTAS 1
 #define TFB_MLP_OPT_KEEP_REDUCED_GRADS 2
 #define TFB_MLP_OPT_TRACE_EXCHANGE 3
+#define TFB_MLP_OPT_EXCHANGE_BUCKETS 4
 int tfb_mlp_set_option(tfb_mlp* m, int option, int64_t value);
 
 /* Forming a group of `world` <= 8 ranks (one handle per rank, same dims). The library does not own a

@@ -54,6 +54,9 @@ struct DpParams {
     DpRank ranks[kMaxWorld];      // one entry per rank this launch runs (blockIdx.y selects it)
     int world;
     long long n_vec;              // float4 vectors in the flat parameter / gradient buffers
+    long long vec_lo, vec_hi;     // the part of them this launch exchanges (a "bucket"); rank r owns slice r of it
+    int cta_base;                 // first flag row of this launch (concurrent launches use disjoint rows)
+    int with_loss;                // this launch also sums the ranks' loss contributions
     long long params_off, grads_off, flags_off;   // byte offsets inside a region
     float lr, mu;
     unsigned long long wait_ns;
@@ -64,7 +67,8 @@ struct DpParams {
 template <int WORLD, int U>
 __device__ __forceinline__ void exchange_slice_unrolled(const DpParams& p, const DpRank& me) {
     const int rank = me.rank;
-    const long long v0 = p.n_vec * rank / WORLD, v1 = p.n_vec * (rank + 1) / WORLD;
+    const long long span = p.vec_hi - p.vec_lo;
+    const long long v0 = p.vec_lo + span * rank / WORLD, v1 = p.vec_lo + span * (rank + 1) / WORLD;
     const float lr = p.lr, mu = p.mu;
     float4* my_params = reinterpret_cast<float4*>(me.region[rank] + p.params_off);
     float4* vel = reinterpret_cast<float4*>(me.velocity);
@@ -110,7 +114,8 @@ __device__ __forceinline__ void exchange_slice_unrolled(const DpParams& p, const
 template <int WORLD>
 __device__ __forceinline__ void exchange_slice(const DpParams& p, const DpRank& me, int world) {
     const int rank = me.rank;
-    const long long v0 = p.n_vec * rank / world, v1 = p.n_vec * (rank + 1) / world;
+    const long long span = p.vec_hi - p.vec_lo;
+    const long long v0 = p.vec_lo + span * rank / world, v1 = p.vec_lo + span * (rank + 1) / world;
     const float lr = p.lr, mu = p.mu;
     float4* my_params = reinterpret_cast<float4*>(me.region[rank] + p.params_off);
     float4* vel = reinterpret_cast<float4*>(me.velocity);
@@ -148,12 +153,12 @@ dp_exchange_kernel(const __grid_constant__ DpParams p) {
     pdl_wait();
     pdl_launch_dependents();
     const DpRank& me = p.ranks[blockIdx.y];
-    const int world = p.world, rank = me.rank, cta = blockIdx.x;
+    const int world = p.world, rank = me.rank, cta = p.cta_base + (int)blockIdx.x;   // flag row
     uint8_t* mine = me.region[rank];
     uint32_t* epoch_word = reinterpret_cast<uint32_t*>(mine + p.flags_off) + cta;
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(epoch_word) + 1u;
     const int t = threadIdx.x;
-    const bool tracing = me.trace != nullptr && cta == 0 && t == 0;
+    const bool tracing = me.trace != nullptr && cta == 0 && t == 0 && p.with_loss != 0;
     if (tracing) me.trace[0] = global_timer_ns();
 
     // Barrier 0: every rank's gradients (written by the kernels before this one on its stream) are complete.
@@ -171,7 +176,7 @@ dp_exchange_kernel(const __grid_constant__ DpParams p) {
     ok = __syncthreads_and(ok);
     if (tracing) me.trace[1] = global_timer_ns();
     if (ok) {
-        if (cta == 0 && t == 0) {
+        if (p.with_loss != 0 && blockIdx.x == 0 && t == 0) {
             // Loss: the ranks' contributions in rank order (the slot after the gradients).
             float l = 0.f;
             for (int r = 0; r < world; ++r) {
@@ -249,6 +254,11 @@ struct tfb_mlp {
     unsigned long long wait_ns = 2000000000ull;
     int exchange_ctas = 0;                // 0 = choose
     bool keep_reduced = false;
+    // Two-bucket step: the gradients of every layer but the first are exchanged on a side stream while the
+    // first layer's weight gradient is still being computed.
+    int buckets = 1;
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     // captured step
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
@@ -298,6 +308,10 @@ void fill_params(const tfb_mlp* m, DpParams& p, int world, float lr, float mu) {
     memset(&p, 0, sizeof(p));
     p.world = world;
     p.n_vec = m->numel / 4;
+    p.vec_lo = 0;
+    p.vec_hi = p.n_vec;
+    p.cta_base = 0;
+    p.with_loss = 1;
     p.params_off = 0;
     p.grads_off = (long long)m->grads_off;
     p.flags_off = (long long)m->flags_off;
@@ -306,15 +320,17 @@ void fill_params(const tfb_mlp* m, DpParams& p, int world, float lr, float mu) {
     p.wait_ns = m->wait_ns;
 }
 
-int exchange_grid(const tfb_mlp* m, int sm_count, int ranks_in_launch, int world) {
+int exchange_grid(const tfb_mlp* m, int sm_count, int ranks_in_launch, int world, long long vecs = -1, int cap = 0) {
     // At most one CTA per SM (all CTAs must be resident while they wait for their peers), and enough
     // of them to keep a few MB of peer loads in flight.
+    if (vecs < 0) vecs = m->numel / 4;
     int g = m->exchange_ctas > 0 ? m->exchange_ctas : 128;
+    if (cap > 0 && g > cap) g = cap;
     // A group of one waits for nobody, so its CTAs need not all be resident: fill the GPU.
     if (world == 1 && m->exchange_ctas == 0) g = 4 * sm_count;
     else if (g > sm_count / ranks_in_launch) g = sm_count / ranks_in_launch;
     if (g > kMaxExchangeCtas) g = kMaxExchangeCtas;
-    const long long vec_per_rank = m->numel / 4 / (world > 0 ? world : 1) + 1;
+    const long long vec_per_rank = vecs / (world > 0 ? world : 1) + 1;
     const long long want = (vec_per_rank + kExchangeThreads - 1) / kExchangeThreads;
     if (g > want) g = (int)want;
     if (g < 1) g = 1;
@@ -339,9 +355,58 @@ int launch_update(tfb_mlp* m, int world_in_kernel, float lr, float mu, cudaStrea
     return launch_pdl(dp_exchange_kernel, dim3((unsigned)grid, 1), dim3(kExchangeThreads), 0, stream, p);
 }
 
+// The flag rows of the early bucket of a two-bucket step, and its CTA limit: few enough to run on the SMs
+// the last weight-gradient product of a shard leaves free.
+constexpr int kEarlyBucketFlagRow = 128;
+constexpr int kEarlyBucketCtas = 32;
+
+// Exchange + update of the float4 range [lo, hi) of the flat buffers over the whole group.
+int launch_bucket(tfb_mlp* m, float lr, float mu, long long lo, long long hi, bool early, cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc != TFB_OK) return rc;
+    DpParams p;
+    fill_params(m, p, m->world, lr, mu);
+    fill_rank(m, p.ranks[0], st->status);
+    p.vec_lo = lo;
+    p.vec_hi = hi;
+    p.cta_base = early ? kEarlyBucketFlagRow : 0;
+    p.with_loss = early ? 0 : 1;
+    int grid = exchange_grid(m, st->sm_count, 1, m->world, hi - lo, early ? kEarlyBucketCtas : 0);
+    if (grid > kEarlyBucketFlagRow) grid = kEarlyBucketFlagRow;   // rows [0, 128) and [128, 256) stay disjoint
+    return launch_pdl(dp_exchange_kernel, dim3((unsigned)grid, 1), dim3(kExchangeThreads), 0, stream, p);
+}
+
+// True when a whole step of this handle runs as two buckets (tfb_mlp_step, and a captured whole step).
+bool two_buckets(const tfb_mlp* m) {
+    if (m->buckets != 2 || m->world < 2 || m->L < 2) return false;
+    for (int r = 0; r < m->world; ++r)
+        if (r != m->rank && m->peer_region[r] == nullptr) return false;
+    return true;
+}
+
+// The side stream and the two events of the two-bucket step, created on first use.
+int bucket_streams(tfb_mlp* m) {
+    if (m->side != nullptr) return TFB_OK;
+    TFB_CUDA_OK(cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking));
+    TFB_CUDA_OK(cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming));
+    TFB_CUDA_OK(cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming));
+    return TFB_OK;
+}
+
+// Forward, loss and backward of one batch. With `exchange` the group's exchange + update is part of the call
+// (lr, mu are then used): as one launch behind the backward pass, or — two_buckets(m) — with the gradients
+// of layers 1.. exchanged on the side stream as soon as layer 1's backward is enqueued, concurrently with
+// layer 0's weight gradient, and layer 0's (with the loss) behind it on `stream`, which then waits for the
+// side stream.
 int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, bool exchange = false, float lr = 0.f, float mu = 0.f) {
     const int L = m->L;
+    const bool bucketed = exchange && two_buckets(m);
+    if (bucketed) {
+        const int rcs = bucket_streams(m);
+        if (rcs != TFB_OK) return rcs;
+    }
     // Where an operand can be its own hi plane (aligned, width a multiple of 4) only its lo plane is written:
     // the parameters as one flat vector, the batch, and each hidden activation.
     const bool raw_params = raw_hi_operand(m->params, m->numel, nullptr);
@@ -434,8 +499,30 @@ int forward_backward(tfb_mlp* m, const float* X, const int64_t* labels, int64_t 
                                   i < L - 1, TFB_DTYPE_F32, stream, xs[(size_t)i], wsv, &d);
         if (rc != TFB_OK) return rc;
         upstream = dX;
+        if (bucketed && i == 1) {
+            // everything layers 1.. contribute is enqueued: finish their bias gradients and exchange them on
+            // the side stream (jobs 0 .. L-2 of `finish` are layers L-1 .. 1)
+            TFB_CUDA_OK(cudaEventRecord(m->ev_fork, stream));
+            TFB_CUDA_OK(cudaStreamWaitEvent(m->side, m->ev_fork, 0));
+            rc = colsum_finish_many(finish.data(), L - 1, nullptr, 0, global_rows, nullptr, m->side);
+            if (rc != TFB_OK) return rc;
+            rc = launch_bucket(m, lr, mu, m->w_off[1] / 4, m->numel / 4, true, m->side);
+            if (rc != TFB_OK) return rc;
+            TFB_CUDA_OK(cudaEventRecord(m->ev_join, m->side));
+        }
     }
-    return colsum_finish_many(finish.data(), L, m->row_loss, rows, global_rows, m->grads + m->numel, stream);
+    if (bucketed) {
+        rc = colsum_finish_many(&finish[(size_t)L - 1], 1, m->row_loss, rows, global_rows, m->grads + m->numel, stream);
+        if (rc != TFB_OK) return rc;
+        rc = launch_bucket(m, lr, mu, 0, m->w_off[1] / 4, false, stream);
+        if (rc != TFB_OK) return rc;
+        TFB_CUDA_OK(cudaStreamWaitEvent(stream, m->ev_join, 0));
+        return TFB_OK;
+    }
+    rc = colsum_finish_many(finish.data(), L, m->row_loss, rows, global_rows, m->grads + m->numel, stream);
+    if (rc != TFB_OK || !exchange) return rc;
+    if (m->world == 1) return launch_update(m, 1, lr, mu, stream);
+    return launch_update(m, m->world, lr, mu, stream);
 }
 
 int check_batch(const tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,
@@ -566,6 +653,9 @@ int tfb_mlp_destroy(tfb_mlp* m) {
     (void)cudaDeviceSynchronize();
     if (m->graph_exec != nullptr) (void)cudaGraphExecDestroy(m->graph_exec);
     if (m->graph != nullptr) (void)cudaGraphDestroy(m->graph);
+    if (m->ev_fork != nullptr) (void)cudaEventDestroy(m->ev_fork);
+    if (m->ev_join != nullptr) (void)cudaEventDestroy(m->ev_join);
+    if (m->side != nullptr) (void)cudaStreamDestroy(m->side);
     for (int r = 0; r < kMaxWorld; ++r)
         if (m->ipc_mapped[r] && m->peer_region[r] != nullptr) (void)cudaIpcCloseMemHandle(m->peer_region[r]);
     (void)cudaFree(m->arena);
@@ -634,11 +724,23 @@ int tfb_mlp_exchange_update(tfb_mlp* m, float lr, float momentum, void* stream) 
     return launch_update(m, m->world, lr, momentum, static_cast<cudaStream_t>(stream));
 }
 
+static int check_connected(const tfb_mlp* m, const char* who) {
+    for (int r = 0; r < m->world; ++r)
+        if (r != m->rank && m->peer_region[r] == nullptr)
+            return fail(TFB_ERR_INVALID_ARG, "%s: rank %d of %d is not connected", who, r, m->world);
+    return TFB_OK;
+}
+
 int tfb_mlp_step(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows, float lr,
                  float momentum, void* stream) {
-    int rc = tfb_mlp_forward_backward(m, X, labels, rows, global_rows, stream);
+    int rc = check_handle(m, "mlp_step");
     if (rc != TFB_OK) return rc;
-    return tfb_mlp_exchange_update(m, lr, momentum, stream);
+    if (global_rows <= 0) global_rows = rows;
+    rc = check_batch(m, X, labels, rows, global_rows, "mlp_step");
+    if (rc != TFB_OK) return rc;
+    rc = check_connected(m, "mlp_step");
+    if (rc != TFB_OK) return rc;
+    return forward_backward(m, X, labels, rows, global_rows, static_cast<cudaStream_t>(stream), true, lr, momentum);
 }
 
 int tfb_mlp_capture_step(tfb_mlp* m, const float* X, const int64_t* labels, int64_t rows, int64_t global_rows,
@@ -655,11 +757,18 @@ int tfb_mlp_capture_step(tfb_mlp* m, const float* X, const int64_t* labels, int6
         return fail(TFB_ERR_INVALID_ARG, "mlp_capture_step: the legacy default stream cannot be captured");
     if (m->graph_exec != nullptr) { (void)cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
     if (m->graph != nullptr) { (void)cudaGraphDestroy(m->graph); m->graph = nullptr; }
+    if (what == TFB_MLP_CAPTURE_STEP) {
+        rc = check_connected(m, "mlp_capture_step");
+        if (rc != TFB_OK) return rc;
+        if (two_buckets(m)) {
+            rc = bucket_streams(m);   // created before the capture begins
+            if (rc != TFB_OK) return rc;
+        }
+    }
     TFB_CUDA_OK(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
     rc = TFB_OK;
-    if (what == TFB_MLP_CAPTURE_STEP || what == TFB_MLP_CAPTURE_FORWARD_BACKWARD)
-        rc = forward_backward(m, X, labels, rows, global_rows, stream);
-    if (rc == TFB_OK && what == TFB_MLP_CAPTURE_STEP) rc = tfb_mlp_exchange_update(m, lr, momentum, stream);
+    if (what == TFB_MLP_CAPTURE_STEP) rc = forward_backward(m, X, labels, rows, global_rows, stream, true, lr, momentum);
+    if (what == TFB_MLP_CAPTURE_FORWARD_BACKWARD) rc = forward_backward(m, X, labels, rows, global_rows, stream);
     if (rc == TFB_OK && what == TFB_MLP_CAPTURE_UPDATE) rc = launch_update(m, 1, lr, momentum, stream);
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(stream, &g);
@@ -702,6 +811,10 @@ int tfb_mlp_set_option(tfb_mlp* m, int option, int64_t value) {
         return TFB_OK;
     case TFB_MLP_OPT_TRACE_EXCHANGE:
         m->trace_on = value != 0;
+        return TFB_OK;
+    case TFB_MLP_OPT_EXCHANGE_BUCKETS:
+        if (value != 1 && value != 2) return fail(TFB_ERR_INVALID_ARG, "mlp_set_option: 1 or 2 exchange buckets");
+        m->buckets = (int)value;
         return TFB_OK;
     default:
         return fail(TFB_ERR_INVALID_ARG, "mlp_set_option: unknown option %d", option);

@@ -56,7 +56,7 @@ class MLP:
 
     P_PARAMS, P_GRADS, P_VELOCITY, P_LOSS, P_REDUCED, P_ACT, P_REGION = range(7)
     CAP_STEP, CAP_FB, CAP_UPDATE = range(3)
-    OPT_WAIT_NS, OPT_CTAS, OPT_KEEP_REDUCED = range(3)
+    OPT_WAIT_NS, OPT_CTAS, OPT_KEEP_REDUCED, OPT_TRACE, OPT_BUCKETS = range(5)
 
     def __init__(self, dims, weights, biases=None, device="cuda", process_group=None, max_rows=8192,
                  exchange="peer"):
@@ -207,11 +207,15 @@ class MLP:
         return self.exchange == "peer" and self._distributed()
 
     def train_step(self, X, labels, lr=0.1, momentum=0.9, global_rows=None):
-        self.forward_backward(X, labels, global_rows)
         if self._use_peer():
+            # the whole step behind one call: with two exchange buckets (OPT_BUCKETS) the library overlaps
+            # the first of them with the end of the backward pass
             self.connect()
-            self.exchange_update(lr, momentum)
+            self._rows = int(X.shape[0])
+            self.capi.check(self.lib.tfb_mlp_step(self.handle, _p(X), _p(labels), self._rows,
+                                                  int(global_rows or self._rows), float(lr), float(momentum), _stream()))
         else:
+            self.forward_backward(X, labels, global_rows)
             self.allreduce_grads()
             self.sgd_step(lr, momentum)
         return self.loss

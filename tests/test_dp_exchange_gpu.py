@@ -131,8 +131,10 @@ def _two_process_worker(rank, world, port, out_dir):
     X = dev(refdata.mnist_like(7, (batch, 784))[b:e])
     L = torch.from_numpy(refdata.labels(8, batch)[b:e]).cuda()
     out = {}
-    for mode in ("peer", "nccl"):
-        m = MLP(dims, ws, max_rows=e - b, exchange=mode)
+    for mode in ("peer", "nccl", "peer2"):
+        m = MLP(dims, ws, max_rows=e - b, exchange="peer" if mode == "peer2" else mode)
+        if mode == "peer2":   # layers 1.. exchanged on a side stream while layer 0's weight gradient is computed
+            m.set_option(MLP.OPT_BUCKETS, 2)
         for _ in range(3):
             m.train_step(X, L, lr=0.1, momentum=0.9, global_rows=batch)
         replay = m.capture_train_step(X, L, lr=0.1, momentum=0.9, global_rows=batch, warmup=1)
@@ -143,24 +145,28 @@ def _two_process_worker(rank, world, port, out_dir):
         m.disconnect()
         dist.barrier()
         del m
-    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), peer=out["peer"][0], nccl=out["nccl"][0],
-             losses=np.array([out["peer"][1], out["nccl"][1]]), status=np.array([out["peer"][2], out["nccl"][2]]))
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), peer=out["peer"][0], nccl=out["nccl"][0], peer2=out["peer2"][0],
+             losses=np.array([out["peer"][1], out["nccl"][1], out["peer2"][1]]),
+             status=np.array([out["peer"][2], out["nccl"][2], out["peer2"][2]]))
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_process_group_peer_exchange_equals_nccl(tmp_path):
-    # Two processes, one GPU each: six steps with the fused peer-memory exchange and six with one NCCL
-    # all-reduce per step. With two ranks both sums are g0 + g1 (commutative), so the trajectories are
+    # Two processes, one GPU each: six steps with the fused peer-memory exchange, six with one NCCL
+    # all-reduce per step, and six with the peer exchange in two buckets (eager and from a captured graph
+    # with a forked side stream). With two ranks every sum is g0 + g1 (commutative), so the trajectories are
     # bit-identical, and both replicas of each run hold the same parameters.
     import torch.multiprocessing as mp
     mp.spawn(_two_process_worker, args=(2, 29541, str(tmp_path)), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
-    assert list(r0["status"]) == [0, 0] and list(r1["status"]) == [0, 0]
+    assert list(r0["status"]) == [0, 0, 0] and list(r1["status"]) == [0, 0, 0]
     assert np.array_equal(r0["peer"], r1["peer"])
     assert np.array_equal(r0["nccl"], r1["nccl"])
+    assert np.array_equal(r0["peer2"], r1["peer2"])
     assert np.array_equal(r0["peer"], r0["nccl"])
-    assert r0["losses"][0] == r0["losses"][1] == r1["losses"][0]
+    assert np.array_equal(r0["peer"], r0["peer2"])
+    assert r0["losses"][0] == r0["losses"][1] == r0["losses"][2] == r1["losses"][0] == r1["losses"][2]
 
 
 # ---- tfb_peer_group: small all-reduce through peer memory, and the batch-sharded convolution ---------
