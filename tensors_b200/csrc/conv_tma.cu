@@ -37,27 +37,43 @@ __device__ __forceinline__ float tf32_rna_c(float x) {
 }
 
 // src[n][c][p] (NCHW, p = y * W + x) -> hi / lo[n][p][cp] (NHWC, channels padded with zeros to cp).
-// One block transposes a 32-channel x 32-position tile through shared memory: reads are contiguous
-// in p, writes contiguous in c. If colsum != nullptr, colsum[(n * pblocks + pb) * cp + c] receives the
-// sum of the tile's 32 positions in ascending order (the bias-gradient partial sums).
+// One block transposes a 32-channel x 128-position tile through shared memory: reads are contiguous in p
+// (16 bytes per lane where the rows allow it, four of them in flight per thread — the pass is bound by bytes
+// in flight, not by DRAM), writes contiguous in c. If colsum != nullptr, colsum[(n * pblocks + pb) * cp + c]
+// receives, for each of the tile's four 32-position blocks pb, the sum of its positions in ascending order
+// (the bias-gradient partial sums).
+constexpr int kSplitTileP = 128;
 __global__ void nhwc_split_kernel(const float* __restrict__ src, int C, int P, int cp, float* __restrict__ hi,
-                                  float* __restrict__ lo, float* __restrict__ colsum) {
-    __shared__ float tile[32][33];
+                                  float* __restrict__ lo, float* __restrict__ colsum, int pblocks) {
+    __shared__ float tile[32][kSplitTileP + 1];
     pdl_wait();
     pdl_launch_dependents();
-    const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+    const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * kSplitTileP;
     const int tx = threadIdx.x, ty = threadIdx.y;
     const float* s = src + (long long)n * C * P;
+    const bool vec = (P & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const int c = c0 + ty + 8 * k, p = p0 + tx;
-        tile[ty + 8 * k][tx] = (c < C && p < P) ? s[(long long)c * P + p] : 0.f;
+        const int cl = ty + 8 * k, c = c0 + cl, p = p0 + 4 * tx;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < C) {
+            const float* row = s + (long long)c * P;
+            if (vec && p + 3 < P) {
+                v = *reinterpret_cast<const float4*>(row + p);
+            } else {
+                if (p < P) v.x = row[p];
+                if (p + 1 < P) v.y = row[p + 1];
+                if (p + 2 < P) v.z = row[p + 2];
+                if (p + 3 < P) v.w = row[p + 3];
+            }
+        }
+        tile[cl][4 * tx] = v.x; tile[cl][4 * tx + 1] = v.y; tile[cl][4 * tx + 2] = v.z; tile[cl][4 * tx + 3] = v.w;
     }
     __syncthreads();
     const int c = c0 + tx;
     if (c < cp) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
+#pragma unroll 4
+        for (int k = 0; k < kSplitTileP / 8; ++k) {
             const int pl = ty + 8 * k, p = p0 + pl;
             if (p < P) {
                 const float v = tile[tx][pl];
@@ -67,11 +83,14 @@ __global__ void nhwc_split_kernel(const float* __restrict__ src, int C, int P, i
                 lo[o] = v - h;
             }
         }
-        if (colsum != nullptr && ty == 0) {
-            float t = 0.f;
+        if (colsum != nullptr && ty < kSplitTileP / 32) {
+            const int pb = blockIdx.x * (kSplitTileP / 32) + ty;
+            if (pb < pblocks) {
+                float t = 0.f;
 #pragma unroll
-            for (int pl = 0; pl < 32; ++pl) t += tile[tx][pl];
-            colsum[((long long)n * gridDim.x + blockIdx.x) * cp + c] = t;
+                for (int pl = 0; pl < 32; ++pl) t += tile[tx][ty * 32 + pl];
+                colsum[((long long)n * pblocks + pb) * cp + c] = t;
+            }
         }
     }
 }
@@ -198,8 +217,9 @@ int pow2_ceil_log2(int64_t v) {
 
 int to_nhwc_planes(const float* src, int64_t N, int64_t C, int64_t P, int64_t cp, float* hi, float* lo,
                    float* colsum, cudaStream_t stream) {
-    dim3 grid((unsigned)((P + 31) / 32), (unsigned)((cp + 31) / 32), (unsigned)N), block(32, 8);
-    return launch_pdl(nhwc_split_kernel, grid, block, 0, stream, src, (int)C, (int)P, (int)cp, hi, lo, colsum);
+    dim3 grid((unsigned)((P + kSplitTileP - 1) / kSplitTileP), (unsigned)((cp + 31) / 32), (unsigned)N), block(32, 8);
+    return launch_pdl(nhwc_split_kernel, grid, block, 0, stream, src, (int)C, (int)P, (int)cp, hi, lo, colsum,
+                      (int)((P + 31) / 32));
 }
 
 // 4-D maps (channel, x, y, sample) over NHWC hi / lo planes with a box of 32 channels x bw x bh positions,
