@@ -72,9 +72,10 @@ const char* tfb_last_error_string(void);
  *                   stream order (environment: TFB_PDL)
  *   GEMM_GROUP_M    0 = default, else the number of M tiles per rasterisation group of the GEMM kernel (tiles
  *                   of one group are visited M-fastest, so a wave of CTAs shares that many A panels)
- *   SMALL_GEMM      1 (default) = FP32 products with at most 128 rows, at most 16384 outputs and a contraction
- *                   of 512..2048 run on the one-launch CUDA-core kernel (exact FP32 FMAs, K split over a
- *                   thread-block cluster), 0 = everything on the tensor-core path
+ *   SMALL_GEMM      1 (default) = FP32 products with at most 128 rows (or, run transposed, at most 128 columns),
+ *                   at most 16384 outputs and a contraction of 512..2048 run on the one-launch CUDA-core
+ *                   kernel (exact FP32 FMAs, K split over a thread-block cluster), 0 = everything on the
+ *                   tensor-core path
  *   RAW_HI          1 = a 16-byte aligned FP32 operand whose leading dimension is a multiple of 4 is read by
  *                   the tensor core as its own hi plane (kind::tf32 drops the low 13 mantissa bits) and
  *                   the split pass writes only the lo plane = the residual against that truncation, which
