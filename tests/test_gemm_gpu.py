@@ -480,7 +480,8 @@ def test_operand_as_its_own_hi_plane(oracle, raw_hi, trans_a, trans_b, product_p
 
 
 @pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True), (True, True)])
-@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1024, 784, 1024), (1000, 900, 1100), (130, 128, 4096), (512, 640, 520)])
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1024, 784, 1024), (1000, 900, 1100), (130, 128, 4096), (512, 640, 520),
+                                   (700, 1001, 777)])
 def test_cluster_split_k_is_the_two_kernel_form_bit_for_bit(oracle, shape, trans_a, trans_b, product_path):
     # FP32 products of a few 128 x 128 tiles with two K splits: by default (knob CLUSTER_K) the two halves of
     # a tile run in the two CTAs of a cluster and meet in distributed shared memory; with the knob off they go
