@@ -1,5 +1,6 @@
 // Host side of the implicit-GEMM convolution: tap tables, operand preparation, tiling, launches,
 // and the extern "C" entry points of nn::Conv2d forward / backward.
+#include <atomic>
 #include <cstring>
 
 #include <cuda_bf16.h>
@@ -101,12 +102,14 @@ int launch_conv(const CUtensorMap maps[2], const ConvArgs& args, int grid, size_
     using S = ConvSmem<BN, STAGES>;
     auto kern = conv_igemm_kernel<MODE, BN, STAGES>;
     const size_t smem = (size_t)S::fixed() + table_bytes;
-    static size_t attr_set[64] = {0};
+    // largest size set so far per (kernel variant, device); several host threads may get here at once
+    static std::atomic<size_t> attr_set[64];
     int dev = 0;
     TFB_CUDA_OK(cudaGetDevice(&dev));
-    if (attr_set[dev] < smem) {
+    if (dev < 0 || dev >= 64) return fail(TFB_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    if (attr_set[dev].load(std::memory_order_acquire) < smem) {
         TFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set[dev] = smem;
+        attr_set[dev].store(smem, std::memory_order_release);
     }
     kern<<<grid, kConvThreads, smem, stream>>>(maps[0], maps[1], args);
     TFB_CUDA_OK(cudaGetLastError());

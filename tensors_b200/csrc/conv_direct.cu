@@ -5,6 +5,7 @@
 // (lanes = consecutive positions: coalesced) and the filter from shared memory (all lanes read the same
 // address: a broadcast). Plain FP32 FMAs in the reference's accumulation order (channel, then filter
 // row, then filter column); any stride, padding and dilation.
+#include <atomic>
 #include <cstdlib>
 
 #include "internal.hpp"
@@ -345,13 +346,14 @@ int conv_direct_forward(const float* x, const float* w, const float* bias, float
 int conv_direct_dgrad(const float* dY, const float* w, float* dX, const ConvShape& s, cudaStream_t stream) {
     const long long P = s.H * s.W;
     const size_t smem = (size_t)(s.Cout * s.kH * s.kW * kDirectCin) * 4;
-    static size_t attr_set[64] = {0};
+    static std::atomic<size_t> attr_set[64];   // per device; several host threads may get here at once
     int dev = 0;
     TFB_CUDA_OK(cudaGetDevice(&dev));
-    if (smem > 48 * 1024 && attr_set[dev] < smem) {
+    if (dev < 0 || dev >= 64) return fail(TFB_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    if (smem > 48 * 1024 && attr_set[dev].load(std::memory_order_acquire) < smem) {
         TFB_CUDA_OK(cudaFuncSetAttribute(conv_direct_dgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kDgradSmemLimit));
-        attr_set[dev] = kDgradSmemLimit;
+        attr_set[dev].store(kDgradSmemLimit, std::memory_order_release);
     }
     dim3 grid((unsigned)((P + kDirectThreads - 1) / kDirectThreads), (unsigned)((s.Cin + kDirectCin - 1) / kDirectCin),
               (unsigned)s.N);
@@ -389,12 +391,13 @@ int conv_direct_wgrad(const float* x, const float* dY, float* dW, float* db, con
     float* partial = static_cast<float*>(ws_v);
     float* sums = reinterpret_cast<float*>(static_cast<uint8_t*>(ws_v) + part_bytes);
     float* stage = reinterpret_cast<float*>(static_cast<uint8_t*>(ws_v) + part_bytes + sums_bytes);
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];
     int dev = 0;
     TFB_CUDA_OK(cudaGetDevice(&dev));
-    if (!attr_set[dev]) {
+    if (dev < 0 || dev >= 64) return fail(TFB_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
         TFB_CUDA_OK(cudaFuncSetAttribute(conv_direct_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kWgSmem));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     dim3 grid((unsigned)chunk_groups, (unsigned)co_tiles, (unsigned)s.N);
     conv_direct_wgrad_kernel<<<grid, kWgThreads, kWgSmem, stream>>>(x, dY, partial, direct_args(s), (int)chunks,

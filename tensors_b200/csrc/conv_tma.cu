@@ -17,6 +17,7 @@
 //   bias gradient    column sums taken by the dY pre-pass
 //
 // Outputs are written NCHW (forward, input gradient) by the kernel's epilogue.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -177,12 +178,14 @@ int launch_feed(const CUtensorMap maps[5], const GemmArgs& args, int workers, cu
     static_assert(S::TOTAL <= 232448, "stage ring + staging exceed the 227 KB shared-memory limit");
     constexpr bool MN = (CONV == kConvWgrad);
     auto kern = gemm_tcgen05_kernel<kKindTF32x3, BN, STAGES, MN, MN, PAIR, CONV>;
-    static bool attr_set[64] = {false};
+    // once per (kernel variant, device); several host threads may get here at the same time
+    static std::atomic<bool> attr_set[64];
     int dev = 0;
     TFB_CUDA_OK(cudaGetDevice(&dev));
-    if (!attr_set[dev]) {
+    if (dev < 0 || dev >= 64) return fail(TFB_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    if (!attr_set[dev].load(std::memory_order_acquire)) {
         TFB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(PAIR ? 2 * workers : workers));
