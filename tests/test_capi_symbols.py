@@ -32,6 +32,28 @@ def test_python_prototypes_match_header():
     assert set(capi.PROTOTYPES) == declared_symbols()
 
 
+def header_defines(prefix):
+    text = open(os.path.join(ROOT, "include", "tfb.h")).read()
+    return {m.group(1): int(m.group(2)) for m in re.finditer(r"#define\s+(" + prefix + r"[A-Z0-9_]+)\s+(-?\d+)", text)}
+
+
+def test_python_constants_match_header_defines():
+    # the numbering of the tuning knobs and of the tfb_mlp options is part of the C-ABI: the Python side must
+    # not drift from include/tfb.h
+    import tensors_b200.capi as capi
+    from tensors_b200.mlp import MLP
+    knobs = header_defines("TFB_TUNE_")
+    count = knobs.pop("TFB_TUNE_COUNT")
+    assert sorted(knobs.values()) == list(range(count))
+    for name, value in knobs.items():
+        assert getattr(capi, name[len("TFB_"):]) == value, name
+    opts = header_defines("TFB_MLP_OPT_")
+    py = {"TFB_MLP_OPT_WAIT_LIMIT_NS": MLP.OPT_WAIT_NS, "TFB_MLP_OPT_EXCHANGE_CTAS": MLP.OPT_CTAS,
+          "TFB_MLP_OPT_KEEP_REDUCED_GRADS": MLP.OPT_KEEP_REDUCED, "TFB_MLP_OPT_TRACE_EXCHANGE": MLP.OPT_TRACE,
+          "TFB_MLP_OPT_EXCHANGE_BUCKETS": MLP.OPT_BUCKETS}
+    assert opts == py
+
+
 def test_tuning_knobs_and_host_only_queries_work_without_gpu():
     # knobs are plain host state (defaults, or the environment read once); nothing here touches CUDA
     import ctypes
