@@ -157,6 +157,12 @@ int tfb_matmul_batched(const void* A, const void* B, void* C, int64_t batch, int
  * so that the fixed latency of small products can be read off directly. NULL turns it off (the default).
  * ref: no counterpart. */
 int tfb_gemm_trace(void* device_stamps);
+/* Host function (no device needed): which plan tfb_gemm_ex would choose for an M x N x K product of `dtype`
+ * operands (both operands aligned, neither pre-split) on a device with `sm_count` SMs, under the current tuning
+ * knobs. plan_out receives 5 ints: tile columns (64 / 128 / 256), CTA pairs (0 / 1), K splits (1 = none),
+ * cluster split-K (0 / 1), CUDA-core small-product kernel (0 / 1; the other four are then 0). For tests that pin
+ * the dispatch and for hosts that want to know what a shape will cost. ref: no counterpart. */
+int tfb_gemm_describe_plan(int64_t M, int64_t N, int64_t K, int dtype, int sm_count, int* plan_out);
 
 /* General form. op(A) is M x K, op(B) is K x N:
  *   trans_a = 0: A stored [M,K] row-major (lda >= K); 1: A stored [K,M] row-major (lda >= M)

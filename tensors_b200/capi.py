@@ -41,6 +41,7 @@ PROTOTYPES = {
     "tfb_matmul": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_matmul_batched": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _vp]),
     "tfb_gemm_trace": (_i32, [_vp]),
+    "tfb_gemm_describe_plan": (_i32, [_i64, _i64, _i64, _i32, _i32, ctypes.POINTER(ctypes.c_int)]),
     "tfb_gemm_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32,
                            _vp, _i32, _vp]),
     "tfb_split_tf32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _vp]),

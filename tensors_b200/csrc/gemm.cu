@@ -784,6 +784,30 @@ int gemm_run_on(const GemmCall& c, cudaStream_t stream, const DeviceState* st) {
 
 }  // namespace tfb
 
+extern "C" int tfb_gemm_describe_plan(int64_t M, int64_t N, int64_t K, int dtype, int sm_count, int* plan_out) {
+    using namespace tfb;
+    if (plan_out == nullptr || M <= 0 || N <= 0 || K < 0 || sm_count < 2)
+        return fail(TFB_ERR_INVALID_ARG, "gemm_describe_plan: bad extent, SM count or output pointer");
+    if (dtype != TFB_DTYPE_F32 && dtype != TFB_DTYPE_F16 && dtype != TFB_DTYPE_BF16)
+        return fail(TFB_ERR_UNSUPPORTED, "gemm_describe_plan: unsupported dtype %d", dtype);
+    GemmCall c;
+    c.M = M; c.N = N; c.K = K;
+    c.lda = K; c.ldb = N; c.ldc = N;
+    c.in_dtype = dtype; c.out_dtype = TFB_DTYPE_F32;
+    if (small_gemm_eligible(c)) {
+        plan_out[0] = plan_out[1] = plan_out[2] = plan_out[3] = 0;
+        plan_out[4] = 1;
+        return TFB_OK;
+    }
+    const GemmPlan p = gemm_plan(c, sm_count);
+    plan_out[0] = p.bn;
+    plan_out[1] = p.pair ? 1 : 0;
+    plan_out[2] = p.split_k;
+    plan_out[3] = p.cluster_k ? 1 : 0;
+    plan_out[4] = 0;
+    return TFB_OK;
+}
+
 extern "C" int tfb_gemm_trace(void* device_stamps) {
     tfb::g_gemm_trace.store(static_cast<unsigned long long*>(device_stamps), std::memory_order_relaxed);
     return TFB_OK;

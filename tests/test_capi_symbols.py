@@ -54,6 +54,34 @@ def test_python_constants_match_header_defines():
     assert opts == py
 
 
+def test_dispatch_of_the_named_shapes_is_pinned():
+    # tfb_gemm_describe_plan is a host function: which kernel and split a shape gets on a 148-SM device under
+    # the default knobs. The choices below were each measured to be the fastest on a B200; a change of the cost
+    # model that moves one of them has to be measured again.
+    import tensors_b200.capi as capi
+    lib = capi.lib
+
+    def plan(M, N, K, dtype=capi.DTYPE_F32):
+        out = (ctypes.c_int * 5)()
+        assert lib.tfb_gemm_describe_plan(M, N, K, dtype, 148, out) == 0
+        return dict(zip(("tile_n", "pair", "splits", "cluster", "cuda_core"), out))
+
+    assert plan(8192, 8192, 8192) == dict(tile_n=256, pair=1, splits=1, cluster=0, cuda_core=0)       # the headline
+    assert plan(8192, 1024, 784) == dict(tile_n=256, pair=1, splits=1, cluster=0, cuda_core=0)        # MLP forward, full batch
+    assert plan(1024, 1024, 8192) == dict(tile_n=256, pair=1, splits=4, cluster=0, cuda_core=0)       # its weight gradients
+    assert plan(1024, 1024, 1024) == dict(tile_n=128, pair=0, splits=2, cluster=1, cuda_core=0)       # a 1024-row shard
+    assert plan(1024, 784, 1024) == dict(tile_n=128, pair=0, splits=2, cluster=1, cuda_core=0)
+    assert plan(2048, 1024, 1024) == dict(tile_n=128, pair=0, splits=1, cluster=0, cuda_core=0)       # a 2048-row shard
+    assert plan(64, 256, 784)["cuda_core"] == 1                                                       # config 2 forward
+    assert plan(10, 1024, 1024)["cuda_core"] == 1 and plan(1024, 10, 1024)["cuda_core"] == 1          # the 10-class head
+    assert plan(10, 1024, 8192)["cuda_core"] == 0 and plan(10, 1024, 8192)["splits"] > 1              # too long for it
+    assert plan(1024, 1024, 1024, capi.DTYPE_BF16)["splits"] == 1                                     # 7.5 us unsplit, 12.9 split
+    assert plan(512, 512, 4096, capi.DTYPE_BF16)["splits"] > 1                                        # 10.9 us split, 18.9 unsplit
+    out = (ctypes.c_int * 5)()
+    assert lib.tfb_gemm_describe_plan(0, 8, 8, 0, 148, out) == -1
+    assert lib.tfb_gemm_describe_plan(8, 8, 8, 7, 148, out) == -2
+
+
 def test_tuning_knobs_and_host_only_queries_work_without_gpu():
     # knobs are plain host state (defaults, or the environment read once); nothing here touches CUDA
     import ctypes
